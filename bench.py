@@ -1,0 +1,334 @@
+#!/usr/bin/env python
+"""Benchmark of the ViG forward (bi-GLA + block kernels) on B200: images/s, roofline of the scan kernel,
+end-to-end number through the public API with host buffers, and the CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload vig_t_1024|vig_s_224|vig_t_224]
+    python bench.py --impl reference ...        # the reference's CPU path (oracle port) on the host cores
+
+Under torchrun (N > 1) every rank runs the same per-GPU batch on its own GPU (image shards, no collective
+on the data path); time is the max over ranks of CUDA-event time; rank 0 prints one JSON line.
+Protocol follows the reference's ``throughput()`` (classification/main.py:389-406): eval mode, one fixed
+batch, warm-up forwards, then timed forwards.  Data are synthetic N(0,1) images and seeded random weights.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (preset, image size, per-GPU batch)
+    "vig_t_1024": ("vig_t_dk64", 1024, 64),
+    "vig_s_224": ("vig_s_dk64", 224, 128),
+    "vig_t_224": ("vig_t_dk64", 224, 128),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="vig_t_1024", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's)")
+    ap.add_argument("--graph", type=int, default=0, help="1: replay the forward as a CUDA graph in the timed region")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx = float(f[1])
+            except ValueError:
+                continue
+            for n, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_model_throughput(preset, size, seconds_cap=40.0):
+    """The oracle (port of the reference's naive PyTorch path) on the host cores: images/s on one image."""
+    import oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    shape = oracle.PRESETS[preset]
+    sd = oracle.make_state_dict(shape, seed=0)
+    img = oracle.make_images(1, size, seed=0)
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        oracle.vig_forward(sd, img, shape)
+    dt = time.perf_counter() - t0
+    return 1.0 / dt, dt
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference's own CPU implementation of the path (its naive recurrent bi-GLA inside its
+    module graph, restated in ``oracle/``) on all host threads; one step = one image of the workload."""
+    if rank != 0:
+        return
+    preset, size, batch = WORKLOADS[args.workload]
+    ips, dt = cpu_model_throughput(preset, size)          # doubles as warm-up and as the cost probe
+    budget = 150.0
+    warm = max(0, min(args.warmup, int(0.2 * budget / dt)))
+    steps = max(1, min(args.steps, int(0.8 * budget / dt)))
+    for _ in range(warm):
+        cpu_model_throughput(preset, size)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_model_throughput(preset, size)
+    el = time.perf_counter() - t0
+    value = steps / el
+    cores = os.cpu_count() or 1
+    sample = f"1 image of {size}x{size} per step ({steps} of the requested {args.steps} steps fit the time bound)"
+    line = {"impl": "reference", "metric": "images_per_sec", "value": value, "unit": "images/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warm, "ms_per_step": 1e3 * el / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, batch),
+            "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, batch):
+    preset, size, _ = WORKLOADS[args.workload]
+    return {"workload": f"{args.workload}: ViG {preset} forward, {size}x{size} images, patch 16 (L={(size // 16) ** 2}), "
+                        f"batch {batch} per GPU, 12 blocks, dk=dv=64",
+            "per_gpu_batch": batch, "image_size": size, "sharding": "images across GPUs, no collective",
+            "cache": "inputs and activations larger than L2 (126 MB)" if batch * 3 * size * size * 2 > 126e6 else "L2 flushed between steps"}
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    import torch.distributed as dist
+    import oracle
+    import vig_b200
+    from vig_b200 import ops as vops
+    from vig_b200 import modules as vmods
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    preset, size, batch = WORKLOADS[args.workload]
+    batch = args.batch or batch
+    shape = oracle.PRESETS[preset]
+    model = vig_b200.ViG.from_shape(shape)
+    model.load_state_dict(oracle.make_state_dict(shape, seed=0))
+    model = model.to(dev, torch.bfloat16).eval()
+    host_images = oracle.make_images(min(batch, 8), size, seed=rank).to(torch.bfloat16)
+    host_images = host_images.repeat((batch + host_images.shape[0] - 1) // host_images.shape[0], 1, 1, 1)[:batch].contiguous().pin_memory()
+    images = host_images.to(dev)
+    host_logits = torch.empty(batch, shape.num_classes, dtype=torch.bfloat16).pin_memory()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if batch * 3 * size * size * 2 <= 126e6 else None
+
+    # count launches of this library's kernels and time the scan operator with events on its stream
+    counts = {"launches": 0}
+    scan_events = []
+    timing = {"on": False}
+    orig = {n: getattr(vops, n) for n in ("bi_gla", "dwconv3x3", "gate_inject", "add_rmsnorm", "swiglu")}
+    L = (size // 16) ** 2
+    scan_launches = 3 if L > 64 else 1
+
+    def wrap(name, n_launch):
+        fn = orig[name]
+
+        def inner(*a, **k):
+            counts["launches"] += n_launch
+            if name == "bi_gla" and timing["on"]:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = fn(*a, **k)
+                e1.record()
+                scan_events.append((e0, e1))
+                return r
+            return fn(*a, **k)
+        return inner
+
+    for n in orig:
+        w = wrap(n, scan_launches if n == "bi_gla" else 1)
+        setattr(vops, n, w)
+        if hasattr(vig_b200, n):
+            setattr(vig_b200, n, w)
+
+    def step():
+        if flush is not None:
+            flush.fill_(1)
+        with torch.no_grad():
+            return model(images)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    graph = None
+    if args.graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = step()
+    sync_all()
+    sampler = ClockSampler(local)
+    sampler.start()
+    counts["launches"] = 0
+    timing["on"] = graph is None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+    e1.record()
+    sync_all()
+    timing["on"] = False
+    ms = e0.elapsed_time(e1)
+    launches = counts["launches"] if graph is None else None
+    clocks = sampler.stop()
+    if graph is not None:                                   # launches per replay = launches of one eager step
+        counts["launches"] = 0
+        step()
+        launches = counts["launches"] * args.steps
+        torch.cuda.synchronize()
+
+    # end to end through the public API: pinned host images -> device -> forward -> logits back to the host
+    sync_all()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        dimg = host_images.to(dev, non_blocking=True)
+        with torch.no_grad():
+            out = model(dimg)
+        host_logits.copy_(out, non_blocking=True)
+    f1.record()
+    sync_all()
+    ms_e2e = f0.elapsed_time(f1)
+
+    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t[0]), float(t[1])
+
+    # roofline of the scan operator: algorithmic bytes = (4 dk + 2 dv) * element size per token and head
+    H, dk, dv = shape.num_heads, shape.key_dim // shape.num_heads, shape.value_dim // shape.num_heads
+    alg_bytes = batch * H * L * (4 * dk + 2 * dv) * 2
+    alg_flops = batch * H * L * 2 * (2 * 64 * dk + 2 * 64 * dv + 4 * dk * dv)
+    if scan_events:
+        scan_ms = sum(a.elapsed_time(b) for a, b in scan_events) / len(scan_events)
+    else:                                                   # graph mode: time the operator alone, same shapes
+        scan_ms = time_scan_alone(vig_b200, batch, H, L, dk, dv, dev)
+    peak, peak_kind = peaks()
+    achieved = alg_bytes / (scan_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "bigla_traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        per_unit = tj.get("dram_bytes_per_token_head")
+        traffic = per_unit * batch * H * L if per_unit else None
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "kernel": "bi-GLA scan operator (all launches of one call)", "peak_kind": peak_kind,
+                "ms_per_launch": scan_ms, "algorithmic_bytes": alg_bytes,
+                "tensor_tflops_accounting": alg_flops / (scan_ms * 1e-3) / 1e12,
+                "share_of_step": scan_ms * shape.depth / (ms / args.steps)}
+
+    if rank == 0:
+        total_images = batch * world * args.steps
+        line = {"metric": "images_per_sec", "value": total_images / (ms * 1e-3), "unit": "images/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": workload_config(args, batch), "clocks": clocks, "gpu_launches": launches,
+                "e2e": {"value": total_images / (ms_e2e * 1e-3), "unit": "images/s",
+                        "h2d_bytes_per_step": host_images.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
+                "roofline": roofline, "graph": bool(args.graph)}
+        if world == 1 and not args.no_cpu_baseline:
+            ips, dt = cpu_model_throughput(preset, size)
+            line["cpu_baseline"] = {"value": ips, "unit": "images/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": f"1 image of {size}x{size} through the CPU oracle (naive recurrent bi-GLA), {dt:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def time_scan_alone(vig_b200, batch, H, L, dk, dv, dev, reps=10):
+    q = torch.randn(batch, L, H * (2 * dk + dv), device=dev, dtype=torch.bfloat16)
+    g = torch.randn(batch, L, 2 * H * dk, device=dev, dtype=torch.bfloat16)
+    heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)
+    a = (heads(q[..., :H * dk], dk), heads(q[..., H * dk:2 * H * dk], dk), heads(q[..., 2 * H * dk:], dv),
+         heads(g[..., :H * dk], dk), heads(g[..., H * dk:], dk))
+    o = torch.empty(batch, L, H, dv, device=dev, dtype=torch.bfloat16).permute(0, 2, 1, 3)
+    for _ in range(3):
+        vig_b200.ops.bi_gla(*a, out=o, gate_logit_normalizer=16.0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        vig_b200.ops.bi_gla(*a, out=o, gate_logit_normalizer=16.0)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+if __name__ == "__main__":
+    main()

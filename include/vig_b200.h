@@ -1,0 +1,143 @@
+/*
+ * vig_b200 -- C ABI of the B200 (sm_100a) bi-directional gated-linear-attention operator and the
+ * bandwidth-bound kernels of the ViG block around it.
+ *
+ * Conventions (all entry points):
+ *   - plain C: pointers are DEVICE pointers unless stated otherwise, sizes are ints, no C++ types;
+ *   - nothing is allocated and nothing synchronises: the caller owns every buffer (workspace
+ *     included) and every launch goes to the `stream` argument (a cudaStream_t passed as void*);
+ *   - return value: 0 = ok, < 0 = rejected argument (VIG_ERR_*), > 0 = a cudaError_t value;
+ *   - dtype codes: 0 = fp32, 1 = bf16, 2 = fp16.  Accumulation, cumulative gates and scan states
+ *     are always fp32;
+ *   - one thread per device at a time per entry point (the reference has the same rule: one Python
+ *     thread per process, one process per GPU).
+ *
+ * Paths cited below are those of the reference repository (hustvl/ViG).
+ */
+#ifndef VIG_B200_H
+#define VIG_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define VIG_API __attribute__((visibility("default")))
+#else
+#define VIG_API
+#endif
+
+#define VIG_DTYPE_F32 0
+#define VIG_DTYPE_BF16 1
+#define VIG_DTYPE_F16 2
+
+#define VIG_OK 0
+#define VIG_ERR_NULL (-1)       /* a required pointer is NULL */
+#define VIG_ERR_SHAPE (-2)      /* unsupported size (dk, dv, C, N, ...) */
+#define VIG_ERR_DTYPE (-3)      /* unknown dtype code */
+#define VIG_ERR_ALIGN (-4)      /* pointer or stride not aligned as the kernel needs */
+#define VIG_ERR_WORKSPACE (-5)  /* workspace missing or too small */
+#define VIG_ERR_ARG (-6)        /* any other rejected argument */
+#define VIG_ERR_DEVICE (-7)     /* not an sm_100 device / driver entry point missing */
+
+/* Which implementation of the scan runs.  AUTO picks the tcgen05 kernel for bf16/fp16 inputs whose
+ * layout it supports and the SIMT kernel otherwise (fp32 inputs always take the SIMT kernel: the
+ * 5th-generation tensor cores have no fp32 MMA and tf32 would miss the 1e-4 bar). */
+#define VIG_IMPL_AUTO 0
+#define VIG_IMPL_SIMT 1
+#define VIG_IMPL_TC 2
+
+VIG_API int vig_version(void);
+VIG_API const char* vig_strerror(int status);
+
+/*
+ * Bi-directional gated linear attention, forward.
+ *
+ *   S^f_t = diag(exp(gf_t)) S^f_{t-1} + k_t^T v_t      (t = 0 .. L-1,  S^f_{-1} = init_state_fwd or 0)
+ *   S^b_t = diag(exp(gb_t)) S^b_{t+1} + k_t^T v_t      (t = L-1 .. 0,  S^b_{L}  = init_state_bwd or 0)
+ *   o_t   = out_scale * scale * q_t (S^f_t + S^b_t)
+ *
+ * Replaces, in one call and one pass over q/k/v/g:
+ *   - `bid_fused_recurrent_gla` (flash-linear-attention/fla/ops/gla/recurrent_fuse.py:659-685, kernel
+ *     :18-148) -- the eval path of classification/models/vig.py:442 (gk[:B] forward gates, gk[B:]
+ *     backward gates, both indexed by original token position; that wrapper returns (o_f+o_b)/2, i.e.
+ *     out_scale = 0.5);
+ *   - `fused_chunk_gla` on batch-doubled, sequence-flipped inputs followed by (o_f + flip(o_b))/2
+ *     (fla/ops/gla/chunk_fuse.py:554-572 and vig.py:407-426), with the flips done by indexing;
+ *   - with dir_mask = 1 or 2, the one-direction `fused_chunk_gla` / `fused_recurrent_gla`
+ *     (chunk_fuse.py:554-572, recurrent_fuse.py:631-657) including initial_state / final_state.
+ *
+ * q, k, g_fwd, g_bwd: [B,H,L,dk]; v, o: [B,H,L,dv]; the last dimension is contiguous and the element
+ * strides of (b, h, l) are given per tensor in strides_*[3] (NULL = contiguous [B,H,L,d]), so views of
+ * a packed [B,L,(h d)] projection need no copy.  scale < 0 means dk^-0.5 (the reference's scale=-1).
+ * gate_logit_normalizer > 0: g_* hold RAW gate logits and the kernel applies
+ * logsigmoid(x) / gate_logit_normalizer (vig.py:439); = 0: g_* are log-space gates (<= 0).
+ * clamp_min: lower clamp of the log-gates (vig.py:440-441); pass a NaN to disable.
+ * init_state_*: fp32 [B,H,dk,dv] or NULL.  final_state_*: fp32 [B,H,dk,dv] out or NULL (state after the
+ * last token in scan order).  total_logdecay_*: fp32 [B,H,dk] out or NULL (sum of the log-gates over L;
+ * with the final state of a zero-initialised scan it is what a sequence split across GPUs exchanges).
+ * o may be NULL when only states are wanted.  dir_mask: 1 forward, 2 backward, 3 both.
+ * status_dev: optional device int32; kernels OR error bits into it (bit 0: a bounded wait ran out,
+ * bit 1: a chunk's cumulative log-gate left the range the tensor-core factorisation covers) -- never a trap.
+ * Supported: dk in {16,32,64,128}, dv in {32,64,128} (SIMT); dk in {32,64}, dv = 64, bf16/fp16 (tensor core).
+ */
+VIG_API size_t vig_bigla_workspace_bytes(int B, int H, int L, int dk, int dv, int dtype, int impl);
+
+VIG_API int vig_bigla_fwd(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, void* o,
+                  int B, int H, int L, int dk, int dv, int dtype,
+                  const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
+                  const int64_t* strides_gf, const int64_t* strides_gb, const int64_t* strides_o,
+                  float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
+                  const float* init_state_fwd, const float* init_state_bwd,
+                  float* final_state_fwd, float* final_state_bwd,
+                  float* total_logdecay_fwd, float* total_logdecay_bwd,
+                  int dir_mask, int impl,
+                  void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/*
+ * Depthwise 3x3 convolution (zero padding 1) over tokens laid out [B, L = h*w, C] with C contiguous,
+ * optional bias, optional SiLU.  Replaces `in_proj` = nn.Conv2d(C, C, 3, padding=1, groups=C) [+ SiLU]
+ * and the two NCHW<->NLC copies around it (classification/models/vig.py:291-294, 428-430).
+ * weight_tap_major: [9][C] (tap = 3*ky + kx), i.e. the reference's [C,1,3,3] parameter transposed;
+ * same dtype as x.  C must be a multiple of 16 bytes / element size.
+ */
+VIG_API int vig_dwconv3x3_fwd(const void* x, const void* weight_tap_major, const void* bias, void* y,
+                      int B, int h, int w, int C, int act_silu, int dtype, void* stream);
+
+/*
+ * 2-D gating locality injection: y = RMSNorm_g(o) * sigmoid(gate_logits) + RMSNorm_l(local) * (1 - sigmoid),
+ * head-wise norms over dv, optional swish on y.  Replaces l_norm, g_norm, sigmoid, the blend, out_act and
+ * the `b h l d -> b l h d` transposes of classification/models/vig.py:444-457 (norm:
+ * fla/modules/rmsnorm.py:491-512).  o: [B,H,L,dv] addressed by strides_o[3] (elements; NULL = contiguous
+ * [B,H,L,dv]); local, gate_logits, y: [B*L, H*dv] row-major with row strides ld_local, ld_gate, ld_y in
+ * elements (H*dv for a contiguous tensor; larger when the operand is a column slice of a wider projection).
+ */
+VIG_API int vig_gate_inject_fwd(const void* o, const int64_t* strides_o, const void* local, const void* gate_logits,
+                        const void* w_gnorm, const void* w_lnorm, void* y,
+                        int64_t ld_local, int64_t ld_gate, int64_t ld_y,
+                        int B, int H, int L, int dv, float eps, int out_act_swish, int dtype, void* stream);
+
+/*
+ * Optional residual add, then RMSNorm: s = x (+ residual); y = s * rsqrt(mean(s^2) + eps) * w;
+ * residual_out (optional) receives s.  Replaces RMSNorm.forward(x, residual, prenorm)
+ * (fla/modules/rmsnorm.py:491-512; reference semantics rms_norm_ref :38-52).  x, residual, y,
+ * residual_out: [rows, N] contiguous; N * element size must be a multiple of 16 and N <= 8192.
+ */
+VIG_API int vig_add_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* residual_out,
+                        int64_t rows, int N, float eps, int dtype, void* stream);
+
+/*
+ * SwiGLU: out = gate * sigmoid(gate) * y (fla/modules/activations.py:109-113, the `swiglu` half of
+ * `swiglu_linear`).  gate, y: [rows, I] with row stride ld_in elements (gate and y are the two halves of
+ * one [rows, 2I] projection in the reference, vig.py:494-497); out: [rows, I] with row stride ld_out.
+ */
+VIG_API int vig_swiglu_fwd(const void* gate, const void* y, void* out, int64_t rows, int I,
+                   int64_t ld_in, int64_t ld_out, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VIG_B200_H */

@@ -1,0 +1,152 @@
+"""Parity of the CUDA bi-GLA operator (through the C ABI) with the CPU oracle and the reference's vectors.
+
+Tolerances: fp32 <= 1e-4, bf16/fp16 <= 2e-2, both as max|a-b| / max|b| against the fp32 reference.
+"""
+import pytest
+import torch
+
+import oracle
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+IMPLS = {"simt": 1, "auto": 0}
+
+
+def _cuda(ts, dtype):
+    return [t.to("cuda", dtype) for t in ts]
+
+
+def _run(q, k, v, gf, gb, dtype, impl=0, **kw):
+    import vig_b200
+    qd, kd, vd, gfd, gbd = _cuda((q, k, v, gf, gb), dtype)
+    out = vig_b200.bi_gla(qd, kd, vd, gfd, gbd, impl=impl, **kw)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("name", ["cfg1", "dk32", "L1", "L17", "L300"])
+@pytest.mark.parametrize("impl", ["simt", "auto"])
+def test_fp32_matches_reference_vectors(golden_bigla, name, impl):
+    B, H, L, dk, dv, seed = (int(x) for x in golden_bigla[f"bigla_{name}_shape"])
+    ins = oracle.make_bigla_inputs(B, H, L, dk, dv, seed)
+    o = _run(*ins, torch.float32, IMPLS[impl])
+    assert rel_err(o, golden_bigla[f"bigla_{name}_o"]) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("impl", ["simt", "auto"])
+@pytest.mark.parametrize("name", ["cfg1", "dk32", "L300"])
+def test_half_precision_matches_fp32_reference(golden_bigla, name, dtype, impl):
+    B, H, L, dk, dv, seed = (int(x) for x in golden_bigla[f"bigla_{name}_shape"])
+    ins = oracle.make_bigla_inputs(B, H, L, dk, dv, seed)
+    o = _run(*ins, dtype, IMPLS[impl])
+    assert rel_err(o.float(), golden_bigla[f"bigla_{name}_o"]) < 2e-2
+
+
+@pytest.mark.parametrize("L", [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 196, 208, 257, 513])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ragged_lengths(L, dtype):
+    ins = oracle.make_bigla_inputs(2, 3, L, 64, 64, seed=L)
+    ref = oracle.naive_bi_gla(*[t.to(dtype).float() for t in ins])
+    o = _run(*ins, dtype)
+    assert rel_err(o.float(), ref) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dk,dv", [(16, 32), (32, 64), (64, 64), (128, 128), (64, 128), (128, 64)])
+def test_head_dims_simt(dk, dv):
+    ins = oracle.make_bigla_inputs(1, 2, 150, dk, dv, seed=dk + dv)
+    ref = oracle.naive_bi_gla(*ins)
+    assert rel_err(_run(*ins, torch.float32, 1), ref) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_strided_views_of_packed_projections(dtype):
+    """q/k/v and the gates as [B,H,L,d] views of [B,L,(h d)] projections, output written as [B,L,H,dv]."""
+    import vig_b200
+    B, H, L, dk, dv = 2, 3, 196, 32, 64
+    gen = torch.Generator().manual_seed(5)
+    z = torch.randn(B, L, 2 * H * dk + H * dv, generator=gen).to(dtype)
+    graw = torch.randn(B, L, 2 * H * dk, generator=gen).to(dtype)
+    heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)
+    split = lambda zz, gg: (heads(zz[..., :H * dk], dk), heads(zz[..., H * dk:2 * H * dk], dk), heads(zz[..., 2 * H * dk:], dv),
+                            heads(gg[..., :H * dk], dk), heads(gg[..., H * dk:], dk))
+    q, k, v, gf, gb = split(z.float(), graw.float())
+    lf = lambda t: torch.nn.functional.logsigmoid(t) / 16
+    ref = oracle.naive_bi_gla(q, k, v, lf(gf), lf(gb), out_scale=0.25)
+    zc, gc = z.cuda(), graw.cuda()
+    qd, kd, vd, gfd, gbd = split(zc, gc)
+    o = torch.empty(B, L, H, dv, dtype=dtype, device="cuda").permute(0, 2, 1, 3)
+    vig_b200.bi_gla(qd, kd, vd, gfd, gbd, out_scale=0.25, out=o, gate_logit_normalizer=16.0)
+    assert rel_err(o.float(), ref) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_direction_with_states(golden_bigla, dtype):
+    import vig_b200
+    q, k, v, g, _ = oracle.make_bigla_inputs(1, 2, 64, 64, 64, 5)
+    h0 = torch.randn(1, 2, 64, 64, generator=torch.Generator().manual_seed(6))
+    o, hT = vig_b200.fused_chunk_gla(*_cuda((q, k, v, g), dtype), initial_state=h0.cuda(), output_final_state=True)
+    tol = TOL[dtype]
+    assert rel_err(o.float(), golden_bigla["gla_state_o"]) < tol
+    assert rel_err(hT, golden_bigla["gla_state_hT"]) < tol
+    # reverse scan == forward scan of the flipped sequence
+    o_r, h_r = vig_b200.fused_recurrent_gla(*_cuda((q, k, v, g), dtype), None, reverse=True, output_final_state=True)
+    ref_o, ref_h = oracle.naive_gla(*[t.to(dtype).float() for t in (q, k, v, g)], reverse=True)
+    assert rel_err(o_r.float(), ref_o) < tol and rel_err(h_r, ref_h) < tol
+
+
+def test_reference_entry_point_bid_fused_recurrent(golden_bigla):
+    import vig_b200
+    B, H, L, dk, dv, seed = (int(x) for x in golden_bigla["bigla_cfg1_shape"])
+    q, k, v, gf, gb = _cuda(oracle.make_bigla_inputs(B, H, L, dk, dv, seed), torch.float32)
+    o, state = vig_b200.bid_fused_recurrent_gla(q, k, v, torch.cat([gf, gb], 0), None)
+    assert state is None
+    assert rel_err(o, golden_bigla["bigla_cfg1_o"] / 2) < 1e-4
+
+
+def test_states_for_sequence_split():
+    """Final states + total log-decay of two halves chain to the full-sequence result."""
+    import vig_b200
+    B, H, L, dk, dv = 1, 2, 256, 64, 64
+    ins = oracle.make_bigla_inputs(B, H, L, dk, dv, seed=9)
+    ref = oracle.naive_bi_gla(*ins)
+    q, k, v, gf, gb = _cuda(ins, torch.float32)
+    half = L // 2
+    lo = [t[:, :, :half] for t in (q, k, v, gf, gb)]
+    hi = [t[:, :, half:] for t in (q, k, v, gf, gb)]
+    _, ex_lo = vig_b200.bi_gla(*lo, output_final_state=True, output_logdecay=True, want_output=False)
+    _, ex_hi = vig_b200.bi_gla(*hi, output_final_state=True, output_logdecay=True, want_output=False)
+    o_lo = vig_b200.bi_gla(*lo, init_state_bwd=ex_hi["final_bwd"])
+    o_hi = vig_b200.bi_gla(*hi, init_state_fwd=ex_lo["final_fwd"])
+    assert rel_err(torch.cat([o_lo, o_hi], 2), ref) < 1e-4
+    assert rel_err(ex_lo["logdecay_fwd"], ins[3][:, :, :half].sum(2)) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_properties_at_full_size(dtype):
+    """Sizes the CPU oracle cannot finish quickly (the L=4096 benchmark shape): flip symmetry and linearity in v."""
+    import vig_b200
+    B, H, L, dk, dv = 4, 3, 4096, 64, 64
+    q, k, v, gf, gb = _cuda(oracle.make_bigla_inputs(B, H, L, dk, dv, seed=1), dtype)
+    o = vig_b200.bi_gla(q, k, v, gf, gb)
+    flip = lambda t: t.flip(2).contiguous()
+    o_flip = vig_b200.bi_gla(flip(q), flip(k), flip(v), flip(gb), flip(gf))      # reversing time swaps the two scans
+    tol = TOL[dtype]
+    assert rel_err(o_flip.flip(2).float(), o.float()) < tol
+    o2 = vig_b200.bi_gla(q, k, (2 * v).contiguous(), gf, gb)
+    assert rel_err(o2.float(), 2 * o.float()) < tol
+    # first 300 tokens of batch 0 with the backward scan off depend only on those tokens: check them against the oracle
+    o_f = vig_b200.bi_gla(q, k, v, gf, None, dir_mask=1)
+    ref, _ = oracle.naive_gla(*[t[:1, :, :300].float().cpu() for t in (q, k, v, gf)])
+    assert rel_err(o_f[:1, :, :300].float(), ref) < tol
+
+
+def test_empty_batch_and_errors():
+    import vig_b200
+    z = torch.zeros(0, 3, 16, 64, device="cuda")
+    assert vig_b200.bi_gla(z, z, z, z, z).shape == (0, 3, 16, 64)
+    bad = torch.zeros(1, 1, 8, 48, device="cuda")
+    with pytest.raises(RuntimeError):
+        vig_b200.bi_gla(bad, bad, bad, bad, bad)

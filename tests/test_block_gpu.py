@@ -1,0 +1,106 @@
+"""Parity of the block's bandwidth kernels, the block and the model (CUDA, through the C ABI) with the oracle."""
+import pytest
+import torch
+
+import oracle
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.fixture(autouse=True)
+def _no_tf32():
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,rows", [(192, 392), (384, 77), (768, 33), (64, 1000), (1024, 5)])
+def test_add_rmsnorm(dtype, N, rows):
+    import vig_b200
+    g = torch.Generator().manual_seed(N)
+    x, r, w = torch.randn(rows, N, generator=g).to(dtype), torch.randn(rows, N, generator=g).to(dtype), (1 + 0.1 * torch.randn(N, generator=g)).to(dtype)
+    y_ref = oracle.rms_norm(x.float(), w.float())
+    assert rel_err(vig_b200.add_rmsnorm(x.cuda(), w.cuda()).float(), y_ref) < TOL[dtype]
+    s_ref = (x.float() + r.float()).to(dtype).float()
+    y2_ref = oracle.rms_norm(s_ref, w.float())
+    y2, s = vig_b200.add_rmsnorm(x.cuda(), w.cuda(), residual=r.cuda(), prenorm=True)
+    assert rel_err(y2.float(), y2_ref) < TOL[dtype]
+    assert torch.equal(s.cpu(), s_ref.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hw,C,act,bias", [((14, 14), 192, True, False), ((7, 9), 384, False, True), ((1, 1), 64, True, True), ((20, 20), 768, False, False)])
+def test_dwconv3x3(dtype, hw, C, act, bias):
+    import vig_b200
+    g = torch.Generator().manual_seed(C)
+    x = torch.randn(2, hw[0] * hw[1], C, generator=g).to(dtype)
+    w = (0.3 * torch.randn(C, 1, 3, 3, generator=g)).to(dtype)
+    b = torch.randn(C, generator=g).to(dtype) if bias else None
+    ref = oracle.dwconv3x3_nlc(x.float(), w.float(), b.float() if bias else None, hw, act)
+    y = vig_b200.dwconv3x3(x.cuda(), w.reshape(C, 9).t().contiguous().cuda(), b.cuda() if bias else None, hw, act)
+    assert rel_err(y.float(), ref) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("out_act", [False, True])
+def test_gate_inject(dtype, out_act):
+    import vig_b200
+    B, H, L, dv = 2, 3, 50, 64
+    g = torch.Generator().manual_seed(3)
+    o = torch.randn(B, H, L, dv, generator=g).to(dtype)
+    wide = torch.randn(B, L, 3 * H * dv, generator=g).to(dtype)        # local / gate logits as column slices
+    wg, wl = (1 + 0.1 * torch.randn(dv, generator=g)).to(dtype), (1 + 0.1 * torch.randn(dv, generator=g)).to(dtype)
+    loc, gl = wide[..., :H * dv], wide[..., 2 * H * dv:]
+    ref = oracle.gate_inject(o.float(), loc.float(), gl.float(), wg.float(), wl.float(), 1e-6, out_act)
+    wc = wide.cuda()
+    y = vig_b200.gate_inject(o.cuda(), wc[..., :H * dv], wc[..., 2 * H * dv:], wg.cuda(), wl.cuda(), 1e-6, out_act)
+    assert rel_err(y.float(), ref) < TOL[dtype]
+    # scan output stored token-major ([B,L,H,dv]) and passed as a permuted view
+    o_tm = o.permute(0, 2, 1, 3).contiguous().cuda().permute(0, 2, 1, 3)
+    y2 = vig_b200.gate_inject(o_tm, wc[..., :H * dv], wc[..., 2 * H * dv:], wg.cuda(), wl.cuda(), 1e-6, out_act)
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    import vig_b200
+    g = torch.Generator().manual_seed(4)
+    gy = (2 * torch.randn(3, 37, 1024, generator=g)).to(dtype)
+    gate, y = gy.chunk(2, -1)
+    ref = oracle.swiglu(gate.float(), y.float())
+    gc = gy.cuda()
+    out = vig_b200.swiglu(*gc.chunk(2, -1))
+    assert rel_err(out.float(), ref) < TOL[dtype]
+
+
+def _shape(preset):
+    base = oracle.PRESETS[preset]
+    return oracle.ViGShape(**{**base.__dict__, "depth": 2, "num_classes": 16})
+
+
+MODEL_CASES = [("t224", "vig_t", 224, 2), ("t320", "vig_t", 320, 1), ("s224", "vig_s", 224, 1), ("tdk64", "vig_t_dk64", 224, 1)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tag,preset,size,batch", MODEL_CASES)
+def test_block_and_model_match_reference_vectors(golden_block, tag, preset, size, batch, dtype):
+    import vig_b200
+    shape = _shape(preset)
+    sd = oracle.make_state_dict(shape, seed=11)
+    model = vig_b200.ViG.from_shape(shape)
+    model.load_state_dict(sd, strict=True)
+    model = model.to("cuda", dtype).eval()
+    g = size // 16
+    x = torch.randn(batch, g * g, shape.embed_dim, generator=torch.Generator().manual_seed(21))
+    with torch.no_grad():
+        blk = model.blocks[0]
+        a = blk.attn(blk.attn_norm(x.to("cuda", dtype)), patch_resolution=(g, g))
+        y = blk(x.to("cuda", dtype), patch_resolution=(g, g))[0]
+        logits = model(oracle.make_images(batch, size, seed=3).to("cuda", dtype))
+    tol = TOL[dtype]
+    assert rel_err(a.float(), golden_block[f"attn_{tag}_y"]) < tol
+    assert rel_err(y.float(), golden_block[f"block_{tag}_y"]) < tol
+    assert rel_err(logits.float(), golden_block[f"vig_{tag}_logits"]) < (2e-4 if dtype == torch.float32 else 3e-2)

@@ -1,0 +1,286 @@
+// Bandwidth-bound kernels of the ViG block: depthwise 3x3 conv in token-major layout, the 2-D gating
+// locality injection, residual-add + RMSNorm, SwiGLU.  Every global access is a 16-byte vector;
+// arithmetic and statistics are fp32.
+#include "common.cuh"
+
+namespace vig {
+namespace {
+
+constexpr int EW_THREADS = 256;
+
+// ---------------------------------------------------------------------------------------------------
+// Depthwise 3x3 conv, x: [B, h*w, C] (C contiguous).  One thread per (token, 16-byte channel group).
+// The nine taps of a token sit in rows y-1..y+1 of the image: 3 runs of 3 neighbouring tokens, so the
+// re-reads hit L1/L2 and DRAM traffic stays at one read + one write of the tensor.
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) dwconv3x3_kernel(const T* __restrict__ x, const T* __restrict__ wt,
+                                                               const T* __restrict__ bias, T* __restrict__ y,
+                                                               int B, int h, int w, int C, int act) {
+    constexpr int V = DType<T>::VEC;
+    const int cv = C / V;
+    const int64_t total = (int64_t)B * h * w * cv;
+    for (int64_t it = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (int64_t)gridDim.x * blockDim.x) {
+        const int c0 = (int)(it % cv) * V;
+        const int64_t tok = it / cv;
+        const int xx = (int)(tok % w);
+        const int yy = (int)((tok / w) % h);
+        float acc[V];
+        if (bias) {
+            Vec16<T> bv; bv.load_nc(bias + c0); bv.to_float(acc);
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        }
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky) {
+            const int y2 = yy + ky - 1;
+            if (y2 < 0 || y2 >= h) continue;
+#pragma unroll
+            for (int kx = 0; kx < 3; ++kx) {
+                const int x2 = xx + kx - 1;
+                if (x2 < 0 || x2 >= w) continue;
+                Vec16<T> xv, wv;
+                xv.load_nc(x + (tok + (int64_t)(ky - 1) * w + (kx - 1)) * C + c0);
+                wv.load_nc(wt + (ky * 3 + kx) * C + c0);
+                float xf[V], wf[V];
+                xv.to_float(xf); wv.to_float(wf);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = fmaf(xf[i], wf[i], acc[i]);
+            }
+        }
+        if (act) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = acc[i] * sigmoidf_(acc[i]);
+        }
+        Vec16<T> ov; ov.from_float(acc); ov.store(y + tok * C + c0);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Gating injection.  LPG lanes share one (token, head) group of dv = LPG * VEC values.
+template <typename T, int LPG>
+__global__ void __launch_bounds__(EW_THREADS) gate_inject_kernel(const T* __restrict__ o, int64_t so_b, int64_t so_h, int64_t so_l,
+                                                                 const T* __restrict__ local, const T* __restrict__ gl,
+                                                                 const T* __restrict__ wg, const T* __restrict__ wl,
+                                                                 T* __restrict__ y, int64_t ld_local, int64_t ld_gate, int64_t ld_y,
+                                                                 int B, int H, int L, float eps, int out_act) {
+    constexpr int V = DType<T>::VEC;
+    constexpr int DV = LPG * V;
+    const int64_t groups = (int64_t)B * L * H;
+    const int lane = threadIdx.x % LPG;
+    float wgf[V], wlf[V];
+    { Vec16<T> t; t.load_nc(wg + lane * V); t.to_float(wgf); t.load_nc(wl + lane * V); t.to_float(wlf); }
+    for (int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPG; g < groups;
+         g += (int64_t)gridDim.x * blockDim.x / LPG) {
+        const int hh = (int)(g % H);
+        const int64_t bl = g / H;
+        const int l = (int)(bl % L);
+        const int b = (int)(bl / L);
+        const int64_t col = hh * DV + lane * V;          // column inside the [B*L, H*dv] operands
+        Vec16<T> ov, lv, gv;
+        ov.load_nc(o + b * so_b + hh * so_h + (int64_t)l * so_l + lane * V);
+        lv.load_nc(local + bl * ld_local + col);
+        gv.load_nc(gl + bl * ld_gate + col);
+        float of[V], lf[V], gf[V];
+        ov.to_float(of); lv.to_float(lf); gv.to_float(gf);
+        float so2 = 0.f, sl2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < V; ++i) { so2 = fmaf(of[i], of[i], so2); sl2 = fmaf(lf[i], lf[i], sl2); }
+#pragma unroll
+        for (int m = 1; m < LPG; m <<= 1) {
+            so2 += __shfl_xor_sync(0xffffffffu, so2, m);
+            sl2 += __shfl_xor_sync(0xffffffffu, sl2, m);
+        }
+        const float ro = rsqrtf(so2 * (1.f / DV) + eps), rl = rsqrtf(sl2 * (1.f / DV) + eps);
+        float out[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float gate = sigmoidf_(gf[i]);
+            float val = of[i] * ro * wgf[i] * gate + lf[i] * rl * wlf[i] * (1.f - gate);
+            if (out_act) val = val * sigmoidf_(val);
+            out[i] = val;
+        }
+        Vec16<T> yv; yv.from_float(out); yv.store(y + bl * ld_y + col);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// (x + residual) -> RMSNorm.  One warp per row, the row stays in registers (MAXV vectors per lane).
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(EW_THREADS) add_rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ res,
+                                                                 const T* __restrict__ w, T* __restrict__ y,
+                                                                 T* __restrict__ res_out, int64_t rows, int N, float eps) {
+    constexpr int V = DType<T>::VEC;
+    const int lane = threadIdx.x & 31;
+    const int nv = N / V;
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp0; r < rows; r += nwarps) {
+        float val[MAXV][V];
+        float ss = 0.f;
+#pragma unroll
+        for (int m = 0; m < MAXV; ++m) {
+            const int vi = lane + m * 32;
+            if (vi < nv) {
+                Vec16<T> xv; xv.load_nc(x + r * N + vi * V); xv.to_float(val[m]);
+                if (res) {
+                    Vec16<T> rv; rv.load_nc(res + r * N + vi * V);
+                    float rf[V]; rv.to_float(rf);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[m][i] += rf[i];
+                    // the reference rounds the sum to the tensor dtype before the norm (rms_norm_ref: (x + residual).to(x.dtype))
+                    Vec16<T> sv; sv.from_float(val[m]); sv.to_float(val[m]);
+                    if (res_out) sv.store(res_out + r * N + vi * V);
+                } else if (res_out) {
+                    xv.store(res_out + r * N + vi * V);
+                }
+#pragma unroll
+                for (int i = 0; i < V; ++i) ss = fmaf(val[m][i], val[m][i], ss);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float rstd = rsqrtf(ss / (float)N + eps);
+#pragma unroll
+        for (int m = 0; m < MAXV; ++m) {
+            const int vi = lane + m * 32;
+            if (vi < nv) {
+                Vec16<T> wv; wv.load_nc(w + vi * V);
+                float wf[V]; wv.to_float(wf);
+#pragma unroll
+                for (int i = 0; i < V; ++i) val[m][i] = val[m][i] * rstd * wf[i];
+                Vec16<T> ov; ov.from_float(val[m]); ov.store(y + r * N + vi * V);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ yy,
+                                                            T* __restrict__ out, int64_t rows, int I, int64_t ld_in, int64_t ld_out) {
+    constexpr int V = DType<T>::VEC;
+    const int iv = I / V;
+    const int64_t total = rows * iv;
+    for (int64_t it = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = it / iv;
+        const int c0 = (int)(it % iv) * V;
+        Vec16<T> gv, yv;
+        gv.load_nc(gate + r * ld_in + c0);
+        yv.load_nc(yy + r * ld_in + c0);
+        float gf[V], yf[V];
+        gv.to_float(gf); yv.to_float(yf);
+#pragma unroll
+        for (int i = 0; i < V; ++i) gf[i] = gf[i] * yf[i] / (1.f + __expf(-gf[i]));
+        Vec16<T> ov; ov.from_float(gf); ov.store(out + r * ld_out + c0);
+    }
+}
+
+inline int grid_for(int64_t items, int per_block) {
+    int64_t g = (items + per_block - 1) / per_block;
+    const int64_t cap = 148 * 16;       // 148 SMs x resident CTAs; the kernels are grid-stride
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T>
+int dwconv_t(const void* x, const void* wt, const void* bias, void* y, int B, int h, int w, int C, int act, cudaStream_t s) {
+    constexpr int V = DType<T>::VEC;
+    if (C % V) return VIG_ERR_SHAPE;
+    const int64_t items = (int64_t)B * h * w * (C / V);
+    dwconv3x3_kernel<T><<<grid_for(items, EW_THREADS), EW_THREADS, 0, s>>>((const T*)x, (const T*)wt, (const T*)bias, (T*)y, B, h, w, C, act);
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int gate_inject_t(const void* o, const int64_t* so, const void* local, const void* gl, const void* wg, const void* wl, void* y,
+                  int64_t ld_local, int64_t ld_gate, int64_t ld_y, int B, int H, int L, int dv, float eps, int out_act, cudaStream_t s) {
+    constexpr int V = DType<T>::VEC;
+    const int lpg = dv / V;
+    if (dv % V || (so[0] % V) || (so[1] % V) || (so[2] % V) || (ld_local % V) || (ld_gate % V) || (ld_y % V)) return VIG_ERR_ALIGN;
+    const int64_t threads = (int64_t)B * L * H * lpg;
+    const int grid = grid_for(threads, EW_THREADS);
+#define VIG_GI(LPG) case LPG: gate_inject_kernel<T, LPG><<<grid, EW_THREADS, 0, s>>>((const T*)o, so[0], so[1], so[2], (const T*)local, \
+        (const T*)gl, (const T*)wg, (const T*)wl, (T*)y, ld_local, ld_gate, ld_y, B, H, L, eps, out_act); break;
+    switch (lpg) { VIG_GI(4) VIG_GI(8) VIG_GI(16) VIG_GI(32) default: return VIG_ERR_SHAPE; }
+#undef VIG_GI
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int add_rmsnorm_t(const void* x, const void* res, const void* w, void* y, void* res_out, int64_t rows, int N, float eps, cudaStream_t s) {
+    constexpr int V = DType<T>::VEC;
+    if (N % V) return VIG_ERR_SHAPE;
+    const int nv = N / V;
+    const int grid = grid_for(rows * 32, EW_THREADS);
+#define VIG_RN(MV) add_rmsnorm_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)res, (const T*)w, (T*)y, (T*)res_out, rows, N, eps)
+    if (nv <= 32) VIG_RN(1); else if (nv <= 64) VIG_RN(2); else if (nv <= 128) VIG_RN(4);
+    else if (nv <= 256) VIG_RN(8); else if (nv <= 512 && V == 4) VIG_RN(16); else return VIG_ERR_SHAPE;
+#undef VIG_RN
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int swiglu_t(const void* g, const void* yy, void* out, int64_t rows, int I, int64_t ld_in, int64_t ld_out, cudaStream_t s) {
+    constexpr int V = DType<T>::VEC;
+    if (I % V || ld_in % V || ld_out % V) return VIG_ERR_ALIGN;
+    swiglu_kernel<T><<<grid_for(rows * (I / V), EW_THREADS), EW_THREADS, 0, s>>>((const T*)g, (const T*)yy, (T*)out, rows, I, ld_in, ld_out);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+}  // namespace vig
+
+using namespace vig;
+
+#define VIG_DISPATCH(dtype, CALL)                                   \
+    switch (dtype) {                                                \
+        case VIG_DTYPE_F32: { using T = float; return CALL; }        \
+        case VIG_DTYPE_BF16: { using T = __nv_bfloat16; return CALL; } \
+        case VIG_DTYPE_F16: { using T = __half; return CALL; }       \
+        default: return VIG_ERR_DTYPE;                              \
+    }
+
+extern "C" int vig_dwconv3x3_fwd(const void* x, const void* wt, const void* bias, void* y, int B, int h, int w, int C,
+                                 int act_silu, int dtype, void* stream) {
+    if (!x || !wt || !y) return VIG_ERR_NULL;
+    if (B < 0 || h <= 0 || w <= 0 || C <= 0) return VIG_ERR_SHAPE;
+    if (B == 0) return VIG_OK;
+    if (!aligned16(x) || !aligned16(wt) || !aligned16(y) || (bias && !aligned16(bias))) return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, dwconv_t<T>(x, wt, bias, y, B, h, w, C, act_silu, (cudaStream_t)stream))
+}
+
+extern "C" int vig_gate_inject_fwd(const void* o, const int64_t* strides_o, const void* local, const void* gate_logits,
+                                   const void* w_gnorm, const void* w_lnorm, void* y,
+                                   int64_t ld_local, int64_t ld_gate, int64_t ld_y, int B, int H, int L, int dv,
+                                   float eps, int out_act_swish, int dtype, void* stream) {
+    if (!o || !local || !gate_logits || !w_gnorm || !w_lnorm || !y) return VIG_ERR_NULL;
+    if (B < 0 || H <= 0 || L < 0 || dv <= 0) return VIG_ERR_SHAPE;
+    if (ld_local < (int64_t)H * dv || ld_gate < (int64_t)H * dv || ld_y < (int64_t)H * dv) return VIG_ERR_ARG;
+    if (B == 0 || L == 0) return VIG_OK;
+    if (!aligned16(o) || !aligned16(local) || !aligned16(gate_logits) || !aligned16(y) || !aligned16(w_gnorm) || !aligned16(w_lnorm))
+        return VIG_ERR_ALIGN;
+    int64_t so[3] = {(int64_t)H * L * dv, (int64_t)L * dv, dv};
+    if (strides_o) { so[0] = strides_o[0]; so[1] = strides_o[1]; so[2] = strides_o[2]; }
+    VIG_DISPATCH(dtype, gate_inject_t<T>(o, so, local, gate_logits, w_gnorm, w_lnorm, y, ld_local, ld_gate, ld_y, B, H, L, dv, eps, out_act_swish, (cudaStream_t)stream))
+}
+
+extern "C" int vig_add_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* residual_out,
+                                   int64_t rows, int N, float eps, int dtype, void* stream) {
+    if (!x || !w || !y) return VIG_ERR_NULL;
+    if (rows < 0 || N <= 0) return VIG_ERR_SHAPE;
+    if (rows == 0) return VIG_OK;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (residual && !aligned16(residual)) || (residual_out && !aligned16(residual_out)))
+        return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, add_rmsnorm_t<T>(x, residual, w, y, residual_out, rows, N, eps, (cudaStream_t)stream))
+}
+
+extern "C" int vig_swiglu_fwd(const void* gate, const void* y, void* out, int64_t rows, int I, int64_t ld_in, int64_t ld_out,
+                              int dtype, void* stream) {
+    if (!gate || !y || !out) return VIG_ERR_NULL;
+    if (rows < 0 || I <= 0) return VIG_ERR_SHAPE;
+    if (rows == 0) return VIG_OK;
+    if (!aligned16(gate) || !aligned16(y) || !aligned16(out)) return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, swiglu_t<T>(gate, y, out, rows, I, ld_in, ld_out, (cudaStream_t)stream))
+}

@@ -1,0 +1,200 @@
+"""Operator API with the reference's names and argument conventions, backed by the CUDA library.
+
+``bid_fused_recurrent_gla`` / ``fused_recurrent_gla`` mirror ``fla/ops/gla/recurrent_fuse.py:631-685``,
+``fused_chunk_gla`` mirrors ``fla/ops/gla/chunk_fuse.py:554-572`` and ``chunk_gla``
+``fla/ops/gla/chunk.py:561-580``; ``bi_gla`` is the explicit form of the merged operator.
+Tensors are ``[B, H, L, d]`` views with a contiguous last dimension; no copies are made.
+Forward only (inference): the autograd backward of the reference is not part of this path.
+"""
+import math
+
+import torch
+
+from . import _lib
+
+_NAN = float("nan")
+_ws_cache = {}
+
+
+def _workspace(nbytes, device):
+    """Per-device scratch buffer that only grows (allocated through torch's caching allocator)."""
+    if nbytes == 0:
+        return None
+    if torch.cuda.is_current_stream_capturing():
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    buf = _ws_cache.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(int(nbytes * 1.25) + 256, dtype=torch.uint8, device=device)
+        _ws_cache[device] = buf
+    return buf
+
+
+def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_logit_normalizer=0.0, clamp_min=None,
+           init_state_fwd=None, init_state_bwd=None, output_final_state=False, output_logdecay=False,
+           dir_mask=3, impl=_lib.IMPL_AUTO, want_output=True):
+    """o_t = out_scale * scale * q_t (S^f_t + S^b_t) with separate forward / backward log-gates.
+
+    Returns ``o`` or ``(o, extras)`` where ``extras`` holds ``final_fwd/final_bwd`` ([B,H,dk,dv] fp32) and
+    ``logdecay_fwd/logdecay_bwd`` ([B,H,dk] fp32) when requested.
+    """
+    _lib.require_cuda(q, k, v, g_fwd, g_bwd)
+    B, H, L, dk = k.shape
+    dv = v.shape[-1]
+    code = _lib.dtype_code(k)
+    for t in (q, v, g_fwd, g_bwd):
+        if t is not None and t.dtype != k.dtype:
+            raise TypeError("q, k, v and the gates must share one dtype")
+    dev = k.device
+    if want_output:
+        if out is None:
+            out = torch.empty(B, H, L, dv, dtype=v.dtype, device=dev)
+    else:
+        out = None
+    f32 = dict(dtype=torch.float32, device=dev)
+    extras = {}
+    if output_final_state:
+        if dir_mask & 1:
+            extras["final_fwd"] = torch.empty(B, H, dk, dv, **f32)
+        if dir_mask & 2:
+            extras["final_bwd"] = torch.empty(B, H, dk, dv, **f32)
+    if output_logdecay:
+        if dir_mask & 1:
+            extras["logdecay_fwd"] = torch.empty(B, H, dk, **f32)
+        if dir_mask & 2:
+            extras["logdecay_bwd"] = torch.empty(B, H, dk, **f32)
+    for s in (init_state_fwd, init_state_bwd):
+        if s is not None and (s.dtype != torch.float32 or not s.is_contiguous() or s.shape != (B, H, dk, dv)):
+            raise ValueError("initial states must be contiguous fp32 [B,H,dk,dv]")
+    L_ = _lib.lib()
+    nbytes = L_.vig_bigla_workspace_bytes(B, H, L, dk, dv, code, impl)
+    ws = _workspace(nbytes, dev)
+    st = L_.vig_bigla_fwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(out),
+        B, H, L, dk, dv, code,
+        _lib.strides3(q) if q is not None else None, _lib.strides3(k), _lib.strides3(v),
+        _lib.strides3(g_fwd) if g_fwd is not None else None, _lib.strides3(g_bwd) if g_bwd is not None else None,
+        _lib.strides3(out) if out is not None else None,
+        float(scale if scale is not None else -1), float(out_scale), float(gate_logit_normalizer),
+        _NAN if clamp_min is None else float(clamp_min),
+        _lib.ptr(init_state_fwd), _lib.ptr(init_state_bwd),
+        _lib.ptr(extras.get("final_fwd")), _lib.ptr(extras.get("final_bwd")),
+        _lib.ptr(extras.get("logdecay_fwd")), _lib.ptr(extras.get("logdecay_bwd")),
+        dir_mask, impl, _lib.ptr(ws), ws.numel() if ws is not None else 0, None, _lib.stream_ptr())
+    _lib.check(st, "vig_bigla_fwd")
+    if extras:
+        return out, extras
+    return out
+
+
+def bid_fused_recurrent_gla(q, k, v, gk=None, gv=None, scale=-1, initial_state=None, output_final_state=False,
+                            causal=True):
+    """``fla/ops/gla/recurrent_fuse.py:659-685``: ``gk`` is ``[2B,H,L,dk]`` (forward gates then backward
+    gates, both in original token order); returns ``((o_f + o_b) / 2, None)``."""
+    if gk is None or gv is not None or initial_state is not None or output_final_state:
+        raise NotImplementedError("only the form ViG calls is implemented: gk given, no gv / states")
+    B = q.shape[0]
+    if gk.shape[0] != 2 * B:
+        raise ValueError("gk must stack forward and backward gates along the batch: [2B,H,L,dk]")
+    return bi_gla(q, k, v, gk[:B], gk[B:], scale=scale, out_scale=0.5), None
+
+
+def _one_direction(q, k, v, g, scale, initial_state, output_final_state, reverse):
+    mask = 2 if reverse else 1
+    kw = dict(init_state_bwd=initial_state) if reverse else dict(init_state_fwd=initial_state)
+    if initial_state is not None:
+        kw = {n: s.detach().float().contiguous() for n, s in kw.items()}
+    res = bi_gla(q, k, v, None if reverse else g, g if reverse else None, scale=scale, dir_mask=mask,
+                 output_final_state=output_final_state, **kw)
+    if output_final_state:
+        o, ex = res
+        return o, ex["final_bwd" if reverse else "final_fwd"]
+    return res, None
+
+
+def fused_chunk_gla(q, k, v, g, scale=-1, initial_state=None, output_final_state=False):
+    """``fla/ops/gla/chunk_fuse.py:554-572``: causal scan, ``(o, final_state)``; ``final_state`` fp32 or None."""
+    return _one_direction(q, k, v, g, scale, initial_state, output_final_state, reverse=False)
+
+
+def chunk_gla(q, k, v, g, scale=-1, initial_state=None, output_final_state=False):
+    """``fla/ops/gla/chunk.py:561-580``: same function as ``fused_chunk_gla``."""
+    return _one_direction(q, k, v, g, scale, initial_state, output_final_state, reverse=False)
+
+
+def fused_recurrent_gla(q, k, v, gk=None, gv=None, scale=-1, initial_state=None, output_final_state=False,
+                        causal=True, reverse=False):
+    """``fla/ops/gla/recurrent_fuse.py:631-657`` with key-wise gates only."""
+    if gk is None or gv is not None:
+        raise NotImplementedError("only key-wise gates (gk) are implemented")
+    return _one_direction(q, k, v, gk, scale, initial_state, output_final_state, reverse=reverse)
+
+
+# --------------------------------------------------------------------------------------------------
+def dwconv3x3(x, weight_tap_major, bias, hw, act_silu, out=None):
+    """Depthwise 3x3 (+SiLU) on ``[B, h*w, C]`` tokens; ``weight_tap_major`` is ``[9, C]``."""
+    _lib.require_cuda(x, weight_tap_major)
+    B, L, C = x.shape
+    h, w = hw
+    if h * w != L or not x.is_contiguous():
+        raise ValueError("x must be contiguous [B, h*w, C]")
+    y = torch.empty_like(x) if out is None else out
+    st = _lib.lib().vig_dwconv3x3_fwd(_lib.ptr(x), _lib.ptr(weight_tap_major), _lib.ptr(bias), _lib.ptr(y),
+                                      B, h, w, C, int(bool(act_silu)), _lib.dtype_code(x), _lib.stream_ptr())
+    _lib.check(st, "vig_dwconv3x3_fwd")
+    return y
+
+
+def _rows(t, what):
+    """Row stride of a [B, L, N] tensor whose (b, l) dimensions collapse to one row index."""
+    if t.stride(-1) != 1 or t.stride(0) != t.shape[1] * t.stride(1):
+        raise ValueError(f"{what} must be a row-major [B, L, N] tensor or a column slice of one")
+    return t.stride(1)
+
+
+def gate_inject(o, local, gate_logits, w_gnorm, w_lnorm, eps, out_act, out=None):
+    """``o`` is a ``[B,H,L,dv]`` view (any b/h/l strides); ``local``, ``gate_logits`` are ``[B,L,H*dv]``
+    (column slices of a wider projection are fine)."""
+    _lib.require_cuda(o, local, gate_logits)
+    B, H, L, dv = o.shape
+    y = torch.empty(B, L, H * dv, dtype=local.dtype, device=local.device) if out is None else out
+    st = _lib.lib().vig_gate_inject_fwd(_lib.ptr(o), _lib.strides3(o), _lib.ptr(local), _lib.ptr(gate_logits),
+                                        _lib.ptr(w_gnorm), _lib.ptr(w_lnorm), _lib.ptr(y),
+                                        _rows(local, "local"), _rows(gate_logits, "gate_logits"), _rows(y, "out"),
+                                        B, H, L, dv, float(eps), int(bool(out_act)), _lib.dtype_code(local), _lib.stream_ptr())
+    _lib.check(st, "vig_gate_inject_fwd")
+    return y
+
+
+def add_rmsnorm(x, weight, residual=None, eps=1e-6, prenorm=False):
+    """``RMSNorm.forward`` semantics (``fla/modules/rmsnorm.py:491-512``): returns ``y`` or ``(y, x + residual)``."""
+    _lib.require_cuda(x, weight)
+    N = x.shape[-1]
+    if not x.is_contiguous() or (residual is not None and not residual.is_contiguous()):
+        raise ValueError("x and residual must be contiguous")
+    y = torch.empty_like(x)
+    res_out = torch.empty_like(x) if (prenorm and residual is not None) else None
+    st = _lib.lib().vig_add_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), _lib.ptr(y), _lib.ptr(res_out),
+                                        x.numel() // N, N, float(eps), _lib.dtype_code(x), _lib.stream_ptr())
+    _lib.check(st, "vig_add_rmsnorm_fwd")
+    if prenorm:
+        return y, (res_out if residual is not None else x)
+    return y
+
+
+def swiglu(gate, y):
+    """``fla/modules/activations.py:109-113``: ``gate * sigmoid(gate) * y``; inputs may be the two halves of one projection."""
+    _lib.require_cuda(gate, y)
+    I = gate.shape[-1]
+    g2, y2 = gate.reshape(-1, I) if gate.is_contiguous() else gate.flatten(0, -2), y.reshape(-1, I) if y.is_contiguous() else y.flatten(0, -2)
+    if g2.stride(1) != 1 or y2.stride(1) != 1 or g2.stride(0) != y2.stride(0):
+        raise ValueError("gate and y must be row-major with equal row strides")
+    out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+    st = _lib.lib().vig_swiglu_fwd(_lib.ptr(g2), _lib.ptr(y2), _lib.ptr(out), g2.shape[0], I, g2.stride(0), I,
+                                   _lib.dtype_code(gate), _lib.stream_ptr())
+    _lib.check(st, "vig_swiglu_fwd")
+    return out
+
+
+def swiglu_linear(x, y, weight, bias):
+    """``fla/modules/activations.py:150-174``: ``F.linear(swiglu(x, y), weight, bias)``."""
+    return torch.nn.functional.linear(swiglu(x, y), weight, bias)

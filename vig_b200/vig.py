@@ -1,0 +1,103 @@
+"""ViG model shell around the CUDA-backed block: ``ViG`` of ``classification/models/vig.py:705-912`` in
+the configuration every shipped YAML uses (v2 patch embed, absolute pos-embed, no cls token, average-pool
+head, RMSNorm + SwiGLU blocks).  Parameter names match the reference so its checkpoints load.
+The stem convolutions, LayerNorm2d, bicubic pos-embed resize, pooling and the classifier run as PyTorch
+library calls; everything inside the blocks except the dense GEMMs is this library's kernels.
+"""
+import math
+from types import SimpleNamespace
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .modules import GLABlock, RMSNorm
+
+
+class LayerNorm2d(nn.LayerNorm):
+    def forward(self, x):
+        return F.layer_norm(x.permute(0, 2, 3, 1), self.normalized_shape, self.weight, self.bias, self.eps).permute(0, 3, 1, 2)
+
+
+class V2PatchEmbed(nn.Module):
+    """``vig.py:625-672``: conv k(p/2+1) s(p/2) p1 -> LN2d -> swish -> conv k3 s2 p1 -> LN2d."""
+
+    def __init__(self, img_size=224, patch_size=16, in_chans=3, embed_dim=768, use_bias_in_patch=True):
+        super().__init__()
+        stride = patch_size // 2
+        self.proj = nn.Sequential(
+            nn.Conv2d(in_chans, embed_dim // 2, kernel_size=stride + 1, stride=stride, padding=1, bias=use_bias_in_patch),
+            LayerNorm2d(embed_dim // 2), nn.SiLU(),
+            nn.Conv2d(embed_dim // 2, embed_dim, kernel_size=3, stride=2, padding=1, bias=use_bias_in_patch),
+            LayerNorm2d(embed_dim))
+        self.num_patches = (img_size // patch_size) ** 2
+
+    def forward(self, x):
+        x = self.proj(x)
+        return x.flatten(2).transpose(1, 2).contiguous(), (x.shape[2], x.shape[3])
+
+
+def resize_pos_embed(pos_embed, src_shape, dst_shape, mode="bicubic"):
+    """``vig.py:915-958`` without extra tokens: bicubic in fp32, align_corners=False."""
+    if tuple(src_shape) == tuple(dst_shape):
+        return pos_embed
+    C = pos_embed.shape[-1]
+    w = pos_embed.reshape(1, src_shape[0], src_shape[1], C).permute(0, 3, 1, 2)
+    w = F.interpolate(w.float(), size=tuple(dst_shape), align_corners=False, mode=mode)
+    return torch.flatten(w, 2).transpose(1, 2).to(pos_embed.dtype)
+
+
+class ViG(nn.Module):
+    def __init__(self, img_size=224, patch_size=16, depth=12, num_heads=3, embed_dim=192, channels=3, num_classes=1000,
+                 use_out_act=False, use_act_in_conv=True, expand_k=0.5, expand_v=1, use_bias_in_patch=True,
+                 use_bias_in_dwconv=False, clamp_min=None, rms_norm_eps=1e-6, **unused):
+        super().__init__()
+        self.embed_dim, self.num_classes = embed_dim, num_classes
+        self.config = SimpleNamespace(hidden_size=embed_dim, num_hidden_layers=depth, num_attention_heads=num_heads,
+                                      expand_k=expand_k, expand_v=expand_v, rms_norm_eps=rms_norm_eps, use_out_act=use_out_act,
+                                      use_act_in_conv=use_act_in_conv, use_bias_in_dwconv=use_bias_in_dwconv,
+                                      clamp_min=clamp_min, attn_mode="fused_chunk", intermediate_size=None, hidden_act="swish")
+        self.patch_embed = V2PatchEmbed(img_size, patch_size, channels, embed_dim, use_bias_in_patch)
+        self.patch_resolution = (img_size // patch_size, img_size // patch_size)
+        self.pos_embed = nn.Parameter(torch.zeros(1, self.patch_embed.num_patches, embed_dim))
+        self.head = nn.Linear(embed_dim, num_classes) if num_classes > 0 else nn.Identity()
+        self.blocks = nn.ModuleList([GLABlock(self.config, i) for i in range(depth)])
+        self.norm = RMSNorm(embed_dim, eps=rms_norm_eps)
+        self._pos_cache = {}
+
+    @classmethod
+    def from_shape(cls, shape, **kw):
+        """Build from an object with embed_dim / num_heads / depth / expand_k / ... attributes."""
+        return cls(depth=shape.depth, num_heads=shape.num_heads, embed_dim=shape.embed_dim, num_classes=shape.num_classes,
+                   use_out_act=shape.use_out_act, use_act_in_conv=shape.use_act_in_conv, expand_k=shape.expand_k,
+                   expand_v=shape.expand_v, clamp_min=shape.clamp_min, rms_norm_eps=shape.eps, **kw)
+
+    def _pos(self, hw):
+        key = (tuple(hw), self.pos_embed.dtype, self.pos_embed.device, self.pos_embed._version)
+        if key not in self._pos_cache:
+            self._pos_cache = {key: resize_pos_embed(self.pos_embed.detach(), self.patch_resolution, hw)}
+        return self._pos_cache[key]
+
+    def forward_features(self, x):
+        x, hw = self.patch_embed(x)
+        x = x + self._pos(hw)
+        h, residual = x, None
+        for blk in self.blocks:
+            h, residual = blk.forward_deferred(h, residual, patch_resolution=hw)
+        x = self.norm(h, residual)                      # last residual add fused into the final norm
+        return x.mean(dim=1)
+
+    def forward(self, x, **kwargs):
+        return self.head(self.forward_features(x))
+
+
+_PRESETS = {
+    "vig_t": dict(embed_dim=192, num_heads=3, use_out_act=True, use_act_in_conv=True),
+    "vig_s": dict(embed_dim=384, num_heads=6, use_out_act=False, use_act_in_conv=False),
+    "vig_b": dict(embed_dim=768, num_heads=12, use_out_act=False, use_act_in_conv=False),
+}
+
+
+def build_vig(name="vig_t", expand_k=0.5, **kw):
+    """ViG-T / S / B of ``classification/configs/vig/vig-{t,s,b}.yaml`` (depth 12, expand_v 1)."""
+    return ViG(depth=12, expand_k=expand_k, expand_v=1, **{**_PRESETS[name], **kw})
