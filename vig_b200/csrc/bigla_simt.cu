@@ -218,6 +218,12 @@ size_t bigla_simt_workspace(int B, int H, int L, int dk, int dv) {
     return (size_t)B * H * nchunk * 2 * ((size_t)dk * dv + dk) * sizeof(float);
 }
 
+int bigla_scan_launch(const BiglaParams& p, cudaStream_t stream) {
+    const int per = (p.dk * p.dv + NT - 1) / NT;
+    bigla_simt_state_scan<<<p.B * p.H * 2 * per, NT, 0, stream>>>(p);
+    return (int)cudaGetLastError();
+}
+
 int bigla_simt_launch(const BiglaParams& p_in, cudaStream_t stream) {
     BiglaParams p = p_in;
     p.nchunk = (p.L + CH - 1) / CH;

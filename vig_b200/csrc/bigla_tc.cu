@@ -1,7 +1,558 @@
-// placeholder until the tcgen05 kernel lands
+// Bi-directional gated linear attention on the 5th-generation tensor cores (tcgen05 + TMEM), bf16 / fp16.
+//
+// One CTA owns one (segment, batch*head): up to SEG_CHUNKS chunks of 128 tokens.  It sweeps its chunks
+// twice -- left to right with the forward gates, right to left with the backward gates -- and keeps the
+// output accumulators of all its chunks in tensor memory between the sweeps, so q/k/v and both gate
+// tensors are fetched by TMA once per sweep and the output is written once.  Per chunk and direction:
+//
+//   G_i      inclusive cumulative log-gate inside the chunk (prefix for forward, suffix for backward), fp32
+//   Qt, Kt   q * scale * exp(G_i - G_ref),  k * exp(G_ref - G_j)     (G_ref = G at the chunk's middle)
+//   P        = mask(Qt Kt^T)            128x128x dk   MMA, accumulator in TMEM, masked to j<=i (j>=i)
+//   O_chunk += bf16(P) V                128x 64x128   MMA
+//   O_chunk += Qt (exp(G_ref) * S_in)   128x 64x dk   MMA   (S_in = state entering the chunk)
+//   U        = Kt^T V                    64x 64x128   MMA   (both operands MN-major views of the tiles)
+//   S_out    = exp(G_last) * S_in + exp(G_last - G_ref) * U          (fp32, in registers)
+//
+// Sequences longer than one segment use the same kernel three times over: STATES_ONLY per segment from a
+// zero state, the scan over segments (SIMT, tiny), then the full pass with each segment's entering states.
+//
+// Every wait on an mbarrier is bounded: when it runs out the CTA sets bit 0 of the status word, stops
+// waiting on anything else, finishes its control flow and frees its tensor memory.
+#include <cuda.h>
+#include <mutex>
 #include "common.cuh"
+
 namespace vig {
-bool bigla_tc_supported(const BiglaParams&) { return false; }
-size_t bigla_tc_workspace(int, int, int, int, int) { return 0; }
-int bigla_tc_launch(const BiglaParams&, void*, size_t, cudaStream_t) { return VIG_ERR_SHAPE; }
+namespace {
+
+constexpr int CHUNK = 128;            // tokens per chunk = rows of one MMA tile
+constexpr int SEG_CHUNKS = 4;         // chunks per CTA: 4 x 64 TMEM columns of output accumulators
+constexpr int SEG = CHUNK * SEG_CHUNKS;
+constexpr int NTHREADS = 256;
+constexpr int DV = 64;
+constexpr float MAX_EXPONENT = 80.f;  // exp() arguments of the factorisation are clamped to +-80
+
+// TMEM columns (fp32): scores, state update, output accumulators
+constexpr uint32_t TM_P = 0, TM_U = 128, TM_O = 192, TM_COLS = 512;
+
+// shared memory map (bytes from a 1024-aligned base)
+constexpr int TILE_B = CHUNK * 64 * 2;                       // 16 KB: 128 rows x 128 B
+constexpr int OFF_STAGE = 0;                                 // 2 stages x {q, k, g, v}
+constexpr int STAGE_B = 4 * TILE_B;
+constexpr int OFF_QT = OFF_STAGE + 2 * STAGE_B;
+constexpr int OFF_KT = OFF_QT + TILE_B;
+constexpr int OFF_P = OFF_KT + TILE_B;                       // 2 blocks of 64 key columns
+constexpr int OFF_ST = OFF_P + 2 * TILE_B;                   // bf16 state operand, 64 rows x 128 B
+constexpr int OFF_PART = OFF_ST + 64 * 128;                  // fp32 [16][64] group sums of log-gates
+constexpr int OFF_VEC = OFF_PART + 16 * 64 * 4;              // fp32 [2][64]: exp(G_last), exp(G_last - G_ref)
+constexpr int OFF_GTOT = OFF_VEC + 2 * 64 * 4;               // fp32 [64] summed log-gates of the segment
+constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: full[2], p, u, o
+constexpr int OFF_MISC = OFF_BAR + 8 * 8;                    // tmem base, abort flag
+constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;             // + slack for the manual 1024-byte alignment
+
+// ---------------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base lane + i)
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (both for K-major
+// tiles with 128-byte rows along K and for MN-major tiles with 128-byte rows along M/N).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);           // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for one 128-byte atom column)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: fp32 accumulate, A/B format (0 fp16, 1 bf16), major-ness (0 K, 1 MN), N, M.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t a_mn, uint32_t b_mn, uint32_t M, uint32_t N) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// Byte offset of bf16 element (row, col) in a K-major / MN-major tile with 128-byte rows and 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t col_bytes) {
+    return row * 128 + ((((col_bytes >> 4) ^ (row & 7)) << 4) | (col_bytes & 15));
+}
+
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+    static constexpr uint32_t FMT = 1;
+    __device__ static uint32_t pack(float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
+    __device__ static float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+};
+template <> struct Pack2<__half> {
+    static constexpr uint32_t FMT = 0;
+    __device__ static uint32_t pack(float a, float b) { __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
+    __device__ static float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+};
+
+struct Waiter {
+    volatile int* abort_flag;
+    int32_t* status;
+    // Bounded wait: ~0.3 s at most, then flag the CTA as aborted so that no later wait spins.
+    __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            if (mbar_try_wait(bar, parity)) return;
+            if (i > 128) {
+                if (*abort_flag) return;
+                __nanosleep(64);
+            }
+        }
+        *abort_flag = 1;
+        if (status) atomicOr(status, 1);
+    }
+};
+
+struct TcMaps { CUtensorMap q, k, v, gf, gb; };
+
+// ---------------------------------------------------------------------------------------------------
+template <int DK, typename T, bool STATES_ONLY>
+__global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_constant__ TcMaps maps, BiglaParams p, int use_ws) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+    const int seg_t0 = seg * SEG;
+    const int nch = min(SEG_CHUNKS, (p.L - seg_t0 + CHUNK - 1) / CHUNK);
+    const int nseg = gridDim.x;
+
+    const uint32_t bar_full0 = sbase + OFF_BAR, bar_p = sbase + OFF_BAR + 16, bar_u = sbase + OFF_BAR + 24, bar_o = sbase + OFF_BAR + 32;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+    float* part = reinterpret_cast<float*>(smem + OFF_PART);
+    float* vec = reinterpret_cast<float*>(smem + OFF_VEC);
+    float* gtot = reinterpret_cast<float*>(smem + OFF_GTOT);
+    const Waiter waiter{abort_flag, p.status};
+
+    if (tid == 0) {
+        mbar_init(bar_full0, 1); mbar_init(bar_full0 + 8, 1);
+        mbar_init(bar_p, 1); mbar_init(bar_u, 1); mbar_init(bar_o, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // ---- thread roles ---------------------------------------------------------------------------
+    // gate preparation: CPW lanes cover the channel pairs of one token row; a warp covers 32/CPW rows at once
+    constexpr int CPW = DK / 2;
+    constexpr int RPW = 32 / CPW;                 // token groups per warp
+    constexpr int NG = 8 * RPW;                   // token groups per chunk
+    constexpr int TPG = CHUNK / NG;               // tokens per group (16 for dk=64, 8 for dk=32)
+    const int cp = lane % CPW;
+    const int grp = warp * RPW + lane / CPW;
+    // state rows: an M=64 accumulator puts row r in TMEM lane (r % 16) + 32 * (r / 16)
+    const bool st_thread = lane < 16 && (16 * (warp & 3) + lane) < DK;
+    const int st_row = 16 * (warp & 3) + lane;    // key channel
+    const int st_col0 = 32 * (warp >> 2);         // first of 32 value columns
+    const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
+
+    constexpr uint32_t IDESC_QK = make_idesc(Pack2<T>::FMT, 0, 0, 128, 128);
+    constexpr uint32_t IDESC_OV = make_idesc(Pack2<T>::FMT, 0, 1, 128, 64);
+    constexpr uint32_t IDESC_U = make_idesc(Pack2<T>::FMT, 1, 1, 64, 64);
+    constexpr uint32_t TX_BYTES = (STATES_ONLY ? 2 : 3) * CHUNK * DK * 2 + CHUNK * DV * 2;
+
+    const int dir_first = (p.dir_mask & 1) ? 0 : 1, dir_last = (p.dir_mask & 2) ? 1 : 0;
+    const int n_iter = (dir_last - dir_first + 1) * nch;      // iterations: sweeps x chunks, stage = n & 1
+
+    auto issue_loads = [&](int n) {         // thread 0 only: tiles of iteration n into stage n & 1
+        const int dir = dir_first + n / nch, ci = n % nch;
+        const int c = dir ? nch - 1 - ci : ci;
+        const int t0 = seg_t0 + c * CHUNK;
+        const uint32_t st = sbase + OFF_STAGE + (n & 1) * STAGE_B, bar = bar_full0 + 8 * (n & 1);
+        mbar_expect_tx(bar, TX_BYTES);
+        if (!STATES_ONLY) tma_load_4d(st, &maps.q, 0, t0, h, b, bar);
+        tma_load_4d(st + TILE_B, &maps.k, 0, t0, h, b, bar);
+        tma_load_4d(st + 2 * TILE_B, dir ? &maps.gb : &maps.gf, 0, t0, h, b, bar);
+        tma_load_4d(st + 3 * TILE_B, &maps.v, 0, t0, h, b, bar);
+    };
+
+    if (tid == 0) issue_loads(0);
+
+    float S[32];                                  // my 32 columns of state row st_row (state threads only)
+
+    for (int n = 0; n < n_iter; ++n) {
+        const int dir = dir_first + n / nch, ci = n % nch;
+        const int c = dir ? nch - 1 - ci : ci;
+        const int t0 = seg_t0 + c * CHUNK;
+        const uint8_t* stg = smem + OFF_STAGE + (n & 1) * STAGE_B;
+        const uint32_t* sq = reinterpret_cast<const uint32_t*>(stg);
+        const uint32_t* sk = reinterpret_cast<const uint32_t*>(stg + TILE_B);
+        const uint32_t* sg = reinterpret_cast<const uint32_t*>(stg + 2 * TILE_B);
+        const uint32_t v_addr = sbase + OFF_STAGE + (n & 1) * STAGE_B + 3 * TILE_B;
+        const uint32_t par = (uint32_t)(n & 1);
+
+        if (ci == 0) {                            // a sweep starts: entering state of the segment, zeroed gate total
+            if (st_thread) {
+                const float* src = nullptr;
+                if (!STATES_ONLY) {
+                    if (use_ws) src = p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV;
+                    else if (dir ? p.init_b : p.init_f) src = (dir ? p.init_b : p.init_f) + (size_t)bh * DK * DV;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) S[j] = src ? src[st_row * DV + st_col0 + j] : 0.f;
+            }
+            if (tid < DK) gtot[tid] = 0.f;
+        }
+        if (tid == 0 && n + 1 < n_iter) issue_loads(n + 1);       // the other stage was released at the end of n-1
+        __syncwarp();
+        waiter.wait(bar_full0 + 8 * (n & 1), (uint32_t)((n >> 1) & 1));
+
+        // ---- phase 1a: log-gates of my tokens, running sum inside my group ----------------------------
+        float2 gl[TPG];
+        {
+            float2 run = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < TPG; ++u) {
+                const int tt = dir ? TPG - 1 - u : u;                 // scan order inside the group
+                const int tok = grp * TPG + tt;
+                float2 g = Pack2<T>::unpack(sg[tok * CPW + cp]);
+                g.x = gate_transform(g.x, p.gate_norm, p.clamp_min);
+                g.y = gate_transform(g.y, p.gate_norm, p.clamp_min);
+                if (t0 + tok >= p.L) g = make_float2(0.f, 0.f);       // padded rows: decay 1
+                run.x += g.x; run.y += g.y;
+                gl[tt] = run;                                         // inclusive cumulative sum in scan order
+            }
+            reinterpret_cast<float2*>(part)[grp * CPW + cp] = run;
+        }
+        __syncthreads();
+        // ---- phase 1b: offsets across groups, reference and last cumulative gate ---------------------
+        float2 off = make_float2(0.f, 0.f), gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int g2 = 0; g2 < NG; ++g2) {
+            const float2 s = reinterpret_cast<const float2*>(part)[g2 * CPW + cp];
+            const bool before = dir ? g2 > grp : g2 < grp;            // scanned before my group
+            const bool in_ref = dir ? g2 >= NG / 2 : g2 < NG / 2;     // part of the cumulative gate at the middle token
+            if (before) { off.x += s.x; off.y += s.y; }
+            if (in_ref) { gref.x += s.x; gref.y += s.y; }
+            glast.x += s.x; glast.y += s.y;
+        }
+        bool out_of_range = false;
+#pragma unroll
+        for (int u = 0; u < TPG; ++u) {
+            const int tok = grp * TPG + u;
+            float ex = off.x + gl[u].x - gref.x, ey = off.y + gl[u].y - gref.y;
+            out_of_range |= fabsf(ex) > MAX_EXPONENT || fabsf(ey) > MAX_EXPONENT;
+            ex = fminf(fmaxf(ex, -MAX_EXPONENT), MAX_EXPONENT);
+            ey = fminf(fmaxf(ey, -MAX_EXPONENT), MAX_EXPONENT);
+            const uint32_t o = swz(tok, cp * 4);
+            const float2 kk = Pack2<T>::unpack(sk[tok * CPW + cp]);
+            *reinterpret_cast<uint32_t*>(smem + OFF_KT + o) = Pack2<T>::pack(kk.x * __expf(-ex), kk.y * __expf(-ey));
+            if (!STATES_ONLY) {
+                const float2 qq = Pack2<T>::unpack(sq[tok * CPW + cp]);
+                *reinterpret_cast<uint32_t*>(smem + OFF_QT + o) = Pack2<T>::pack(qq.x * p.qscale * __expf(ex), qq.y * p.qscale * __expf(ey));
+            }
+        }
+        if (out_of_range && p.status) atomicOr(p.status, 2);
+        if (grp == 0) {
+            vec[2 * cp] = __expf(glast.x); vec[2 * cp + 1] = __expf(glast.y);
+            vec[64 + 2 * cp] = __expf(glast.x - gref.x); vec[64 + 2 * cp + 1] = __expf(glast.y - gref.y);
+            gtot[2 * cp] += glast.x; gtot[2 * cp + 1] += glast.y;
+        }
+        // state operand for the inter-chunk product: bf16(exp(G_ref) * S_in), MN-major [channel][value]
+        if (!STATES_ONLY && st_thread) {
+            float gr = 0.f;
+#pragma unroll
+            for (int g2 = 0; g2 < NG / 2; ++g2) gr += part[(dir ? g2 + NG / 2 : g2) * DK + st_row];
+            const float eg = __expf(gr);
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 w;
+                w.x = Pack2<T>::pack(S[j] * eg, S[j + 1] * eg); w.y = Pack2<T>::pack(S[j + 2] * eg, S[j + 3] * eg);
+                w.z = Pack2<T>::pack(S[j + 4] * eg, S[j + 5] * eg); w.w = Pack2<T>::pack(S[j + 6] * eg, S[j + 7] * eg);
+                *reinterpret_cast<uint4*>(smem + OFF_ST + swz(st_row, (st_col0 + j) * 2)) = w;
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- MMA issue 1: scores, inter-chunk product, state update ------------------------------------
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t qt = sbase + OFF_QT, kt = sbase + OFF_KT, st = sbase + OFF_ST;
+            if (!STATES_ONLY) {
+#pragma unroll
+                for (int k4 = 0; k4 < DK / 16; ++k4)
+                    tc_mma(tmem + TM_P, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
+                tc_commit(bar_p);
+                const bool first_touch = dir == dir_first;            // the chunk's accumulator has no content yet
+#pragma unroll
+                for (int k4 = 0; k4 < DK / 16; ++k4)
+                    tc_mma(tmem + TM_O + c * 64, make_desc(qt + k4 * 32), make_desc(st + k4 * 2048), IDESC_OV, !(first_touch && k4 == 0));
+            }
+#pragma unroll
+            for (int k8 = 0; k8 < CHUNK / 16; ++k8)
+                tc_mma(tmem + TM_U, make_desc(kt + k8 * 2048), make_desc(v_addr + k8 * 2048), IDESC_U, k8 > 0);
+            tc_commit(bar_u);
+        }
+        __syncwarp();
+
+        // ---- scores -> masked bf16 P tile --------------------------------------------------------------
+        if (!STATES_ONLY) {
+            waiter.wait(bar_p, par);
+            tc_fence_after();
+            const int row = 32 * (warp & 3) + lane;                   // query token inside the chunk
+            const int colh = 64 * (warp >> 2);                        // my 64 key columns
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float a[32];
+                const int j0 = colh + 32 * half;
+                tc_ld32(tmem + lane_base + TM_P + j0, a);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    float m[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int jj = j0 + j + e;
+                        m[e] = (dir ? jj >= row : jj <= row) ? a[j + e] : 0.f;
+                    }
+                    uint4 w;
+                    w.x = Pack2<T>::pack(m[0], m[1]); w.y = Pack2<T>::pack(m[2], m[3]);
+                    w.z = Pack2<T>::pack(m[4], m[5]); w.w = Pack2<T>::pack(m[6], m[7]);
+                    const int jj = j0 + j;                            // key column of the first element
+                    *reinterpret_cast<uint4*>(smem + OFF_P + (jj >> 6) * TILE_B + swz(row, (jj & 63) * 2)) = w;
+                }
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after();
+                const uint32_t pa = sbase + OFF_P;
+#pragma unroll
+                for (int k8 = 0; k8 < CHUNK / 16; ++k8)
+                    tc_mma(tmem + TM_O + c * 64, make_desc(pa + (k8 >> 2) * TILE_B + (k8 & 3) * 32), make_desc(v_addr + k8 * 2048), IDESC_OV, 1);
+                tc_commit(bar_o);
+            }
+            __syncwarp();
+        }
+
+        // ---- state update in registers ---------------------------------------------------------------
+        waiter.wait(bar_u, par);
+        tc_fence_after();
+        {
+            float u[32];
+            tc_ld32(tmem + lane_base + TM_U + st_col0, u);            // warp-wide; only state threads use the result
+            tc_wait_ld();
+            if (st_thread) {
+                const float e_last = vec[st_row], e_rel = vec[64 + st_row];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) S[j] = fmaf(S[j], e_last, e_rel * u[j]);
+            }
+        }
+        if (!STATES_ONLY) waiter.wait(bar_o, par);                    // operands and the V stage are free again
+        tc_fence_before();
+        __syncthreads();
+
+        if (ci == nch - 1) {                      // a sweep ends: hand the state out
+            float* dst = nullptr;
+            float* gdst = nullptr;
+            if (STATES_ONLY) {
+                const size_t slot = ((size_t)bh * nseg + seg) * 2 + dir;
+                dst = p.ws_state + slot * DK * DV;
+                gdst = p.ws_decay + slot * DK;
+            } else if (!use_ws) {                 // single segment: final state / total decay straight to the caller
+                if (dir ? p.final_b : p.final_f) dst = (dir ? p.final_b : p.final_f) + (size_t)bh * DK * DV;
+                if (dir ? p.logdecay_b : p.logdecay_f) gdst = (dir ? p.logdecay_b : p.logdecay_f) + (size_t)bh * DK;
+            }
+            if (dst && st_thread) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) dst[st_row * DV + st_col0 + j] = S[j];
+            }
+            if (gdst && tid < DK) gdst[tid] = gtot[tid];
+        }
+    }
+
+    // ---- epilogue: output accumulators -> global -----------------------------------------------------
+    if (!STATES_ONLY && p.o) {
+        tc_fence_after();
+        T* obase = reinterpret_cast<T*>(p.o) + b * p.so[0] + h * p.so[1];
+        const int row = 32 * (warp & 3) + lane, col0 = 32 * (warp >> 2);
+        for (int c = 0; c < nch; ++c) {
+            float a[32];
+            tc_ld32(tmem + lane_base + TM_O + c * 64 + col0, a);
+            tc_wait_ld();
+            const int tok = seg_t0 + c * CHUNK + row;
+            if (tok < p.L) {
+                uint4* dst = reinterpret_cast<uint4*>(obase + (int64_t)tok * p.so[2] + col0);
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 w;
+                    w.x = Pack2<T>::pack(a[j], a[j + 1]); w.y = Pack2<T>::pack(a[j + 2], a[j + 3]);
+                    w.z = Pack2<T>::pack(a[j + 4], a[j + 5]); w.w = Pack2<T>::pack(a[j + 6], a[j + 7]);
+                    dst[j / 8] = w;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Host side: tensor maps through the driver entry point (no link-time dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// [B,H,L,d] view with element strides s = (b, h, l): box of 128 tokens x d channels of one (b, h).
+bool make_map(CUtensorMap* m, const void* base, const int64_t* s, int B, int H, int L, int d, int dtype, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)s[2] * 2, (cuuint64_t)s[1] * 2, (cuuint64_t)s[0] * 2};
+    cuuint32_t box[4] = {(cuuint32_t)d, CHUNK, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, dtype == VIG_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+bool tma_ok(const void* base, const int64_t* s, int B, int H) {
+    if (!base) return true;
+    if (reinterpret_cast<uintptr_t>(base) & 15) return false;
+    for (int i = 0; i < 3; ++i) {
+        const bool unused = (i == 0 && B == 1) || (i == 1 && H == 1);
+        if (s[i] <= 0 && !unused) return false;
+        if ((s[i] * 2) % 16) return false;
+    }
+    return true;
+}
+
+template <int DK, typename T>
+int launch_tc(const BiglaParams& p_in, const TcMaps& maps, cudaStream_t stream) {
+    BiglaParams p = p_in;
+    const int nseg = (p.L + SEG - 1) / SEG;
+    const int BH = p.B * p.H;
+    const bool need_states = p.final_f || p.final_b || p.logdecay_f || p.logdecay_b;
+    const int use_ws = nseg > 1;
+    dim3 grid(nseg, BH);
+    auto kA = bigla_tc_kernel<DK, T, true>;
+    auto kC = bigla_tc_kernel<DK, T, false>;
+    cudaError_t e;
+    if (use_ws || (need_states && !p.o)) {
+        if ((e = cudaFuncSetAttribute(kA, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
+        kA<<<grid, NTHREADS, SMEM_BYTES, stream>>>(maps, p, 1);
+        p.nchunk = nseg;
+        if (int st = bigla_scan_launch(p, stream)) return st;
+    }
+    if (p.o) {
+        if ((e = cudaFuncSetAttribute(kC, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
+        kC<<<grid, NTHREADS, SMEM_BYTES, stream>>>(maps, p, use_ws);
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+bool bigla_tc_supported(const BiglaParams& p) {
+    if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
+    if (p.dv != DV || (p.dk != 32 && p.dk != 64)) return false;
+    if (!tma_ok(p.q, p.sq, p.B, p.H) || !tma_ok(p.k, p.sk, p.B, p.H) || !tma_ok(p.v, p.sv, p.B, p.H) ||
+        !tma_ok(p.gf, p.sgf, p.B, p.H) || !tma_ok(p.gb, p.sgb, p.B, p.H))
+        return false;
+    if (p.o && ((reinterpret_cast<uintptr_t>(p.o) & 15) || (p.so[0] * 2) % 16 || (p.so[1] * 2) % 16 || (p.so[2] * 2) % 16)) return false;
+    return encode_fn() != nullptr;
+}
+
+size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv) {
+    const size_t nseg = (L + SEG - 1) / SEG;
+    return (size_t)B * H * nseg * 2 * ((size_t)dk * dv + dk) * sizeof(float);
+}
+
+int bigla_tc_launch(const BiglaParams& p_in, void* ws, size_t ws_bytes, cudaStream_t stream) {
+    BiglaParams p = p_in;
+    const size_t nseg = (p.L + SEG - 1) / SEG;
+    if (ws_bytes < bigla_tc_workspace(p.B, p.H, p.L, p.dk, p.dv)) return VIG_ERR_WORKSPACE;
+    p.ws_state = reinterpret_cast<float*>(ws);
+    p.ws_decay = p.ws_state + (size_t)p.B * p.H * nseg * 2 * p.dk * p.dv;
+    TcMaps maps;
+    const void* qsrc = p.q ? p.q : p.k;           // states-only calls pass no q; the map is then never used
+    const int64_t* qs = p.q ? p.sq : p.sk;
+    const void* gfs = p.gf ? p.gf : p.gb;
+    const int64_t* gfst = p.gf ? p.sgf : p.sgb;
+    const void* gbs = p.gb ? p.gb : p.gf;
+    const int64_t* gbst = p.gb ? p.sgb : p.sgf;
+    if (!make_map(&maps.q, qsrc, qs, p.B, p.H, p.L, p.dk, p.dtype, false) ||
+        !make_map(&maps.k, p.k, p.sk, p.B, p.H, p.L, p.dk, p.dtype, false) ||
+        !make_map(&maps.v, p.v, p.sv, p.B, p.H, p.L, p.dv, p.dtype, true) ||
+        !make_map(&maps.gf, gfs, gfst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
+        !make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false))
+        return VIG_ERR_DEVICE;
+#define VIG_TC(DKV, TT) if (p.dk == DKV) return launch_tc<DKV, TT>(p, maps, stream);
+    if (p.dtype == VIG_DTYPE_BF16) { VIG_TC(64, __nv_bfloat16) VIG_TC(32, __nv_bfloat16) }
+    else { VIG_TC(64, __half) VIG_TC(32, __half) }
+#undef VIG_TC
+    return VIG_ERR_SHAPE;
+}
+
+}  // namespace vig

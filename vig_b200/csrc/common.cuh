@@ -75,6 +75,8 @@ __device__ __forceinline__ float gate_transform(float x, float gate_norm, float 
 
 int bigla_simt_launch(const BiglaParams& p, cudaStream_t stream);
 size_t bigla_simt_workspace(int B, int H, int L, int dk, int dv);
+// scan over p.nchunk per-chunk (or per-segment) local states in the workspace, in place (phase B)
+int bigla_scan_launch(const BiglaParams& p, cudaStream_t stream);
 int bigla_tc_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream);
 size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv);
 bool bigla_tc_supported(const BiglaParams& p);
