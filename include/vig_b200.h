@@ -42,6 +42,7 @@ extern "C" {
 #define VIG_ERR_WORKSPACE (-5)  /* workspace missing or too small */
 #define VIG_ERR_ARG (-6)        /* any other rejected argument */
 #define VIG_ERR_DEVICE (-7)     /* not an sm_100 device / driver entry point missing */
+#define VIG_ERR_SCRATCH_LIMIT (-8) /* the call needs more scratch than vig_bigla_fwd_noalloc's fixed array holds */
 
 /* Which implementation of the scan runs.  AUTO picks the tcgen05 kernel for bf16/fp16 inputs whose
  * layout it supports and the SIMT kernel otherwise (fp32 inputs always take the SIMT kernel: the
@@ -96,6 +97,35 @@ VIG_API int vig_bigla_fwd(const void* q, const void* k, const void* v, const voi
                   float* total_logdecay_fwd, float* total_logdecay_bwd,
                   int dir_mask, int impl,
                   void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/*
+ * Bi-GLA forward for callers that cannot allocate device memory (no counterpart in the reference: its
+ * operators allocate their temporaries through PyTorch on every call).
+ *
+ * Who needs it: a host that is given only input and output buffers and may not call cudaMalloc when it
+ * runs the operator -- an inference plugin inside someone else's runtime, a server whose memory pool is
+ * fixed after start-up, any caller without a workspace to lend.  Same arithmetic and same kernels as
+ * vig_bigla_fwd with both directions, no initial / final states; the scratch that call takes as
+ * `workspace` lives here in a fixed device array of VIG_NOALLOC_SCRATCH_BYTES inside the library, which
+ * every GPU that loads the library holds until the process exits.
+ *
+ * Limit: vig_bigla_workspace_bytes(B,H,L,dk,dv,dtype,impl) must not exceed VIG_NOALLOC_SCRATCH_BYTES,
+ * else VIG_ERR_SCRATCH_LIMIT is returned and nothing is launched (sequences of at most one 512-token
+ * segment on the tensor-core path, or 64 tokens on the SIMT path, need no scratch at all).
+ * The call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
+ * The first call on each device looks up the array's device address (with that device current); make that
+ * first call outside any stream capture.  All calls on a device share the one array: calls that may overlap
+ * on the GPU (different streams without ordering between them) race on it -- keep them on one stream or
+ * order them with events.  Nothing in the array has to start at zero; each call overwrites what it uses.
+ */
+#define VIG_NOALLOC_SCRATCH_BYTES (16u << 20)
+VIG_API size_t vig_bigla_noalloc_scratch_bytes(void);
+VIG_API int vig_bigla_fwd_noalloc(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, void* o,
+                          int B, int H, int L, int dk, int dv, int dtype,
+                          const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
+                          const int64_t* strides_gf, const int64_t* strides_gb, const int64_t* strides_o,
+                          float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
+                          int impl, int32_t* status_dev, void* stream);
 
 /*
  * Depthwise 3x3 convolution (zero padding 1) over tokens laid out [B, L = h*w, C] with C contiguous,

@@ -1,0 +1,51 @@
+"""The entry point for callers that cannot allocate device memory (an inference plugin that is handed only
+its buffers, a server with a frozen memory pool): ``vig_bigla_fwd_noalloc`` keeps the scan's scratch in a
+fixed array inside the library.  It runs the same kernels as ``vig_bigla_fwd``, so its output must equal
+that entry point's, also on a second call that reuses the array with other data and another shape.
+This file is collected last on purpose: a run that stops at the first failure has then run everything else.
+"""
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(B, H, L, dk, dtype, seed):
+    return [t.to("cuda", dtype) for t in oracle.make_bigla_inputs(B, H, L, dk, 64, seed=seed)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_noalloc_matches_workspace_entry_point_twice_in_a_row(dtype):
+    import vig_b200
+    from vig_b200 import ops
+    # both shapes span several segments, so the scratch array is really used; the second call is larger
+    for call, (B, H, L, dk) in enumerate([(2, 3, 1300, 64), (3, 2, 2100, 32)]):
+        q, k, v, gf, gb = _inputs(B, H, L, dk, dtype, seed=40 + call)
+        expected = vig_b200.bi_gla(q, k, v, gf, gb, out_scale=0.5)
+        out = torch.full_like(expected, float("nan"))
+        before = torch.cuda.memory_allocated()
+        ops.bi_gla_noalloc(q, k, v, gf, gb, out, out_scale=0.5)
+        assert torch.cuda.memory_allocated() == before           # nothing came from torch's allocator either
+        torch.cuda.synchronize()
+        assert torch.equal(out, expected), f"call {call}: max diff {(out.float() - expected.float()).abs().max()}"
+        ref = oracle.naive_bi_gla(*[t.float().cpu() for t in (q, k, v, gf, gb)], out_scale=0.5)
+        err = float((out.float().cpu() - ref).abs().max() / ref.abs().max())
+        assert err < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_noalloc_rejects_problems_beyond_the_fixed_scratch():
+    from vig_b200 import _lib, ops
+    L_ = _lib.lib()
+    limit = L_.vig_bigla_noalloc_scratch_bytes()
+    B, H, L, dk = 64, 3, 4096, 64
+    assert L_.vig_bigla_workspace_bytes(B, H, L, dk, 64, 1, 0) > limit
+    # sizes are checked before any pointer is touched, so tiny placeholder tensors are enough
+    x = torch.zeros(1, device="cuda", dtype=torch.bfloat16)
+    args = [_lib.ptr(x)] * 6 + [B, H, L, dk, 64, 1] + [None] * 6 + [-1.0, 1.0, 0.0, float("nan"), 0, None, None]
+    st = L_.vig_bigla_fwd_noalloc(*args)
+    assert st == -8
+    assert b"scratch" in L_.vig_strerror(st)
+    with pytest.raises(RuntimeError, match="scratch"):
+        _lib.check(st, "vig_bigla_fwd_noalloc")

@@ -16,6 +16,7 @@ extern "C" const char* vig_strerror(int status) {
         case VIG_ERR_WORKSPACE: return "workspace missing or too small";
         case VIG_ERR_ARG: return "invalid argument";
         case VIG_ERR_DEVICE: return "device or driver does not support this kernel";
+        case VIG_ERR_SCRATCH_LIMIT: return "problem needs more scratch than the fixed no-allocation array holds; use vig_bigla_fwd with a workspace";
     }
     if (status > 0) return cudaGetErrorString((cudaError_t)status);
     return "unknown status";

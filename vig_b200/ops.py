@@ -86,6 +86,23 @@ def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_log
     return out
 
 
+def bi_gla_noalloc(q, k, v, g_fwd, g_bwd, out, scale=-1, out_scale=1.0, gate_logit_normalizer=0.0, clamp_min=None,
+                   impl=_lib.IMPL_AUTO):
+    """``bi_gla`` through the entry point that allocates nothing: the caller supplies ``out`` and the scan's
+    scratch is a fixed array inside the library (see ``vig_bigla_fwd_noalloc`` in the header for who needs
+    this and for its size limit).  Calls on one device must not overlap on the GPU."""
+    _lib.require_cuda(q, k, v, g_fwd, g_bwd, out)
+    B, H, L, dk = k.shape
+    dv = v.shape[-1]
+    st = _lib.lib().vig_bigla_fwd_noalloc(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(out), B, H, L, dk, dv,
+        _lib.dtype_code(k), _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(g_fwd), _lib.strides3(g_bwd),
+        _lib.strides3(out), float(scale if scale is not None else -1), float(out_scale), float(gate_logit_normalizer),
+        _NAN if clamp_min is None else float(clamp_min), impl, None, _lib.stream_ptr())
+    _lib.check(st, "vig_bigla_fwd_noalloc")
+    return out
+
+
 def bid_fused_recurrent_gla(q, k, v, gk=None, gv=None, scale=-1, initial_state=None, output_final_state=False,
                             causal=True):
     """``fla/ops/gla/recurrent_fuse.py:659-685``: ``gk`` is ``[2B,H,L,dk]`` (forward gates then backward
