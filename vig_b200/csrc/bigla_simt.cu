@@ -111,15 +111,27 @@ __global__ void __launch_bounds__(NT) bigla_simt_state_scan(BiglaParams p) {
     const float* init = dir ? p.init_b : p.init_f;
     float S = init ? init[(size_t)bh * DKDV + e] : 0.f;
     float gsum = 0.f;
-    for (int cc = 0; cc < p.nchunk; ++cc) {
-        const int c = dir ? p.nchunk - 1 - cc : cc;
-        const size_t slot = ((size_t)bh * p.nchunk + c) * 2 + dir;
-        float* U = p.ws_state + slot * DKDV + e;
-        const float g = p.ws_decay[slot * p.dk + d];
-        const float u = *U;
-        *U = S;                                         // state entering chunk c
-        S = fmaf(S, __expf(g), u);
-        gsum += g;
+    constexpr int PF = 4;                               // loads of PF chunks are in flight before the dependent chain runs
+    for (int cc0 = 0; cc0 < p.nchunk; cc0 += PF) {
+        float u[PF], g[PF];
+        float* slotp[PF];
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            const int cc = cc0 + i;
+            const int c = dir ? p.nchunk - 1 - cc : cc;
+            const size_t slot = ((size_t)bh * p.nchunk + (cc < p.nchunk ? c : 0)) * 2 + dir;
+            slotp[i] = p.ws_state + slot * DKDV + e;
+            u[i] = cc < p.nchunk ? __ldcg(slotp[i]) : 0.f;
+            g[i] = cc < p.nchunk ? __ldcg(p.ws_decay + slot * p.dk + d) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+            if (cc0 + i < p.nchunk) {
+                *slotp[i] = S;                          // state entering chunk c
+                S = fmaf(S, __expf(g[i]), u[i]);
+                gsum += g[i];
+            }
+        }
     }
     float* fin = dir ? p.final_b : p.final_f;
     if (fin) fin[(size_t)bh * DKDV + e] = S;

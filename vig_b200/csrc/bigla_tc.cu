@@ -1,6 +1,7 @@
 // Bi-directional gated linear attention on the 5th-generation tensor cores (tcgen05 + TMEM), bf16 / fp16.
 //
-// One CTA owns one (segment, batch*head): up to SEG_CHUNKS chunks of 128 tokens.  It sweeps its chunks
+// One CTA owns one (segment, batch*head): up to SEG_CHUNKS chunks of 128 tokens (two CTAs share an SM, so
+// one of them computes gates while the other waits for TMA or the tensor pipe).  It sweeps its chunks
 // twice -- left to right with the forward gates, right to left with the backward gates -- and keeps the
 // output accumulators of all its chunks in tensor memory between the sweeps, so q/k/v and both gate
 // tensors are fetched by TMA once per sweep and the output is written once.  Per chunk and direction:
@@ -26,27 +27,29 @@ namespace vig {
 namespace {
 
 constexpr int CHUNK = 128;            // tokens per chunk = rows of one MMA tile
-constexpr int SEG_CHUNKS = 4;         // chunks per CTA: 4 x 64 TMEM columns of output accumulators
+constexpr int SEG_CHUNKS = 2;         // chunks per CTA: 2 x 64 TMEM columns of output accumulators
 constexpr int SEG = CHUNK * SEG_CHUNKS;
 constexpr int NTHREADS = 256;
 constexpr int DV = 64;
 constexpr float MAX_EXPONENT = 80.f;  // exp() arguments of the factorisation are clamped to +-80
 
-// TMEM columns (fp32): scores, state update, output accumulators
-constexpr uint32_t TM_P = 0, TM_U = 128, TM_O = 192, TM_COLS = 512;
+// TMEM columns (fp32), 256 per CTA so that two CTAs fit in an SM's 512: scores for key columns 0..63,
+// scores for key columns 64..127 (reused for the state update once the scores are read), outputs
+constexpr uint32_t TM_P0 = 0, TM_P1 = 64, TM_U = 64, TM_O = 128, TM_COLS = 256;
 
-// shared memory map (bytes from a 1024-aligned base)
+// shared memory map (bytes from a 1024-aligned base); ~108 KB so that two CTAs fit in one SM
 constexpr int TILE_B = CHUNK * 64 * 2;                       // 16 KB: 128 rows x 128 B
-constexpr int OFF_STAGE = 0;                                 // 2 stages x {q, k, g, v}
-constexpr int STAGE_B = 4 * TILE_B;
-constexpr int OFF_QT = OFF_STAGE + 2 * STAGE_B;
+constexpr int OFF_RQ = 0;                                    // raw q tile; later the P tile of key columns 64..127
+constexpr int OFF_RK = OFF_RQ + TILE_B;                      // raw k tile
+constexpr int OFF_RG = OFF_RK + TILE_B;                      // raw gate tile; later the P tile of key columns 0..63
+constexpr int OFF_V = OFF_RG + TILE_B;                       // v tile (128-byte swizzle, MMA operand as loaded)
+constexpr int OFF_QT = OFF_V + TILE_B;
 constexpr int OFF_KT = OFF_QT + TILE_B;
-constexpr int OFF_P = OFF_KT + TILE_B;                       // 2 blocks of 64 key columns
-constexpr int OFF_ST = OFF_P + 2 * TILE_B;                   // bf16 state operand, 64 rows x 128 B
+constexpr int OFF_ST = OFF_KT + TILE_B;                      // bf16 state operand, 64 rows x 128 B
 constexpr int OFF_PART = OFF_ST + 64 * 128;                  // fp32 [16][64] group sums of log-gates
 constexpr int OFF_VEC = OFF_PART + 16 * 64 * 4;              // fp32 [2][64]: exp(G_last), exp(G_last - G_ref)
 constexpr int OFF_GTOT = OFF_VEC + 2 * 64 * 4;               // fp32 [64] summed log-gates of the segment
-constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: full[2], p, u, o
+constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: full, p0, p1, o
 constexpr int OFF_MISC = OFF_BAR + 8 * 8;                    // tmem base, abort flag
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;             // + slack for the manual 1024-byte alignment
 
@@ -147,8 +150,16 @@ struct Waiter {
 struct TcMaps { CUtensorMap q, k, v, gf, gb; };
 
 // ---------------------------------------------------------------------------------------------------
+// log-gate from a raw logit with the fast intrinsics: min(x,0) - log(1 + exp(-|x|)), scaled; or pass-through
+__device__ __forceinline__ float fast_gate(float x, float gate_norm, float inv_norm, float clamp_min) {
+    float g = x;
+    if (gate_norm > 0.f) g = (fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x)))) * inv_norm;
+    if (clamp_min == clamp_min) g = fmaxf(g, clamp_min);
+    return g;
+}
+
 template <int DK, typename T, bool STATES_ONLY>
-__global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_constant__ TcMaps maps, BiglaParams p, int use_ws) {
+__global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_constant__ TcMaps maps, BiglaParams p, int use_ws) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -158,7 +169,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
     const int nch = min(SEG_CHUNKS, (p.L - seg_t0 + CHUNK - 1) / CHUNK);
     const int nseg = gridDim.x;
 
-    const uint32_t bar_full0 = sbase + OFF_BAR, bar_p = sbase + OFF_BAR + 16, bar_u = sbase + OFF_BAR + 24, bar_o = sbase + OFF_BAR + 32;
+    const uint32_t bar_full = sbase + OFF_BAR, bar_p0 = bar_full + 8, bar_p1 = bar_full + 16, bar_o = bar_full + 24;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
     float* part = reinterpret_cast<float*>(smem + OFF_PART);
@@ -167,8 +178,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
     const Waiter waiter{abort_flag, p.status};
 
     if (tid == 0) {
-        mbar_init(bar_full0, 1); mbar_init(bar_full0 + 8, 1);
-        mbar_init(bar_p, 1); mbar_init(bar_u, 1); mbar_init(bar_o, 1);
+        mbar_init(bar_full, 1); mbar_init(bar_p0, 1); mbar_init(bar_p1, 1); mbar_init(bar_o, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -194,40 +204,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
     const int st_row = 16 * (warp & 3) + lane;    // key channel
     const int st_col0 = 32 * (warp >> 2);         // first of 32 value columns
     const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
+    const float inv_norm = p.gate_norm > 0.f ? 1.f / p.gate_norm : 1.f;
 
-    constexpr uint32_t IDESC_QK = make_idesc(Pack2<T>::FMT, 0, 0, 128, 128);
+    constexpr uint32_t IDESC_QK = make_idesc(Pack2<T>::FMT, 0, 0, 128, 64);
     constexpr uint32_t IDESC_OV = make_idesc(Pack2<T>::FMT, 0, 1, 128, 64);
     constexpr uint32_t IDESC_U = make_idesc(Pack2<T>::FMT, 1, 1, 64, 64);
     constexpr uint32_t TX_BYTES = (STATES_ONLY ? 2 : 3) * CHUNK * DK * 2 + CHUNK * DV * 2;
 
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, dir_last = (p.dir_mask & 2) ? 1 : 0;
-    const int n_iter = (dir_last - dir_first + 1) * nch;      // iterations: sweeps x chunks, stage = n & 1
+    const int n_iter = (dir_last - dir_first + 1) * nch;      // iterations: sweeps x chunks
 
-    auto issue_loads = [&](int n) {         // thread 0 only: tiles of iteration n into stage n & 1
+    auto issue_loads = [&](int n) {         // thread 0 only: tiles of iteration n
         const int dir = dir_first + n / nch, ci = n % nch;
         const int c = dir ? nch - 1 - ci : ci;
         const int t0 = seg_t0 + c * CHUNK;
-        const uint32_t st = sbase + OFF_STAGE + (n & 1) * STAGE_B, bar = bar_full0 + 8 * (n & 1);
-        mbar_expect_tx(bar, TX_BYTES);
-        if (!STATES_ONLY) tma_load_4d(st, &maps.q, 0, t0, h, b, bar);
-        tma_load_4d(st + TILE_B, &maps.k, 0, t0, h, b, bar);
-        tma_load_4d(st + 2 * TILE_B, dir ? &maps.gb : &maps.gf, 0, t0, h, b, bar);
-        tma_load_4d(st + 3 * TILE_B, &maps.v, 0, t0, h, b, bar);
+        mbar_expect_tx(bar_full, TX_BYTES);
+        if (!STATES_ONLY) tma_load_4d(sbase + OFF_RQ, &maps.q, 0, t0, h, b, bar_full);
+        tma_load_4d(sbase + OFF_RK, &maps.k, 0, t0, h, b, bar_full);
+        tma_load_4d(sbase + OFF_RG, dir ? &maps.gb : &maps.gf, 0, t0, h, b, bar_full);
+        tma_load_4d(sbase + OFF_V, &maps.v, 0, t0, h, b, bar_full);
     };
-
     if (tid == 0) issue_loads(0);
 
     float S[32];                                  // my 32 columns of state row st_row (state threads only)
+    const uint32_t* sq = reinterpret_cast<const uint32_t*>(smem + OFF_RQ);
+    const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + OFF_RK);
+    const uint32_t* sg = reinterpret_cast<const uint32_t*>(smem + OFF_RG);
 
     for (int n = 0; n < n_iter; ++n) {
         const int dir = dir_first + n / nch, ci = n % nch;
         const int c = dir ? nch - 1 - ci : ci;
         const int t0 = seg_t0 + c * CHUNK;
-        const uint8_t* stg = smem + OFF_STAGE + (n & 1) * STAGE_B;
-        const uint32_t* sq = reinterpret_cast<const uint32_t*>(stg);
-        const uint32_t* sk = reinterpret_cast<const uint32_t*>(stg + TILE_B);
-        const uint32_t* sg = reinterpret_cast<const uint32_t*>(stg + 2 * TILE_B);
-        const uint32_t v_addr = sbase + OFF_STAGE + (n & 1) * STAGE_B + 3 * TILE_B;
         const uint32_t par = (uint32_t)(n & 1);
 
         if (ci == 0) {                            // a sweep starts: entering state of the segment, zeroed gate total
@@ -242,9 +249,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
             }
             if (tid < DK) gtot[tid] = 0.f;
         }
-        if (tid == 0 && n + 1 < n_iter) issue_loads(n + 1);       // the other stage was released at the end of n-1
-        __syncwarp();
-        waiter.wait(bar_full0 + 8 * (n & 1), (uint32_t)((n >> 1) & 1));
+        waiter.wait(bar_full, par);
 
         // ---- phase 1a: log-gates of my tokens, running sum inside my group ----------------------------
         float2 gl[TPG];
@@ -255,11 +260,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
                 const int tt = dir ? TPG - 1 - u : u;                 // scan order inside the group
                 const int tok = grp * TPG + tt;
                 float2 g = Pack2<T>::unpack(sg[tok * CPW + cp]);
-                g.x = gate_transform(g.x, p.gate_norm, p.clamp_min);
-                g.y = gate_transform(g.y, p.gate_norm, p.clamp_min);
+                g.x = fast_gate(g.x, p.gate_norm, inv_norm, p.clamp_min);
+                g.y = fast_gate(g.y, p.gate_norm, inv_norm, p.clamp_min);
                 if (t0 + tok >= p.L) g = make_float2(0.f, 0.f);       // padded rows: decay 1
                 run.x += g.x; run.y += g.y;
-                gl[tt] = run;                                         // inclusive cumulative sum in scan order
+                gl[u] = run;                                          // inclusive cumulative sum, indexed in scan order
             }
             reinterpret_cast<float2*>(part)[grp * CPW + cp] = run;
         }
@@ -268,19 +273,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
         float2 off = make_float2(0.f, 0.f), gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
 #pragma unroll
         for (int g2 = 0; g2 < NG; ++g2) {
-            const float2 s = reinterpret_cast<const float2*>(part)[g2 * CPW + cp];
+            const float2 s2 = reinterpret_cast<const float2*>(part)[g2 * CPW + cp];
             const bool before = dir ? g2 > grp : g2 < grp;            // scanned before my group
             const bool in_ref = dir ? g2 >= NG / 2 : g2 < NG / 2;     // part of the cumulative gate at the middle token
-            if (before) { off.x += s.x; off.y += s.y; }
-            if (in_ref) { gref.x += s.x; gref.y += s.y; }
-            glast.x += s.x; glast.y += s.y;
+            if (before) { off.x += s2.x; off.y += s2.y; }
+            if (in_ref) { gref.x += s2.x; gref.y += s2.y; }
+            glast.x += s2.x; glast.y += s2.y;
         }
+        off.x -= gref.x; off.y -= gref.y;
         bool out_of_range = false;
 #pragma unroll
         for (int u = 0; u < TPG; ++u) {
-            const int tok = grp * TPG + u;
-            float ex = off.x + gl[u].x - gref.x, ey = off.y + gl[u].y - gref.y;
-            out_of_range |= fabsf(ex) > MAX_EXPONENT || fabsf(ey) > MAX_EXPONENT;
+            const int tok = grp * TPG + (dir ? TPG - 1 - u : u);
+            float ex = off.x + gl[u].x, ey = off.y + gl[u].y;
+            out_of_range |= fmaxf(fabsf(ex), fabsf(ey)) > MAX_EXPONENT;
             ex = fminf(fmaxf(ex, -MAX_EXPONENT), MAX_EXPONENT);
             ey = fminf(fmaxf(ey, -MAX_EXPONENT), MAX_EXPONENT);
             const uint32_t o = swz(tok, cp * 4);
@@ -313,72 +319,76 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
         }
         fence_proxy_async();
         tc_fence_before();
-        __syncthreads();
+        __syncthreads();                          // raw q / k / gate tiles are dead from here on
 
-        // ---- MMA issue 1: scores, inter-chunk product, state update ------------------------------------
-        if (tid == 0) {
-            tc_fence_after();
-            const uint32_t qt = sbase + OFF_QT, kt = sbase + OFF_KT, st = sbase + OFF_ST;
-            if (!STATES_ONLY) {
+        const uint32_t kt = sbase + OFF_KT, v_addr = sbase + OFF_V;
+        if (!STATES_ONLY) {
+            // ---- MMA issue 1: scores in two halves of 64 key columns, inter-chunk product ----------------
+            if (tid == 0) {
+                tc_fence_after();
+                const uint32_t qt = sbase + OFF_QT, st = sbase + OFF_ST;
 #pragma unroll
                 for (int k4 = 0; k4 < DK / 16; ++k4)
-                    tc_mma(tmem + TM_P, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
-                tc_commit(bar_p);
+                    tc_mma(tmem + TM_P0, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
+                tc_commit(bar_p0);
+#pragma unroll
+                for (int k4 = 0; k4 < DK / 16; ++k4)
+                    tc_mma(tmem + TM_P1, make_desc(qt + k4 * 32), make_desc(kt + 64 * 128 + k4 * 32), IDESC_QK, k4 > 0);
+                tc_commit(bar_p1);
                 const bool first_touch = dir == dir_first;            // the chunk's accumulator has no content yet
 #pragma unroll
                 for (int k4 = 0; k4 < DK / 16; ++k4)
                     tc_mma(tmem + TM_O + c * 64, make_desc(qt + k4 * 32), make_desc(st + k4 * 2048), IDESC_OV, !(first_touch && k4 == 0));
             }
-#pragma unroll
-            for (int k8 = 0; k8 < CHUNK / 16; ++k8)
-                tc_mma(tmem + TM_U, make_desc(kt + k8 * 2048), make_desc(v_addr + k8 * 2048), IDESC_U, k8 > 0);
-            tc_commit(bar_u);
-        }
-        __syncwarp();
-
-        // ---- scores -> masked bf16 P tile --------------------------------------------------------------
-        if (!STATES_ONLY) {
-            waiter.wait(bar_p, par);
-            tc_fence_after();
+            __syncwarp();
+            // ---- scores -> masked bf16 P tiles (warps 0-3: keys 0..63 over the dead gate tile,
+            //      warps 4-7: keys 64..127 over the dead q tile) ----------------------------------------
+            const int half = warp >> 2;
             const int row = 32 * (warp & 3) + lane;                   // query token inside the chunk
-            const int colh = 64 * (warp >> 2);                        // my 64 key columns
+            uint8_t* ptile = smem + (half ? OFF_RQ : OFF_RG);
+            waiter.wait(half ? bar_p1 : bar_p0, par);
+            tc_fence_after();
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            for (int part32 = 0; part32 < 2; ++part32) {
                 float a[32];
-                const int j0 = colh + 32 * half;
-                tc_ld32(tmem + lane_base + TM_P + j0, a);
+                tc_ld32(tmem + lane_base + (half ? TM_P1 : TM_P0) + 32 * part32, a);
                 tc_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
+                    const int jj = 64 * half + 32 * part32 + j;       // key token of the first of 8 elements
                     float m[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int jj = j0 + j + e;
-                        m[e] = (dir ? jj >= row : jj <= row) ? a[j + e] : 0.f;
-                    }
+                    for (int e = 0; e < 8; ++e) m[e] = (dir ? jj + e >= row : jj + e <= row) ? a[j + e] : 0.f;
                     uint4 w;
                     w.x = Pack2<T>::pack(m[0], m[1]); w.y = Pack2<T>::pack(m[2], m[3]);
                     w.z = Pack2<T>::pack(m[4], m[5]); w.w = Pack2<T>::pack(m[6], m[7]);
-                    const int jj = j0 + j;                            // key column of the first element
-                    *reinterpret_cast<uint4*>(smem + OFF_P + (jj >> 6) * TILE_B + swz(row, (jj & 63) * 2)) = w;
+                    *reinterpret_cast<uint4*>(ptile + swz(row, (32 * part32 + j) * 2)) = w;
                 }
             }
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
-            if (tid == 0) {
-                tc_fence_after();
-                const uint32_t pa = sbase + OFF_P;
+        }
+        // ---- MMA issue 2: P V into the output accumulator, state update into the second score buffer ----
+        if (tid == 0) {
+            tc_fence_after();
+            if (!STATES_ONLY) {
 #pragma unroll
                 for (int k8 = 0; k8 < CHUNK / 16; ++k8)
-                    tc_mma(tmem + TM_O + c * 64, make_desc(pa + (k8 >> 2) * TILE_B + (k8 & 3) * 32), make_desc(v_addr + k8 * 2048), IDESC_OV, 1);
-                tc_commit(bar_o);
+                    tc_mma(tmem + TM_O + c * 64, make_desc(sbase + (k8 < 4 ? OFF_RG : OFF_RQ) + (k8 & 3) * 32),
+                           make_desc(v_addr + k8 * 2048), IDESC_OV, 1);
             }
-            __syncwarp();
+#pragma unroll
+            for (int k8 = 0; k8 < CHUNK / 16; ++k8)
+                tc_mma(tmem + TM_U, make_desc(kt + k8 * 2048), make_desc(v_addr + k8 * 2048), IDESC_U, k8 > 0);
+            tc_commit(bar_o);
         }
+        __syncwarp();
 
         // ---- state update in registers ---------------------------------------------------------------
-        waiter.wait(bar_u, par);
+        waiter.wait(bar_o, par);                  // all MMAs of the iteration are done: every tile is free again
+        if (tid == 0 && n + 1 < n_iter) issue_loads(n + 1);
+        __syncwarp();
         tc_fence_after();
         {
             float u[32];
@@ -390,7 +400,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) bigla_tc_kernel(const __grid_cons
                 for (int j = 0; j < 32; ++j) S[j] = fmaf(S[j], e_last, e_rel * u[j]);
             }
         }
-        if (!STATES_ONLY) waiter.wait(bar_o, par);                    // operands and the V stage are free again
         tc_fence_before();
         __syncthreads();
 
