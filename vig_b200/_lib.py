@@ -9,7 +9,7 @@ from ctypes import c_float, c_int, c_int32, c_int64, c_size_t, c_void_p, POINTER
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libvig_b200.so")
+LIB_PATH = os.environ.get("VIG_B200_LIB") or os.path.join(_HERE, "libvig_b200.so")
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 IMPL_AUTO, IMPL_SIMT, IMPL_TC = 0, 1, 2

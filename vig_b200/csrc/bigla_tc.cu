@@ -21,6 +21,7 @@
 // waiting on anything else, finishes its control flow and frees its tensor memory.
 #include <cuda.h>
 #include <mutex>
+#include <type_traits>
 #include "common.cuh"
 
 namespace vig {
@@ -147,15 +148,36 @@ struct Waiter {
     }
 };
 
+// 128-thread named barriers with immediate ids (a register id would make the compiler reserve all 16 barriers)
+__device__ __forceinline__ void half_bar_sync(int half) {
+    if (half) asm volatile("bar.sync 2, 128;" ::: "memory");
+    else asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
 struct TcMaps { CUtensorMap q, k, v, gf, gb; };
 
+#ifdef VIG_TC_TIMING
+__device__ long long g_tc_timing[64 * 16];
+#define TC_STAMP(slot) do { if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 1 && n < 4) g_tc_timing[(STATES_ONLY ? 0 : 512) + n * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TC_STAMP(slot) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------------------
-// log-gate from a raw logit with the fast intrinsics: min(x,0) - log(1 + exp(-|x|)), scaled; or pass-through
-__device__ __forceinline__ float fast_gate(float x, float gate_norm, float inv_norm, float clamp_min) {
-    float g = x;
-    if (gate_norm > 0.f) g = (fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x)))) * inv_norm;
-    if (clamp_min == clamp_min) g = fmaxf(g, clamp_min);
-    return g;
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+// single-instruction exp2 / log2 (flush-to-zero forms: no denormal fix-up code around the MUFU)
+__device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float lg2(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+constexpr float MAX_EXPONENT2 = MAX_EXPONENT * LOG2E;   // the exponent bound in log2 units
+
+// Log-gate in LOG2 units.  From a raw logit: logsigmoid(x) = min(x,0) - log(1 + exp(-|x|)), here with y = x log2(e):
+// min(y,0) - log2(1 + 2^-|y|), times 1/normalizer.  From a log-gate: x log2(e).  clamp_lo is -inf when unused.
+__device__ __forceinline__ float fast_gate2(float x, bool raw_logits, float inv_norm, float clamp_lo) {
+    const float y = x * LOG2E;
+    float g = y;
+    if (raw_logits) g = (fminf(y, 0.f) - lg2(1.f + ex2(-fabsf(y)))) * inv_norm;
+    return fmaxf(g, clamp_lo);
 }
 
 template <int DK, typename T, bool STATES_ONLY>
@@ -204,7 +226,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const int st_row = 16 * (warp & 3) + lane;    // key channel
     const int st_col0 = 32 * (warp >> 2);         // first of 32 value columns
     const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
-    const float inv_norm = p.gate_norm > 0.f ? 1.f / p.gate_norm : 1.f;
+    const bool raw_logits = p.gate_norm > 0.f;
+    const float inv_norm = raw_logits ? 1.f / p.gate_norm : 1.f;
+    const float clamp_lo = (p.clamp_min == p.clamp_min) ? p.clamp_min * LOG2E : -INFINITY;
+    const float lq = __log2f(fabsf(p.qscale));   // |scale * out_scale| folded into the exponent of the q operand
+    const float o_sign = p.qscale < 0.f ? -1.f : 1.f;
 
     constexpr uint32_t IDESC_QK = make_idesc(Pack2<T>::FMT, 0, 0, 128, 64);
     constexpr uint32_t IDESC_OV = make_idesc(Pack2<T>::FMT, 0, 1, 128, 64);
@@ -245,62 +271,72 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                     else if (dir ? p.init_b : p.init_f) src = (dir ? p.init_b : p.init_f) + (size_t)bh * DK * DV;
                 }
 #pragma unroll
-                for (int j = 0; j < 32; ++j) S[j] = src ? src[st_row * DV + st_col0 + j] : 0.f;
+                for (int j = 0; j < 32; j += 4) {
+                    const float4 t4 = src ? __ldg(reinterpret_cast<const float4*>(src + st_row * DV + st_col0 + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    S[j] = t4.x; S[j + 1] = t4.y; S[j + 2] = t4.z; S[j + 3] = t4.w;
+                }
             }
             if (tid < DK) gtot[tid] = 0.f;
         }
-        waiter.wait(bar_full, par);
+        TC_STAMP(0);
+        if (warp == 0) waiter.wait(bar_full, par);            // one warp polls; the others sleep in the barrier
+        __syncthreads();
+        TC_STAMP(1);
 
-        // ---- phase 1a: log-gates of my tokens, running sum inside my group ----------------------------
-        float2 gl[TPG];
-        {
+        // ---- phase 1: cumulative gates (log2 units) and the scaled operand tiles ------------------------
+        // Instantiated per direction so that token indices, and with them the swizzled addresses, are static.
+        float2 gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
+        bool out_of_range = false;
+        auto phase1 = [&](auto dir_c) {
+            constexpr int DIR = decltype(dir_c)::value;
+            const int n_valid = p.L - t0;                             // rows at or past it are padding: decay 1
+            float2 gl[TPG];
             float2 run = make_float2(0.f, 0.f);
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) {
-                const int tt = dir ? TPG - 1 - u : u;                 // scan order inside the group
-                const int tok = grp * TPG + tt;
+            for (int u = 0; u < TPG; ++u) {                           // u runs in scan order inside the group
+                const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
                 float2 g = Pack2<T>::unpack(sg[tok * CPW + cp]);
-                g.x = fast_gate(g.x, p.gate_norm, inv_norm, p.clamp_min);
-                g.y = fast_gate(g.y, p.gate_norm, inv_norm, p.clamp_min);
-                if (t0 + tok >= p.L) g = make_float2(0.f, 0.f);       // padded rows: decay 1
+                g.x = fast_gate2(g.x, raw_logits, inv_norm, clamp_lo);
+                g.y = fast_gate2(g.y, raw_logits, inv_norm, clamp_lo);
+                if (tok >= n_valid) g = make_float2(0.f, 0.f);
                 run.x += g.x; run.y += g.y;
-                gl[u] = run;                                          // inclusive cumulative sum, indexed in scan order
+                gl[u] = run;                                          // inclusive cumulative sum
             }
             reinterpret_cast<float2*>(part)[grp * CPW + cp] = run;
-        }
-        __syncthreads();
-        // ---- phase 1b: offsets across groups, reference and last cumulative gate ---------------------
-        float2 off = make_float2(0.f, 0.f), gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
+            __syncthreads();
+            float2 off = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int g2 = 0; g2 < NG; ++g2) {
-            const float2 s2 = reinterpret_cast<const float2*>(part)[g2 * CPW + cp];
-            const bool before = dir ? g2 > grp : g2 < grp;            // scanned before my group
-            const bool in_ref = dir ? g2 >= NG / 2 : g2 < NG / 2;     // part of the cumulative gate at the middle token
-            if (before) { off.x += s2.x; off.y += s2.y; }
-            if (in_ref) { gref.x += s2.x; gref.y += s2.y; }
-            glast.x += s2.x; glast.y += s2.y;
-        }
-        off.x -= gref.x; off.y -= gref.y;
-        bool out_of_range = false;
-#pragma unroll
-        for (int u = 0; u < TPG; ++u) {
-            const int tok = grp * TPG + (dir ? TPG - 1 - u : u);
-            float ex = off.x + gl[u].x, ey = off.y + gl[u].y;
-            out_of_range |= fmaxf(fabsf(ex), fabsf(ey)) > MAX_EXPONENT;
-            ex = fminf(fmaxf(ex, -MAX_EXPONENT), MAX_EXPONENT);
-            ey = fminf(fmaxf(ey, -MAX_EXPONENT), MAX_EXPONENT);
-            const uint32_t o = swz(tok, cp * 4);
-            const float2 kk = Pack2<T>::unpack(sk[tok * CPW + cp]);
-            *reinterpret_cast<uint32_t*>(smem + OFF_KT + o) = Pack2<T>::pack(kk.x * __expf(-ex), kk.y * __expf(-ey));
-            if (!STATES_ONLY) {
-                const float2 qq = Pack2<T>::unpack(sq[tok * CPW + cp]);
-                *reinterpret_cast<uint32_t*>(smem + OFF_QT + o) = Pack2<T>::pack(qq.x * p.qscale * __expf(ex), qq.y * p.qscale * __expf(ey));
+            for (int g2 = 0; g2 < NG; ++g2) {
+                const float2 s2 = reinterpret_cast<const float2*>(part)[g2 * CPW + cp];
+                const bool before = DIR ? g2 > grp : g2 < grp;        // scanned before my group
+                const bool in_ref = DIR ? g2 >= NG / 2 : g2 < NG / 2; // part of the cumulative gate at the middle token
+                if (before) { off.x += s2.x; off.y += s2.y; }
+                if (in_ref) { gref.x += s2.x; gref.y += s2.y; }
+                glast.x += s2.x; glast.y += s2.y;
             }
-        }
+            off.x -= gref.x; off.y -= gref.y;
+            // gates are <= 0, so the cumulative sums are monotone and the extreme exponents sit at the chunk ends
+            out_of_range = fmaxf(fmaxf(-gref.x, -gref.y), fmaxf(gref.x - glast.x, gref.y - glast.y)) > MAX_EXPONENT2;
+#pragma unroll
+            for (int u = 0; u < TPG; ++u) {
+                const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
+                const float ex = fminf(fmaxf(off.x + gl[u].x, -MAX_EXPONENT2), MAX_EXPONENT2);
+                const float ey = fminf(fmaxf(off.y + gl[u].y, -MAX_EXPONENT2), MAX_EXPONENT2);
+                const uint32_t o = swz(tok, cp * 4);
+                const float2 kk = Pack2<T>::unpack(sk[tok * CPW + cp]);
+                *reinterpret_cast<uint32_t*>(smem + OFF_KT + o) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                if (!STATES_ONLY) {
+                    const float2 qq = Pack2<T>::unpack(sq[tok * CPW + cp]);
+                    *reinterpret_cast<uint32_t*>(smem + OFF_QT + o) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                }
+            }
+        };
+        if (dir) phase1(std::integral_constant<int, 1>{}); else phase1(std::integral_constant<int, 0>{});
+        TC_STAMP(2);
         if (out_of_range && p.status) atomicOr(p.status, 2);
         if (grp == 0) {
-            vec[2 * cp] = __expf(glast.x); vec[2 * cp + 1] = __expf(glast.y);
-            vec[64 + 2 * cp] = __expf(glast.x - gref.x); vec[64 + 2 * cp + 1] = __expf(glast.y - gref.y);
+            vec[2 * cp] = ex2(glast.x); vec[2 * cp + 1] = ex2(glast.y);
+            vec[64 + 2 * cp] = ex2(glast.x - gref.x); vec[64 + 2 * cp + 1] = ex2(glast.y - gref.y);
             gtot[2 * cp] += glast.x; gtot[2 * cp + 1] += glast.y;
         }
         // state operand for the inter-chunk product: bf16(exp(G_ref) * S_in), MN-major [channel][value]
@@ -308,7 +344,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             float gr = 0.f;
 #pragma unroll
             for (int g2 = 0; g2 < NG / 2; ++g2) gr += part[(dir ? g2 + NG / 2 : g2) * DK + st_row];
-            const float eg = __expf(gr);
+            const float eg = ex2(gr);
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
                 uint4 w;
@@ -320,6 +356,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();                          // raw q / k / gate tiles are dead from here on
+        TC_STAMP(3);
 
         const uint32_t kt = sbase + OFF_KT, v_addr = sbase + OFF_V;
         if (!STATES_ONLY) {
@@ -341,33 +378,53 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                     tc_mma(tmem + TM_O + c * 64, make_desc(qt + k4 * 32), make_desc(st + k4 * 2048), IDESC_OV, !(first_touch && k4 == 0));
             }
             __syncwarp();
+            TC_STAMP(4);
             // ---- scores -> masked bf16 P tiles (warps 0-3: keys 0..63 over the dead gate tile,
             //      warps 4-7: keys 64..127 over the dead q tile) ----------------------------------------
             const int half = warp >> 2;
-            const int row = 32 * (warp & 3) + lane;                   // query token inside the chunk
+            const int quad = warp & 3;                                // my 32 query rows: 32*quad .. 32*quad+31
+            const int row = 32 * quad + lane;                         // query token inside the chunk
             uint8_t* ptile = smem + (half ? OFF_RQ : OFF_RG);
-            waiter.wait(half ? bar_p1 : bar_p0, par);
+            if ((warp & 3) == 0) waiter.wait(half ? bar_p1 : bar_p0, par);
+            half_bar_sync(half);
+            TC_STAMP(5);
             tc_fence_after();
+            // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal; the test is warp-uniform.
+            auto convert = [&](auto dir_c) {
+                constexpr int DIR = decltype(dir_c)::value;
 #pragma unroll
-            for (int part32 = 0; part32 < 2; ++part32) {
-                float a[32];
-                tc_ld32(tmem + lane_base + (half ? TM_P1 : TM_P0) + 32 * part32, a);
-                tc_wait_ld();
+                for (int part32 = 0; part32 < 2; ++part32) {
+                    const int cb = 2 * half + part32;                 // key block: keys 32*cb .. 32*cb+31
+                    const bool all_zero = DIR ? cb < quad : cb > quad;
+                    const bool diagonal = cb == quad;
+                    float a[32];
+                    if (!all_zero) {
+                        tc_ld32(tmem + lane_base + (half ? TM_P1 : TM_P0) + 32 * part32, a);
+                        tc_wait_ld();
+                    }
 #pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    const int jj = 64 * half + 32 * part32 + j;       // key token of the first of 8 elements
-                    float m[8];
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+                        if (!all_zero) {
+                            float m[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) m[e] = (dir ? jj + e >= row : jj + e <= row) ? a[j + e] : 0.f;
-                    uint4 w;
-                    w.x = Pack2<T>::pack(m[0], m[1]); w.y = Pack2<T>::pack(m[2], m[3]);
-                    w.z = Pack2<T>::pack(m[4], m[5]); w.w = Pack2<T>::pack(m[6], m[7]);
-                    *reinterpret_cast<uint4*>(ptile + swz(row, (32 * part32 + j) * 2)) = w;
+                            for (int e = 0; e < 8; ++e) {
+                                const bool keep = !diagonal || (DIR ? j + e >= lane : j + e <= lane);
+                                m[e] = keep ? a[j + e] : 0.f;
+                            }
+                            w.x = Pack2<T>::pack(m[0], m[1]); w.y = Pack2<T>::pack(m[2], m[3]);
+                            w.z = Pack2<T>::pack(m[4], m[5]); w.w = Pack2<T>::pack(m[6], m[7]);
+                        }
+                        *reinterpret_cast<uint4*>(ptile + swz(row, (32 * part32 + j) * 2)) = w;
+                    }
                 }
-            }
+            };
+            if (dir) convert(std::integral_constant<int, 1>{}); else convert(std::integral_constant<int, 0>{});
+            TC_STAMP(6);
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
+            TC_STAMP(7);
         }
         // ---- MMA issue 2: P V into the output accumulator, state update into the second score buffer ----
         if (tid == 0) {
@@ -384,11 +441,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             tc_commit(bar_o);
         }
         __syncwarp();
+        TC_STAMP(8);
 
         // ---- state update in registers ---------------------------------------------------------------
-        waiter.wait(bar_o, par);                  // all MMAs of the iteration are done: every tile is free again
-        if (tid == 0 && n + 1 < n_iter) issue_loads(n + 1);
-        __syncwarp();
+        if (warp == 0) {
+            waiter.wait(bar_o, par);              // all MMAs of the iteration are done: every tile is free again
+            if (tid == 0 && n + 1 < n_iter) issue_loads(n + 1);
+        }
+        __syncthreads();
+        TC_STAMP(9);
         tc_fence_after();
         {
             float u[32];
@@ -400,8 +461,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 for (int j = 0; j < 32; ++j) S[j] = fmaf(S[j], e_last, e_rel * u[j]);
             }
         }
-        tc_fence_before();
-        __syncthreads();
+        TC_STAMP(10);
+        tc_fence_before();                        // ordered before the next tensor-core write of this buffer by the
+                                                  // CTA barriers of the next iteration
 
         if (ci == nch - 1) {                      // a sweep ends: hand the state out
             float* dst = nullptr;
@@ -416,9 +478,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
             if (dst && st_thread) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) dst[st_row * DV + st_col0 + j] = S[j];
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(dst + st_row * DV + st_col0 + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
             }
-            if (gdst && tid < DK) gdst[tid] = gtot[tid];
+            if (gdst && tid < DK) gdst[tid] = gtot[tid] * LN2;          // back to natural-log units
         }
     }
 
@@ -437,8 +500,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 w;
-                    w.x = Pack2<T>::pack(a[j], a[j + 1]); w.y = Pack2<T>::pack(a[j + 2], a[j + 3]);
-                    w.z = Pack2<T>::pack(a[j + 4], a[j + 5]); w.w = Pack2<T>::pack(a[j + 6], a[j + 7]);
+                    w.x = Pack2<T>::pack(o_sign * a[j], o_sign * a[j + 1]); w.y = Pack2<T>::pack(o_sign * a[j + 2], o_sign * a[j + 3]);
+                    w.z = Pack2<T>::pack(o_sign * a[j + 4], o_sign * a[j + 5]); w.w = Pack2<T>::pack(o_sign * a[j + 6], o_sign * a[j + 7]);
                     dst[j / 8] = w;
                 }
             }
@@ -522,6 +585,12 @@ int launch_tc(const BiglaParams& p_in, const TcMaps& maps, cudaStream_t stream) 
 }
 
 }  // namespace
+
+#ifdef VIG_TC_TIMING
+extern "C" __attribute__((visibility("default"))) int vig_dbg_tc_timing(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_tc_timing, sizeof(long long) * 64 * 16);
+}
+#endif
 
 bool bigla_tc_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
