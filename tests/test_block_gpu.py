@@ -65,6 +65,36 @@ def test_gate_inject(dtype, out_act):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,act", [(96, True), (192, False), (384, True), (768, False)])
+def test_layernorm_act(dtype, N, act):
+    import vig_b200
+    g = torch.Generator().manual_seed(N)
+    x = (3 * torch.randn(3, 5, 7, N, generator=g) + 1).to(dtype)
+    w, b = (1 + 0.2 * torch.randn(N, generator=g)).to(dtype), (0.3 * torch.randn(N, generator=g)).to(dtype)
+    ref = torch.nn.functional.layer_norm(x.float(), (N,), w.float(), b.float(), 1e-5)
+    if act:
+        ref = ref * torch.sigmoid(ref)
+    y = vig_b200.layernorm_act(x.cuda(), w.cuda(), b.cuda(), 1e-5, act)
+    assert rel_err(y.float(), ref) < TOL[dtype]
+
+
+def test_patch_embed_matches_oracle():
+    import vig_b200
+    shape = oracle.ViGShape(192, 3, 1, 0.5, 1.0, True, True, num_classes=16)
+    sd = oracle.make_state_dict(shape, seed=2)
+    model = vig_b200.ViG.from_shape(shape)
+    model.load_state_dict(sd)
+    model = model.cuda().eval()
+    for size in (224, 320):
+        img = oracle.make_images(2, size, seed=size)
+        ref, hw = oracle.patch_embed_v2({k: v.float() for k, v in sd.items()}, img)
+        with torch.no_grad():
+            tok, hw2 = model.patch_embed(img.cuda())
+        assert tuple(hw) == tuple(hw2)
+        assert rel_err(tok, ref) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     import vig_b200
     g = torch.Generator().manual_seed(4)

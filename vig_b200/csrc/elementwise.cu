@@ -9,21 +9,32 @@ namespace {
 constexpr int EW_THREADS = 256;
 
 // ---------------------------------------------------------------------------------------------------
-// Depthwise 3x3 conv, x: [B, h*w, C] (C contiguous).  One thread per (token, 16-byte channel group).
-// The nine taps of a token sit in rows y-1..y+1 of the image: 3 runs of 3 neighbouring tokens, so the
-// re-reads hit L1/L2 and DRAM traffic stays at one read + one write of the tensor.
+// Depthwise 3x3 conv, x: [B, h*w, C] (C contiguous).  One thread per (token, 16-byte channel group); its nine
+// independent 16-byte loads are in flight together.  The taps of a token sit in rows y-1..y+1 of the image:
+// the re-reads hit L1 (same row) or L2 (neighbouring rows), so DRAM traffic stays at one read + one write
+// of the tensor.  Index arithmetic is 32-bit (the host rejects tensors with 2^31 or more vectors).
 template <typename T>
 __global__ void __launch_bounds__(EW_THREADS) dwconv3x3_kernel(const T* __restrict__ x, const T* __restrict__ wt,
                                                                const T* __restrict__ bias, T* __restrict__ y,
                                                                int B, int h, int w, int C, int act) {
     constexpr int V = DType<T>::VEC;
-    const int cv = C / V;
-    const int64_t total = (int64_t)B * h * w * cv;
-    for (int64_t it = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (int64_t)gridDim.x * blockDim.x) {
-        const int c0 = (int)(it % cv) * V;
-        const int64_t tok = it / cv;
-        const int xx = (int)(tok % w);
-        const int yy = (int)((tok / w) % h);
+    const uint32_t cv = C / V;
+    const uint32_t total = (uint32_t)B * h * w * cv;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < total; it += gridDim.x * blockDim.x) {
+        const uint32_t c0 = (it % cv) * V;
+        const uint32_t tok = it / cv;
+        const int xx = (int)(tok % (uint32_t)w);
+        const int yy = (int)((tok / (uint32_t)w) % (uint32_t)h);
+        Vec16<T> xv[9];
+        bool ok[9];
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < 3; ++kx) {
+                const int y2 = yy + ky - 1, x2 = xx + kx - 1;
+                ok[ky * 3 + kx] = y2 >= 0 && y2 < h && x2 >= 0 && x2 < w;
+                if (ok[ky * 3 + kx]) xv[ky * 3 + kx].load_nc(x + ((size_t)tok + (ky - 1) * w + (kx - 1)) * C + c0);
+            }
         float acc[V];
         if (bias) {
             Vec16<T> bv; bv.load_nc(bias + c0); bv.to_float(acc);
@@ -32,27 +43,19 @@ __global__ void __launch_bounds__(EW_THREADS) dwconv3x3_kernel(const T* __restri
             for (int i = 0; i < V; ++i) acc[i] = 0.f;
         }
 #pragma unroll
-        for (int ky = 0; ky < 3; ++ky) {
-            const int y2 = yy + ky - 1;
-            if (y2 < 0 || y2 >= h) continue;
+        for (int t = 0; t < 9; ++t) {
+            if (!ok[t]) continue;
+            Vec16<T> wv; wv.load_nc(wt + t * C + c0);
+            float xf[V], wf[V];
+            xv[t].to_float(xf); wv.to_float(wf);
 #pragma unroll
-            for (int kx = 0; kx < 3; ++kx) {
-                const int x2 = xx + kx - 1;
-                if (x2 < 0 || x2 >= w) continue;
-                Vec16<T> xv, wv;
-                xv.load_nc(x + (tok + (int64_t)(ky - 1) * w + (kx - 1)) * C + c0);
-                wv.load_nc(wt + (ky * 3 + kx) * C + c0);
-                float xf[V], wf[V];
-                xv.to_float(xf); wv.to_float(wf);
-#pragma unroll
-                for (int i = 0; i < V; ++i) acc[i] = fmaf(xf[i], wf[i], acc[i]);
-            }
+            for (int i = 0; i < V; ++i) acc[i] = fmaf(xf[i], wf[i], acc[i]);
         }
         if (act) {
 #pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] = acc[i] * sigmoidf_(acc[i]);
+            for (int i = 0; i < V; ++i) acc[i] = __fdividef(acc[i], 1.f + __expf(-acc[i]));
         }
-        Vec16<T> ov; ov.from_float(acc); ov.store(y + tok * C + c0);
+        Vec16<T> ov; ov.from_float(acc); ov.store(y + (size_t)tok * C + c0);
     }
 }
 
@@ -66,16 +69,16 @@ __global__ void __launch_bounds__(EW_THREADS) gate_inject_kernel(const T* __rest
                                                                  int B, int H, int L, float eps, int out_act) {
     constexpr int V = DType<T>::VEC;
     constexpr int DV = LPG * V;
-    const int64_t groups = (int64_t)B * L * H;
+    const uint32_t groups = (uint32_t)B * L * H;
     const int lane = threadIdx.x % LPG;
     float wgf[V], wlf[V];
     { Vec16<T> t; t.load_nc(wg + lane * V); t.to_float(wgf); t.load_nc(wl + lane * V); t.to_float(wlf); }
-    for (int64_t g = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPG; g < groups;
-         g += (int64_t)gridDim.x * blockDim.x / LPG) {
-        const int hh = (int)(g % H);
-        const int64_t bl = g / H;
-        const int l = (int)(bl % L);
-        const int b = (int)(bl / L);
+    for (uint32_t g = (blockIdx.x * blockDim.x + threadIdx.x) / LPG; g < groups; g += gridDim.x * blockDim.x / LPG) {
+        const int hh = (int)(g % (uint32_t)H);
+        const uint32_t bl32 = g / (uint32_t)H;
+        const int l = (int)(bl32 % (uint32_t)L);
+        const int b = (int)(bl32 / (uint32_t)L);
+        const int64_t bl = bl32;
         const int64_t col = hh * DV + lane * V;          // column inside the [B*L, H*dv] operands
         Vec16<T> ov, lv, gv;
         ov.load_nc(o + b * so_b + hh * so_h + (int64_t)l * so_l + lane * V);
@@ -156,13 +159,70 @@ __global__ void __launch_bounds__(EW_THREADS) add_rmsnorm_kernel(const T* __rest
 }
 
 // ---------------------------------------------------------------------------------------------------
+// LayerNorm over the last dimension with affine parameters and an optional swish: the two LayerNorm2d
+// stages of the patch-embedding stem on channels-last activations.  One warp per row, row in registers.
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                                   const T* __restrict__ bias, T* __restrict__ y,
+                                                                   int64_t rows, int N, float eps, int act) {
+    constexpr int V = DType<T>::VEC;
+    const int lane = threadIdx.x & 31;
+    const int nv = N / V;
+    const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t r = warp0; r < rows; r += nwarps) {
+        float val[MAXV][V];
+        float sum = 0.f;
+#pragma unroll
+        for (int m = 0; m < MAXV; ++m) {
+            const int vi = lane + m * 32;
+            if (vi < nv) {
+                Vec16<T> xv; xv.load_nc(x + r * N + vi * V); xv.to_float(val[m]);
+#pragma unroll
+                for (int i = 0; i < V; ++i) sum += val[m][i];
+            }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        const float mean = sum / (float)N;
+        float ss = 0.f;
+#pragma unroll
+        for (int m = 0; m < MAXV; ++m) {
+            const int vi = lane + m * 32;
+            if (vi < nv) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) { const float d = val[m][i] - mean; ss = fmaf(d, d, ss); }
+            }
+        }
+#pragma unroll
+        for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        const float rstd = rsqrtf(ss / (float)N + eps);
+#pragma unroll
+        for (int m = 0; m < MAXV; ++m) {
+            const int vi = lane + m * 32;
+            if (vi < nv) {
+                Vec16<T> wv, bv; wv.load_nc(w + vi * V); bv.load_nc(bias + vi * V);
+                float wf[V], bf[V]; wv.to_float(wf); bv.to_float(bf);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    float t = (val[m][i] - mean) * rstd * wf[i] + bf[i];
+                    if (act) t = __fdividef(t, 1.f + __expf(-t));
+                    val[m][i] = t;
+                }
+                Vec16<T> ov; ov.from_float(val[m]); ov.store(y + r * N + vi * V);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(EW_THREADS) swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ yy,
                                                             T* __restrict__ out, int64_t rows, int I, int64_t ld_in, int64_t ld_out) {
     constexpr int V = DType<T>::VEC;
-    const int iv = I / V;
-    const int64_t total = rows * iv;
-    for (int64_t it = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t iv = I / V;
+    const uint32_t total = (uint32_t)rows * iv;
+    for (uint32_t it = blockIdx.x * blockDim.x + threadIdx.x; it < total; it += gridDim.x * blockDim.x) {
         const int64_t r = it / iv;
         const int c0 = (int)(it % iv) * V;
         Vec16<T> gv, yv;
@@ -171,7 +231,7 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_kernel(const T* __restrict_
         float gf[V], yf[V];
         gv.to_float(gf); yv.to_float(yf);
 #pragma unroll
-        for (int i = 0; i < V; ++i) gf[i] = gf[i] * yf[i] / (1.f + __expf(-gf[i]));
+        for (int i = 0; i < V; ++i) gf[i] = __fdividef(gf[i] * yf[i], 1.f + __expf(-gf[i]));
         Vec16<T> ov; ov.from_float(gf); ov.store(out + r * ld_out + c0);
     }
 }
@@ -189,6 +249,7 @@ int dwconv_t(const void* x, const void* wt, const void* bias, void* y, int B, in
     constexpr int V = DType<T>::VEC;
     if (C % V) return VIG_ERR_SHAPE;
     const int64_t items = (int64_t)B * h * w * (C / V);
+    if (items >= (1ll << 31)) return VIG_ERR_SHAPE;                             // 32-bit index arithmetic in the kernel
     dwconv3x3_kernel<T><<<grid_for(items, EW_THREADS), EW_THREADS, 0, s>>>((const T*)x, (const T*)wt, (const T*)bias, (T*)y, B, h, w, C, act);
     return (int)cudaGetLastError();
 }
@@ -200,6 +261,7 @@ int gate_inject_t(const void* o, const int64_t* so, const void* local, const voi
     const int lpg = dv / V;
     if (dv % V || (so[0] % V) || (so[1] % V) || (so[2] % V) || (ld_local % V) || (ld_gate % V) || (ld_y % V)) return VIG_ERR_ALIGN;
     const int64_t threads = (int64_t)B * L * H * lpg;
+    if (threads >= (1ll << 31)) return VIG_ERR_SHAPE;                           // 32-bit index arithmetic in the kernel
     const int grid = grid_for(threads, EW_THREADS);
 #define VIG_GI(LPG) case LPG: gate_inject_kernel<T, LPG><<<grid, EW_THREADS, 0, s>>>((const T*)o, so[0], so[1], so[2], (const T*)local, \
         (const T*)gl, (const T*)wg, (const T*)wl, (T*)y, ld_local, ld_gate, ld_y, B, H, L, eps, out_act); break;
@@ -222,9 +284,23 @@ int add_rmsnorm_t(const void* x, const void* res, const void* w, void* y, void* 
 }
 
 template <typename T>
+int layernorm_act_t(const void* x, const void* w, const void* b, void* y, int64_t rows, int N, float eps, int act, cudaStream_t s) {
+    constexpr int V = DType<T>::VEC;
+    if (N % V) return VIG_ERR_SHAPE;
+    const int nv = N / V;
+    const int grid = grid_for(rows * 32, EW_THREADS);
+#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act)
+    if (nv <= 32) VIG_LN(1); else if (nv <= 64) VIG_LN(2); else if (nv <= 128) VIG_LN(4);
+    else if (nv <= 256) VIG_LN(8); else return VIG_ERR_SHAPE;
+#undef VIG_LN
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
 int swiglu_t(const void* g, const void* yy, void* out, int64_t rows, int I, int64_t ld_in, int64_t ld_out, cudaStream_t s) {
     constexpr int V = DType<T>::VEC;
     if (I % V || ld_in % V || ld_out % V) return VIG_ERR_ALIGN;
+    if (rows * (I / V) >= (1ll << 31)) return VIG_ERR_SHAPE;                     // 32-bit index arithmetic in the kernel
     swiglu_kernel<T><<<grid_for(rows * (I / V), EW_THREADS), EW_THREADS, 0, s>>>((const T*)g, (const T*)yy, (T*)out, rows, I, ld_in, ld_out);
     return (int)cudaGetLastError();
 }
@@ -274,6 +350,15 @@ extern "C" int vig_add_rmsnorm_fwd(const void* x, const void* residual, const vo
     if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (residual && !aligned16(residual)) || (residual_out && !aligned16(residual_out)))
         return VIG_ERR_ALIGN;
     VIG_DISPATCH(dtype, add_rmsnorm_t<T>(x, residual, w, y, residual_out, rows, N, eps, (cudaStream_t)stream))
+}
+
+extern "C" int vig_layernorm_act_fwd(const void* x, const void* w, const void* bias, void* y, int64_t rows, int N, float eps,
+                                    int act_swish, int dtype, void* stream) {
+    if (!x || !w || !bias || !y) return VIG_ERR_NULL;
+    if (rows < 0 || N <= 0) return VIG_ERR_SHAPE;
+    if (rows == 0) return VIG_OK;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y)) return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, w, bias, y, rows, N, eps, act_swish, (cudaStream_t)stream))
 }
 
 extern "C" int vig_swiglu_fwd(const void* gate, const void* y, void* out, int64_t rows, int I, int64_t ld_in, int64_t ld_out,

@@ -83,7 +83,8 @@ class GatedLinearAttention(nn.Module):
         heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)           # [B,H,L,d] views, no copy
         q, k, v = heads(z[..., :kd], dk), heads(z[..., kd:2 * kd], dk), heads(z[..., 2 * kd:2 * kd + vd], dv)
         gate_logits = z[..., 2 * kd + vd:2 * kd + 2 * vd]
-        gk = self.gk_proj[1](z[..., 2 * kd + 2 * vd:])                               # raw gate logits [B,L,2*kd]
+        # raw gate logits [B,L,2*kd]: bias and the strided low-rank slice go straight into one GEMM call
+        gk = torch.addmm(self.gk_proj[1].bias, z.view(B * L, -1)[:, 2 * kd + 2 * vd:], self.gk_proj[1].weight.t()).view(B, L, 2 * kd)
         g_fwd, g_bwd = heads(gk[..., :kd], dk), heads(gk[..., kd:], dk)
         o = torch.empty(B, L, H, dv, dtype=x.dtype, device=x.device).permute(0, 2, 1, 3)
         # reference: (o_f + o_b) / 2 in the operator wrapper, / 2 again in the eval branch (vig.py:443)

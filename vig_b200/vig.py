@@ -20,21 +20,61 @@ class LayerNorm2d(nn.LayerNorm):
 
 
 class V2PatchEmbed(nn.Module):
-    """``vig.py:625-672``: conv k(p/2+1) s(p/2) p1 -> LN2d -> swish -> conv k3 s2 p1 -> LN2d."""
+    """``vig.py:625-672``: conv k(p/2+1) s(p/2) p1 -> LN2d -> swish -> conv k3 s2 p1 -> LN2d.
+
+    Same parameters as the reference; the forward keeps activations channels-last so both LayerNorm2d stages
+    run as this library's fused LayerNorm(+swish) kernel on contiguous rows, and evaluates the first
+    convolution (kernel s+1, stride s, 3 input channels -- a shape cuDNN serves without tensor cores) as a
+    2x2 convolution over s x s pixel blocks (space-to-depth), which is the same sum with zero weights at the
+    taps the original kernel does not have.
+    """
 
     def __init__(self, img_size=224, patch_size=16, in_chans=3, embed_dim=768, use_bias_in_patch=True):
         super().__init__()
         stride = patch_size // 2
+        self.stride = stride
         self.proj = nn.Sequential(
             nn.Conv2d(in_chans, embed_dim // 2, kernel_size=stride + 1, stride=stride, padding=1, bias=use_bias_in_patch),
             LayerNorm2d(embed_dim // 2), nn.SiLU(),
             nn.Conv2d(embed_dim // 2, embed_dim, kernel_size=3, stride=2, padding=1, bias=use_bias_in_patch),
             LayerNorm2d(embed_dim))
         self.num_patches = (img_size // patch_size) ** 2
+        self._w_blocks = None
+
+    def _block_weight(self):
+        """[O, s*s*Cin, 2, 2] weight of the space-to-depth form, channels-last, cached per parameter version."""
+        w = self.proj[0].weight
+        key = (w.dtype, w.device, w._version)
+        if self._w_blocks is None or self._w_blocks[0] != key:
+            s = self.stride
+            O, Cin = w.shape[0], w.shape[1]
+            big = w.new_zeros(O, Cin, 2 * s, 2 * s)
+            big[:, :, :s + 1, :s + 1] = w.detach()
+            # (O, Cin, cy, dy, cx, dx) -> (O, dy, dx, Cin, cy, cx) -> (O, s*s*Cin, 2, 2)
+            wb = big.view(O, Cin, 2, s, 2, s).permute(0, 3, 5, 1, 2, 4).reshape(O, s * s * Cin, 2, 2)
+            self._w_blocks = (key, wb.contiguous(memory_format=torch.channels_last))
+        return self._w_blocks[1]
+
+    def _conv1(self, x):
+        conv = self.proj[0]
+        s = self.stride
+        B, Cin, H, W = x.shape
+        if H % s or W % s or Cin * s * s % 8:
+            return conv(x.contiguous(memory_format=torch.channels_last))
+        # pad one pixel before (the conv's padding) and s-1 after, then fold s x s pixels into channels
+        xp = F.pad(x.permute(0, 2, 3, 1), (0, 0, 1, s - 1, 1, s - 1))                     # [B, H+s, W+s, Cin]
+        cells = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
+        return F.conv2d(cells.permute(0, 3, 1, 2), self._block_weight(), conv.bias)
 
     def forward(self, x):
-        x = self.proj(x)
-        return x.flatten(2).transpose(1, 2).contiguous(), (x.shape[2], x.shape[3])
+        from . import ops
+        ln1, ln2, conv2 = self.proj[1], self.proj[4], self.proj[3]
+        y = self._conv1(x)                                                # logical NCHW, channels-last memory
+        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=True)
+        y = conv2(y.permute(0, 3, 1, 2))
+        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln2.weight, ln2.bias, ln2.eps, act_swish=False)
+        B, h, w, C = y.shape
+        return y.view(B, h * w, C), (h, w)
 
 
 def resize_pos_embed(pos_embed, src_shape, dst_shape, mode="bicubic"):
@@ -64,6 +104,14 @@ class ViG(nn.Module):
         self.blocks = nn.ModuleList([GLABlock(self.config, i) for i in range(depth)])
         self.norm = RMSNorm(embed_dim, eps=rms_norm_eps)
         self._pos_cache = {}
+
+    def _apply(self, fn, *args, **kwargs):
+        # keep the stem's conv weights in channels_last after every .to() / .cuda() / .bfloat16()
+        super()._apply(fn, *args, **kwargs)
+        for m in self.patch_embed.proj:
+            if isinstance(m, nn.Conv2d):
+                m.weight.data = m.weight.data.contiguous(memory_format=torch.channels_last)
+        return self
 
     @classmethod
     def from_shape(cls, shape, **kw):
