@@ -161,12 +161,13 @@ VIG_API int vig_add_rmsnorm_fwd(const void* x, const void* residual, const void*
 
 /*
  * LayerNorm over the last dimension with weight and bias, optional swish on the result:
- * y = swish?((x - mean) * rsqrt(var + eps) * w + b).  Replaces `LayerNorm2d` (+ the swish that follows the
+ * y = swish?((x' - mean) * rsqrt(var + eps) * w + b) with x' = x + pre_bias (pre_bias: optional [N] vector, the
+ * bias of the convolution that produced x, rounded to the tensor dtype like the convolution would).  Replaces `LayerNorm2d` (+ the swish that follows the
  * first one) of the patch-embedding stem (classification/models/vig.py:619-624, 650-656) on channels-last
  * activations viewed as [rows = B*h*w, N = channels].  x, y contiguous; N * element size a multiple of 16.
  */
-VIG_API int vig_layernorm_act_fwd(const void* x, const void* w, const void* bias, void* y, int64_t rows, int N,
-                          float eps, int act_swish, int dtype, void* stream);
+VIG_API int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, void* y,
+                          int64_t rows, int N, float eps, int act_swish, int dtype, void* stream);
 
 /*
  * SwiGLU: out = gate * sigmoid(gate) * y (fla/modules/activations.py:109-113, the `swiglu` half of

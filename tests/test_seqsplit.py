@@ -1,0 +1,90 @@
+"""Sequence-split bi-GLA: the fold of per-slice summaries reproduces the unsplit scan.
+CPU: real ranks over gloo with the oracle standing in for the CUDA operator (host logic + collective).
+GPU: the slices of P emulated ranks run one after the other on one device through the C ABI."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from conftest import rel_err
+from vig_b200 import seqsplit
+
+
+def _oracle_summary(q, k, v, gf, gb, **kw):
+    _, s_f, s_b = oracle.naive_bi_gla(q, k, v, gf, gb, return_states=True)
+    return seqsplit.pack_summary(s_f, gf.float().sum(2), s_b, gb.float().sum(2))
+
+
+def _oracle_scan(q, k, v, gf, gb, init_f, init_b, **kw):
+    return oracle.naive_bi_gla(q, k, v, gf, gb, init_fwd=init_f, init_bwd=init_b, out_scale=kw.get("out_scale", 1.0))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, L, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ins = oracle.make_bigla_inputs(1, 2, L, 32, 64, seed=12)
+        per = L // world
+        sl = [t[:, :, rank * per:(rank + 1) * per if rank < world - 1 else L] for t in ins]
+        o = seqsplit.bi_gla_sequence_parallel(*sl, summary_fn=_oracle_summary, scan_fn=_oracle_scan, out_scale=0.5)
+        ret[rank] = o
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_split_over_gloo_matches_unsplit_oracle(world):
+    L = 101
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), L, ret), nprocs=world, join=True)
+    ref = oracle.naive_bi_gla(*oracle.make_bigla_inputs(1, 2, L, 32, 64, seed=12), out_scale=0.5)
+    got = torch.cat([ret[r] for r in range(world)], dim=2)
+    assert rel_err(got, ref) < 1e-5
+
+
+def test_fold_with_outer_initial_states():
+    ins = oracle.make_bigla_inputs(1, 1, 60, 32, 64, seed=3)
+    g = torch.Generator().manual_seed(1)
+    i_f, i_b = torch.randn(1, 1, 32, 64, generator=g), torch.randn(1, 1, 32, 64, generator=g)
+    ref = oracle.naive_bi_gla(*ins, init_fwd=i_f, init_bwd=i_b)
+    cuts = [0, 13, 40, 60]
+    slices = [[t[:, :, a:b] for t in ins] for a, b in zip(cuts[:-1], cuts[1:])]
+    summaries = [_oracle_summary(*s) for s in slices]
+    outs = []
+    for r, s in enumerate(slices):
+        s_f, s_b = seqsplit.fold(summaries, r, 32, 64, init_fwd=i_f, init_bwd=i_b)
+        outs.append(_oracle_scan(*s, s_f, s_b))
+    assert rel_err(torch.cat(outs, 2), ref) < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,P,L", [(torch.float32, 4, 1000), (torch.bfloat16, 4, 4096), (torch.bfloat16, 8, 16384)])
+def test_sequence_split_on_gpu_matches_unsplit(dtype, P, L):
+    import vig_b200
+    B, H, dk, dv = 1, 2, 64, 64
+    ins = [t.to("cuda", dtype) for t in oracle.make_bigla_inputs(B, H, L, dk, dv, seed=8)]
+    whole = vig_b200.bi_gla(*ins, out_scale=0.5)
+    per = (L + P - 1) // P
+    slices = [[t[:, :, r * per:min(L, (r + 1) * per)] for t in ins] for r in range(P)]
+    summaries = [seqsplit.cuda_summary(*s) for s in slices]          # what each rank would all-gather
+    outs = []
+    for r, s in enumerate(slices):
+        s_f, s_b = seqsplit.fold(summaries, r, dk, dv)
+        outs.append(seqsplit.cuda_scan(*s, s_f, s_b, out_scale=0.5))
+    got = torch.cat(outs, 2)
+    tol = 1e-4 if dtype == torch.float32 else 1e-3 * 8          # split == unsplit up to bf16 rounding of boundary states
+    assert rel_err(got.float(), whole.float()) < tol
+    if L <= 4096:
+        ref = oracle.naive_bi_gla(*[t.float().cpu() for t in ins], out_scale=0.5)
+        assert rel_err(got.float(), ref) < (1e-4 if dtype == torch.float32 else 2e-2)

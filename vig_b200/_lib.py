@@ -28,7 +28,7 @@ _SIGNATURES = {
     "vig_dwconv3x3_fwd": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_void_p]),
     "vig_gate_inject_fwd": (c_int, [c_void_p, _P64] + [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_float, c_int, c_int, c_void_p]),
     "vig_add_rmsnorm_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_void_p]),
-    "vig_layernorm_act_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_float, c_int, c_int, c_void_p]),
+    "vig_layernorm_act_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_int, c_void_p]),
     "vig_swiglu_fwd": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_int64, c_int64, c_int, c_void_p]),
 }
 EXPORTS = tuple(_SIGNATURES)

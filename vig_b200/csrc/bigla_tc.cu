@@ -40,17 +40,17 @@ constexpr uint32_t TM_P0 = 0, TM_P1 = 64, TM_U = 64, TM_O = 128, TM_COLS = 256;
 
 // shared memory map (bytes from a 1024-aligned base); ~108 KB so that two CTAs fit in one SM
 constexpr int TILE_B = CHUNK * 64 * 2;                       // 16 KB: 128 rows x 128 B
-constexpr int OFF_RQ = 0;                                    // raw q tile; later the P tile of key columns 64..127
+constexpr int OFF_RQ = 0;                                    // raw q tile; later the P tile of key columns 0..63
 constexpr int OFF_RK = OFF_RQ + TILE_B;                      // raw k tile
-constexpr int OFF_RG = OFF_RK + TILE_B;                      // raw gate tile; later the P tile of key columns 0..63
+constexpr int OFF_RG = OFF_RK + TILE_B;                      // raw gate tile
 constexpr int OFF_V = OFF_RG + TILE_B;                       // v tile (128-byte swizzle, MMA operand as loaded)
-constexpr int OFF_QT = OFF_V + TILE_B;
+constexpr int OFF_QT = OFF_V + TILE_B;                       // scaled q operand; later the P tile of key columns 64..127
 constexpr int OFF_KT = OFF_QT + TILE_B;
 constexpr int OFF_ST = OFF_KT + TILE_B;                      // bf16 state operand, 64 rows x 128 B
 constexpr int OFF_PART = OFF_ST + 64 * 128;                  // fp32 [16][64] group sums of log-gates
 constexpr int OFF_VEC = OFF_PART + 16 * 64 * 4;              // fp32 [2][64]: exp(G_last), exp(G_last - G_ref)
 constexpr int OFF_GTOT = OFF_VEC + 2 * 64 * 4;               // fp32 [64] summed log-gates of the segment
-constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: full, p0, p1, o
+constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: gk, q, v, p, o
 constexpr int OFF_MISC = OFF_BAR + 8 * 8;                    // tmem base, abort flag
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;             // + slack for the manual 1024-byte alignment
 
@@ -81,10 +81,18 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+// Low word: start address (bits 0-13, in 16-byte units) and leading byte offset 1 (bits 16-29; unused for one
+// 128-byte atom column).  High word: stride byte offset 1024 >> 4 (bits 32-45), descriptor version 1 (bit 46),
+// SWIZZLE_128B (bits 61-63).
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t make_desc(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+// a_lo / b_lo: low words of the shared-memory descriptors (see make_desc_lo); the high word is the same constant
+// for every tile of this kernel, so an MMA costs one integer add per operand to set up.
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI) : "memory");
 }
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base lane + i)
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
@@ -100,15 +108,6 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
 
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (both for K-major
 // tiles with 128-byte rows along K and for MN-major tiles with 128-byte rows along M/N).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);           // start address
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for one 128-byte atom column)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
-    return d;
-}
 // Instruction descriptor: fp32 accumulate, A/B format (0 fp16, 1 bf16), major-ness (0 K, 1 MN), N, M.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t a_mn, uint32_t b_mn, uint32_t M, uint32_t N) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
@@ -172,18 +171,17 @@ __device__ __forceinline__ float lg2(float x) { float y; asm("lg2.approx.ftz.f32
 constexpr float MAX_EXPONENT2 = MAX_EXPONENT * LOG2E;   // the exponent bound in log2 units
 
 // Log-gate in LOG2 units.  From a raw logit: logsigmoid(x) = min(x,0) - log(1 + exp(-|x|)), here with y = x log2(e):
-// min(y,0) - log2(1 + 2^-|y|), times 1/normalizer.  From a log-gate: x log2(e).  clamp_lo is -inf when unused.
-__device__ __forceinline__ float fast_gate2(float x, bool raw_logits, float inv_norm, float clamp_lo) {
+// min(y,0) - log2(1 + 2^-|y|), times 1/normalizer.  From a log-gate: x log2(e).
+__device__ __forceinline__ float fast_gate2(float x, bool raw_logits, float inv_norm) {
     const float y = x * LOG2E;
-    float g = y;
-    if (raw_logits) g = (fminf(y, 0.f) - lg2(1.f + ex2(-fabsf(y)))) * inv_norm;
-    return fmaxf(g, clamp_lo);
+    return raw_logits ? (fminf(y, 0.f) - lg2(1.f + ex2(-fabsf(y)))) * inv_norm : y;
 }
 
 template <int DK, typename T, bool STATES_ONLY>
 __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_constant__ TcMaps maps, BiglaParams p, int use_ws) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // align by an integer offset (not by casting through an integer) so that accesses stay shared-space loads
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seg = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
@@ -191,7 +189,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const int nch = min(SEG_CHUNKS, (p.L - seg_t0 + CHUNK - 1) / CHUNK);
     const int nseg = gridDim.x;
 
-    const uint32_t bar_full = sbase + OFF_BAR, bar_p0 = bar_full + 8, bar_p1 = bar_full + 16, bar_o = bar_full + 24;
+    const uint32_t bar_gk = sbase + OFF_BAR, bar_q = bar_gk + 8, bar_v = bar_gk + 16, bar_p0 = bar_gk + 24, bar_o = bar_gk + 32;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
     float* part = reinterpret_cast<float*>(smem + OFF_PART);
@@ -200,7 +198,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const Waiter waiter{abort_flag, p.status};
 
     if (tid == 0) {
-        mbar_init(bar_full, 1); mbar_init(bar_p0, 1); mbar_init(bar_p1, 1); mbar_init(bar_o, 1);
+        mbar_init(bar_gk, 1); mbar_init(bar_q, 1); mbar_init(bar_v, 1); mbar_init(bar_p0, 1); mbar_init(bar_o, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -232,25 +230,36 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const float lq = __log2f(fabsf(p.qscale));   // |scale * out_scale| folded into the exponent of the q operand
     const float o_sign = p.qscale < 0.f ? -1.f : 1.f;
 
-    constexpr uint32_t IDESC_QK = make_idesc(Pack2<T>::FMT, 0, 0, 128, 64);
+    constexpr uint32_t IDESC_QK = make_idesc(Pack2<T>::FMT, 0, 0, 128, 128);
     constexpr uint32_t IDESC_OV = make_idesc(Pack2<T>::FMT, 0, 1, 128, 64);
     constexpr uint32_t IDESC_U = make_idesc(Pack2<T>::FMT, 1, 1, 64, 64);
-    constexpr uint32_t TX_BYTES = (STATES_ONLY ? 2 : 3) * CHUNK * DK * 2 + CHUNK * DV * 2;
 
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, dir_last = (p.dir_mask & 2) ? 1 : 0;
     const int n_iter = (dir_last - dir_first + 1) * nch;      // iterations: sweeps x chunks
 
-    auto issue_loads = [&](int n) {         // thread 0 only: tiles of iteration n
+    // Tiles of iteration n (thread 0 only).  Three groups with their own barriers, because their buffers become
+    // free at different times: k and the gates right after the operand tiles are written, q and v only when
+    // the MMAs of the iteration are done (the q buffer is reused for scores, v is an MMA operand).
+    auto chunk_t0 = [&](int n) {
         const int dir = dir_first + n / nch, ci = n % nch;
-        const int c = dir ? nch - 1 - ci : ci;
-        const int t0 = seg_t0 + c * CHUNK;
-        mbar_expect_tx(bar_full, TX_BYTES);
-        if (!STATES_ONLY) tma_load_4d(sbase + OFF_RQ, &maps.q, 0, t0, h, b, bar_full);
-        tma_load_4d(sbase + OFF_RK, &maps.k, 0, t0, h, b, bar_full);
-        tma_load_4d(sbase + OFF_RG, dir ? &maps.gb : &maps.gf, 0, t0, h, b, bar_full);
-        tma_load_4d(sbase + OFF_V, &maps.v, 0, t0, h, b, bar_full);
+        return seg_t0 + (dir ? nch - 1 - ci : ci) * CHUNK;
     };
-    if (tid == 0) issue_loads(0);
+    auto issue_gk = [&](int n) {
+        const int dir = dir_first + n / nch, t0 = chunk_t0(n);
+        mbar_expect_tx(bar_gk, 2 * CHUNK * DK * 2);
+        tma_load_4d(sbase + OFF_RK, &maps.k, 0, t0, h, b, bar_gk);
+        tma_load_4d(sbase + OFF_RG, dir ? &maps.gb : &maps.gf, 0, t0, h, b, bar_gk);
+    };
+    auto issue_qv = [&](int n) {
+        const int t0 = chunk_t0(n);
+        if (!STATES_ONLY) {
+            mbar_expect_tx(bar_q, CHUNK * DK * 2);
+            tma_load_4d(sbase + OFF_RQ, &maps.q, 0, t0, h, b, bar_q);
+        }
+        mbar_expect_tx(bar_v, CHUNK * DV * 2);
+        tma_load_4d(sbase + OFF_V, &maps.v, 0, t0, h, b, bar_v);
+    };
+    if (tid == 0) { issue_gk(0); issue_qv(0); }
 
     float S[32];                                  // my 32 columns of state row st_row (state threads only)
     const uint32_t* sq = reinterpret_cast<const uint32_t*>(smem + OFF_RQ);
@@ -279,7 +288,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             if (tid < DK) gtot[tid] = 0.f;
         }
         TC_STAMP(0);
-        if (warp == 0) waiter.wait(bar_full, par);            // one warp polls; the others sleep in the barrier
+        if (warp == 0) waiter.wait(bar_gk, par);              // one warp polls; the others sleep in the barrier
         __syncthreads();
         TC_STAMP(1);
 
@@ -287,8 +296,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         // Instantiated per direction so that token indices, and with them the swizzled addresses, are static.
         float2 gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
         bool out_of_range = false;
-        auto phase1 = [&](auto dir_c) {
+        // PLAIN: full chunk and no lower clamp of the gates -- the common case skips the padding select and the clamp.
+        const bool plain = !(p.clamp_min == p.clamp_min) && (p.L - t0 >= CHUNK);
+        auto phase1 = [&](auto dir_c, auto plain_c) {
             constexpr int DIR = decltype(dir_c)::value;
+            constexpr bool PLAIN = decltype(plain_c)::value != 0;
             const int n_valid = p.L - t0;                             // rows at or past it are padding: decay 1
             float2 gl[TPG];
             float2 run = make_float2(0.f, 0.f);
@@ -296,14 +308,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             for (int u = 0; u < TPG; ++u) {                           // u runs in scan order inside the group
                 const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
                 float2 g = Pack2<T>::unpack(sg[tok * CPW + cp]);
-                g.x = fast_gate2(g.x, raw_logits, inv_norm, clamp_lo);
-                g.y = fast_gate2(g.y, raw_logits, inv_norm, clamp_lo);
-                if (tok >= n_valid) g = make_float2(0.f, 0.f);
+                g.x = fast_gate2(g.x, raw_logits, inv_norm);
+                g.y = fast_gate2(g.y, raw_logits, inv_norm);
+                if (!PLAIN) {
+                    g.x = fmaxf(g.x, clamp_lo); g.y = fmaxf(g.y, clamp_lo);
+                    if (tok >= n_valid) g = make_float2(0.f, 0.f);
+                }
                 run.x += g.x; run.y += g.y;
                 gl[u] = run;                                          // inclusive cumulative sum
             }
             reinterpret_cast<float2*>(part)[grp * CPW + cp] = run;
-            __syncthreads();
+            if (!STATES_ONLY && warp == 0) waiter.wait(bar_q, par);   // q is first read after the barrier below
+            // If no group of the chunk decays by more than MAX/NG, no exponent below can leave +-MAX and the
+            // clamps are skipped for the whole CTA (the vote doubles as the barrier that publishes `part`).
+            const int risky = __syncthreads_or(fmaxf(fabsf(run.x), fabsf(run.y)) > MAX_EXPONENT2 / NG);
             float2 off = make_float2(0.f, 0.f);
 #pragma unroll
             for (int g2 = 0; g2 < NG; ++g2) {
@@ -315,23 +333,34 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 glast.x += s2.x; glast.y += s2.y;
             }
             off.x -= gref.x; off.y -= gref.y;
-            // gates are <= 0, so the cumulative sums are monotone and the extreme exponents sit at the chunk ends
-            out_of_range = fmaxf(fmaxf(-gref.x, -gref.y), fmaxf(gref.x - glast.x, gref.y - glast.y)) > MAX_EXPONENT2;
+            auto scale_tiles = [&](auto clamp_c) {
+                constexpr bool CLAMP = decltype(clamp_c)::value != 0;
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) {
-                const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
-                const float ex = fminf(fmaxf(off.x + gl[u].x, -MAX_EXPONENT2), MAX_EXPONENT2);
-                const float ey = fminf(fmaxf(off.y + gl[u].y, -MAX_EXPONENT2), MAX_EXPONENT2);
-                const uint32_t o = swz(tok, cp * 4);
-                const float2 kk = Pack2<T>::unpack(sk[tok * CPW + cp]);
-                *reinterpret_cast<uint32_t*>(smem + OFF_KT + o) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
-                if (!STATES_ONLY) {
-                    const float2 qq = Pack2<T>::unpack(sq[tok * CPW + cp]);
-                    *reinterpret_cast<uint32_t*>(smem + OFF_QT + o) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                for (int u = 0; u < TPG; ++u) {
+                    const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
+                    float ex = off.x + gl[u].x, ey = off.y + gl[u].y;
+                    if (CLAMP) {
+                        out_of_range |= fmaxf(fabsf(ex), fabsf(ey)) > MAX_EXPONENT2;
+                        ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
+                        ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
+                    }
+                    const uint32_t o = swz(tok, cp * 4);
+                    const float2 kk = Pack2<T>::unpack(sk[tok * CPW + cp]);
+                    *reinterpret_cast<uint32_t*>(smem + OFF_KT + o) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                    if (!STATES_ONLY) {
+                        const float2 qq = Pack2<T>::unpack(sq[tok * CPW + cp]);
+                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + o) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                    }
                 }
-            }
+            };
+            if (risky) scale_tiles(std::integral_constant<int, 1>{}); else scale_tiles(std::integral_constant<int, 0>{});
         };
-        if (dir) phase1(std::integral_constant<int, 1>{}); else phase1(std::integral_constant<int, 0>{});
+        {
+            using I0 = std::integral_constant<int, 0>;
+            using I1 = std::integral_constant<int, 1>;
+            if (dir) { if (plain) phase1(I1{}, I1{}); else phase1(I1{}, I0{}); }
+            else     { if (plain) phase1(I0{}, I1{}); else phase1(I0{}, I0{}); }
+        }
         TC_STAMP(2);
         if (out_of_range && p.status) atomicOr(p.status, 2);
         if (grp == 0) {
@@ -356,36 +385,33 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();                          // raw q / k / gate tiles are dead from here on
+        if (tid == 0 && n + 1 < n_iter) issue_gk(n + 1);
         TC_STAMP(3);
 
         const uint32_t kt = sbase + OFF_KT, v_addr = sbase + OFF_V;
         if (!STATES_ONLY) {
-            // ---- MMA issue 1: scores in two halves of 64 key columns, inter-chunk product ----------------
+            // ---- MMA issue 1: inter-chunk product, then the 128x128 scores ---------------------------------
             if (tid == 0) {
                 tc_fence_after();
                 const uint32_t qt = sbase + OFF_QT, st = sbase + OFF_ST;
-#pragma unroll
-                for (int k4 = 0; k4 < DK / 16; ++k4)
-                    tc_mma(tmem + TM_P0, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
-                tc_commit(bar_p0);
-#pragma unroll
-                for (int k4 = 0; k4 < DK / 16; ++k4)
-                    tc_mma(tmem + TM_P1, make_desc(qt + k4 * 32), make_desc(kt + 64 * 128 + k4 * 32), IDESC_QK, k4 > 0);
-                tc_commit(bar_p1);
                 const bool first_touch = dir == dir_first;            // the chunk's accumulator has no content yet
 #pragma unroll
                 for (int k4 = 0; k4 < DK / 16; ++k4)
                     tc_mma(tmem + TM_O + c * 64, make_desc(qt + k4 * 32), make_desc(st + k4 * 2048), IDESC_OV, !(first_touch && k4 == 0));
+#pragma unroll
+                for (int k4 = 0; k4 < DK / 16; ++k4)      // all 128 key columns at once: TM_P0 and TM_P1 are adjacent
+                    tc_mma(tmem + TM_P0, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
+                tc_commit(bar_p0);                        // MMAs complete in order: both readers of the scaled q tile are done
             }
             __syncwarp();
             TC_STAMP(4);
-            // ---- scores -> masked bf16 P tiles (warps 0-3: keys 0..63 over the dead gate tile,
-            //      warps 4-7: keys 64..127 over the dead q tile) ----------------------------------------
+            // ---- scores -> masked bf16 P tiles (warps 0-3: keys 0..63 over the dead raw q tile,
+            //      warps 4-7: keys 64..127 over the dead scaled q tile) ---------------------------------
             const int half = warp >> 2;
             const int quad = warp & 3;                                // my 32 query rows: 32*quad .. 32*quad+31
             const int row = 32 * quad + lane;                         // query token inside the chunk
-            uint8_t* ptile = smem + (half ? OFF_RQ : OFF_RG);
-            if ((warp & 3) == 0) waiter.wait(half ? bar_p1 : bar_p0, par);
+            uint8_t* ptile = smem + (half ? OFF_QT : OFF_RQ);         // both tiles are dead once the score MMA is done
+            if ((warp & 3) == 0) waiter.wait(bar_p0, par);
             half_bar_sync(half);
             TC_STAMP(5);
             tc_fence_after();
@@ -428,11 +454,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         }
         // ---- MMA issue 2: P V into the output accumulator, state update into the second score buffer ----
         if (tid == 0) {
+            waiter.wait(bar_v, par);              // only the tensor core reads v, so only the issuing thread waits for it
             tc_fence_after();
             if (!STATES_ONLY) {
 #pragma unroll
                 for (int k8 = 0; k8 < CHUNK / 16; ++k8)
-                    tc_mma(tmem + TM_O + c * 64, make_desc(sbase + (k8 < 4 ? OFF_RG : OFF_RQ) + (k8 & 3) * 32),
+                    tc_mma(tmem + TM_O + c * 64, make_desc(sbase + (k8 < 4 ? OFF_RQ : OFF_QT) + (k8 & 3) * 32),
                            make_desc(v_addr + k8 * 2048), IDESC_OV, 1);
             }
 #pragma unroll
@@ -446,7 +473,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         // ---- state update in registers ---------------------------------------------------------------
         if (warp == 0) {
             waiter.wait(bar_o, par);              // all MMAs of the iteration are done: every tile is free again
-            if (tid == 0 && n + 1 < n_iter) issue_loads(n + 1);
+            if (tid == 0 && n + 1 < n_iter) issue_qv(n + 1);
         }
         __syncthreads();
         TC_STAMP(9);

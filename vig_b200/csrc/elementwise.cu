@@ -162,9 +162,9 @@ __global__ void __launch_bounds__(EW_THREADS) add_rmsnorm_kernel(const T* __rest
 // LayerNorm over the last dimension with affine parameters and an optional swish: the two LayerNorm2d
 // stages of the patch-embedding stem on channels-last activations.  One warp per row, row in registers.
 template <typename T, int MAXV>
-__global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                                                   const T* __restrict__ bias, T* __restrict__ y,
-                                                                   int64_t rows, int N, float eps, int act) {
+__global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __restrict__ x, const T* __restrict__ pre_bias,
+                                                                   const T* __restrict__ w, const T* __restrict__ bias,
+                                                                   T* __restrict__ y, int64_t rows, int N, float eps, int act) {
     constexpr int V = DType<T>::VEC;
     const int lane = threadIdx.x & 31;
     const int nv = N / V;
@@ -178,6 +178,12 @@ __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __re
             const int vi = lane + m * 32;
             if (vi < nv) {
                 Vec16<T> xv; xv.load_nc(x + r * N + vi * V); xv.to_float(val[m]);
+                if (pre_bias) {                          // per-channel bias of the producing convolution, folded in here
+                    Vec16<T> pv; pv.load_nc(pre_bias + vi * V);
+                    float pf[V]; pv.to_float(pf);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[m][i] = DType<T>::to_f(DType<T>::from_f(val[m][i] + pf[i]));
+                }
 #pragma unroll
                 for (int i = 0; i < V; ++i) sum += val[m][i];
             }
@@ -284,12 +290,12 @@ int add_rmsnorm_t(const void* x, const void* res, const void* w, void* y, void* 
 }
 
 template <typename T>
-int layernorm_act_t(const void* x, const void* w, const void* b, void* y, int64_t rows, int N, float eps, int act, cudaStream_t s) {
+int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b, void* y, int64_t rows, int N, float eps, int act, cudaStream_t s) {
     constexpr int V = DType<T>::VEC;
     if (N % V) return VIG_ERR_SHAPE;
     const int nv = N / V;
     const int grid = grid_for(rows * 32, EW_THREADS);
-#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act)
+#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act)
     if (nv <= 32) VIG_LN(1); else if (nv <= 64) VIG_LN(2); else if (nv <= 128) VIG_LN(4);
     else if (nv <= 256) VIG_LN(8); else return VIG_ERR_SHAPE;
 #undef VIG_LN
@@ -352,13 +358,14 @@ extern "C" int vig_add_rmsnorm_fwd(const void* x, const void* residual, const vo
     VIG_DISPATCH(dtype, add_rmsnorm_t<T>(x, residual, w, y, residual_out, rows, N, eps, (cudaStream_t)stream))
 }
 
-extern "C" int vig_layernorm_act_fwd(const void* x, const void* w, const void* bias, void* y, int64_t rows, int N, float eps,
-                                    int act_swish, int dtype, void* stream) {
+extern "C" int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, void* y, int64_t rows,
+                                    int N, float eps, int act_swish, int dtype, void* stream) {
     if (!x || !w || !bias || !y) return VIG_ERR_NULL;
+    if (pre_bias && !aligned16(pre_bias)) return VIG_ERR_ALIGN;
     if (rows < 0 || N <= 0) return VIG_ERR_SHAPE;
     if (rows == 0) return VIG_OK;
     if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y)) return VIG_ERR_ALIGN;
-    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, w, bias, y, rows, N, eps, act_swish, (cudaStream_t)stream))
+    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, y, rows, N, eps, act_swish, (cudaStream_t)stream))
 }
 
 extern "C" int vig_swiglu_fwd(const void* gate, const void* y, void* out, int64_t rows, int I, int64_t ld_in, int64_t ld_out,

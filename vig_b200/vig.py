@@ -60,19 +60,22 @@ class V2PatchEmbed(nn.Module):
         s = self.stride
         B, Cin, H, W = x.shape
         if H % s or W % s or Cin * s * s % 8:
-            return conv(x.contiguous(memory_format=torch.channels_last))
+            return F.conv2d(x.contiguous(memory_format=torch.channels_last), conv.weight, None, conv.stride, conv.padding)
         # pad one pixel before (the conv's padding) and s-1 after, then fold s x s pixels into channels
         xp = F.pad(x.permute(0, 2, 3, 1), (0, 0, 1, s - 1, 1, s - 1))                     # [B, H+s, W+s, Cin]
         cells = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
-        return F.conv2d(cells.permute(0, 3, 1, 2), self._block_weight(), conv.bias)
+        return F.conv2d(cells.permute(0, 3, 1, 2), self._block_weight(), None)
 
     def forward(self, x):
         from . import ops
         ln1, ln2, conv2 = self.proj[1], self.proj[4], self.proj[3]
+        # the convolutions run without their bias; it is added inside the LayerNorm kernel that follows
         y = self._conv1(x)                                                # logical NCHW, channels-last memory
-        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=True)
-        y = conv2(y.permute(0, 3, 1, 2))
-        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln2.weight, ln2.bias, ln2.eps, act_swish=False)
+        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=True,
+                              pre_bias=self.proj[0].bias)
+        y = F.conv2d(y.permute(0, 3, 1, 2), conv2.weight, None, conv2.stride, conv2.padding)
+        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln2.weight, ln2.bias, ln2.eps, act_swish=False,
+                              pre_bias=conv2.bias)
         B, h, w, C = y.shape
         return y.view(B, h * w, C), (h, w)
 
