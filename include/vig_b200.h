@@ -110,7 +110,7 @@ VIG_API int vig_bigla_fwd(const void* q, const void* k, const void* v, const voi
  * every GPU that loads the library holds until the process exits.
  *
  * Limit: vig_bigla_workspace_bytes(B,H,L,dk,dv,dtype,impl) must not exceed VIG_NOALLOC_SCRATCH_BYTES,
- * else VIG_ERR_SCRATCH_LIMIT is returned and nothing is launched (sequences of at most one 512-token
+ * else VIG_ERR_SCRATCH_LIMIT is returned and nothing is launched (sequences of at most one 256-token
  * segment on the tensor-core path, or 64 tokens on the SIMT path, need no scratch at all).
  * The call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
  * The first call on each device looks up the array's device address (with that device current); make that
