@@ -47,7 +47,7 @@ __device__ __forceinline__ float log_sigmoid(float x) {
     return fminf(x, 0.f) - log1pf(__expf(-fabsf(x)));
 }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 // Parameter block of the bi-GLA launchers (host fills it from the C ABI arguments).
 struct BiglaParams {
