@@ -28,7 +28,11 @@ WORKLOADS = {
     "vig_t_1024": ("vig_t_dk64", 1024, 64),
     "vig_s_224": ("vig_s_dk64", 224, 128),
     "vig_t_224": ("vig_t_dk64", 224, 128),
+    # ViG-B at 2048x2048 (L = 16384): under torchrun the token sequence of every image is split across the ranks
+    # (boundary states + one conv halo row per block over NCCL); the batch is the same on every rank
+    "vig_b_2048_seq": ("vig_b_dk64", 2048, 8),
 }
+SEQ_SPLIT = {"vig_b_2048_seq"}
 
 
 def parse():
@@ -143,7 +147,9 @@ def workload_config(args, batch):
     preset, size, _ = WORKLOADS[args.workload]
     return {"workload": f"{args.workload}: ViG {preset} forward, {size}x{size} images, patch 16 (L={(size // 16) ** 2}), "
                         f"batch {batch} per GPU, 12 blocks, dk=dv=64",
-            "per_gpu_batch": batch, "image_size": size, "sharding": "images across GPUs, no collective",
+            "per_gpu_batch": batch, "image_size": size,
+            "sharding": ("token sequence across GPUs by image rows (all-gather of boundary states and conv halo rows per block)"
+                         if args.workload in SEQ_SPLIT else "images across GPUs, no collective"),
             "cache": "inputs and activations larger than L2 (126 MB)" if batch * 3 * size * size * 2 > 126e6 else "L2 flushed between steps"}
 
 
@@ -172,7 +178,8 @@ def main():
     model = vig_b200.ViG.from_shape(shape)
     model.load_state_dict(oracle.make_state_dict(shape, seed=0))
     model = model.to(dev, torch.bfloat16).eval()
-    host_images = oracle.make_images(min(batch, 8), size, seed=rank).to(torch.bfloat16)
+    seq_split = args.workload in SEQ_SPLIT and world > 1
+    host_images = oracle.make_images(min(batch, 8), size, seed=0 if args.workload in SEQ_SPLIT else rank).to(torch.bfloat16)
     host_images = host_images.repeat((batch + host_images.shape[0] - 1) // host_images.shape[0], 1, 1, 1)[:batch].contiguous().pin_memory()
     images = host_images.to(dev)
     host_logits = torch.empty(batch, shape.num_classes, dtype=torch.bfloat16).pin_memory()
@@ -207,11 +214,16 @@ def main():
         if hasattr(vig_b200, n):
             setattr(vig_b200, n, w)
 
+    from vig_b200 import seqsplit
+
+    def forward(x):
+        with torch.no_grad():
+            return seqsplit.vig_forward_sequence_parallel(model, x) if seq_split else model(x)
+
     def step():
         if flush is not None:
             flush.fill_(1)
-        with torch.no_grad():
-            return model(images)
+        return forward(images)
 
     def sync_all():
         torch.cuda.synchronize()
@@ -277,8 +289,7 @@ def main():
         if i + 1 < args.steps:
             upload(i + 1)
         main_stream.wait_event(uploaded[i % 2])
-        with torch.no_grad():
-            out = model(dbuf[i % 2])
+        out = forward(dbuf[i % 2])
         consumed[i % 2].record(main_stream)
         host_logits.copy_(out, non_blocking=True)
     f1.record()
@@ -314,11 +325,11 @@ def main():
                 "share_of_step": scan_ms * shape.depth / (ms / args.steps)}
 
     if rank == 0:
-        total_images = batch * world * args.steps
+        total_images = batch * (1 if args.workload in SEQ_SPLIT else world) * args.steps
         line = {"metric": "images_per_sec", "value": total_images / (ms * 1e-3), "unit": "images/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": workload_config(args, batch), "clocks": clocks, "gpu_launches": launches,
+                "scaling": "strong" if args.workload in SEQ_SPLIT else "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": workload_config(args, batch), "clocks": clocks, "gpu_launches": launches,
                 "e2e": {"value": total_images / (ms_e2e * 1e-3), "unit": "images/s",
                         "h2d_bytes_per_step": host_images.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
                 "roofline": roofline, "graph": bool(args.graph)}

@@ -77,7 +77,13 @@ class GatedLinearAttention(nn.Module):
         hw = kwargs["patch_resolution"]
         H, dk, dv, kd, vd = self.num_heads, self.head_qk_dim, self.head_v_dim, self.key_dim, self.value_dim
         taps, w_in, b_in = self._pack()
-        xs = ops.dwconv3x3(x, taps, self.in_proj[0].bias, hw, self.use_act_in_conv)
+        # ``local_fn`` / ``scan_fn`` let a caller substitute the two steps that look beyond the tokens at hand (the
+        # 3x3 neighbourhood and the scan) -- the sequence-parallel driver supplies halo and boundary-state versions
+        local_fn, scan_fn = kwargs.get("local_fn"), kwargs.get("scan_fn")
+        if local_fn is None:
+            xs = ops.dwconv3x3(x, taps, self.in_proj[0].bias, hw, self.use_act_in_conv)
+        else:
+            xs = local_fn(x, taps, self.in_proj[0].bias, hw, self.use_act_in_conv)
         # one GEMM for [q | k | v | output-gate logits | low-rank gate features]
         z = F.linear(xs, w_in, b_in)
         heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)           # [B,H,L,d] views, no copy
@@ -88,8 +94,11 @@ class GatedLinearAttention(nn.Module):
         g_fwd, g_bwd = heads(gk[..., :kd], dk), heads(gk[..., kd:], dk)
         o = torch.empty(B, L, H, dv, dtype=x.dtype, device=x.device).permute(0, 2, 1, 3)
         # reference: (o_f + o_b) / 2 in the operator wrapper, / 2 again in the eval branch (vig.py:443)
-        ops.bi_gla(q, k, v, g_fwd, g_bwd, out_scale=0.25, out=o, gate_logit_normalizer=float(self.gate_logit_normalizer),
-                   clamp_min=self.clamp_min)
+        scan_kw = dict(out_scale=0.25, out=o, gate_logit_normalizer=float(self.gate_logit_normalizer), clamp_min=self.clamp_min)
+        if scan_fn is None:
+            ops.bi_gla(q, k, v, g_fwd, g_bwd, **scan_kw)
+        else:
+            scan_fn(q, k, v, g_fwd, g_bwd, **scan_kw)
         y = ops.gate_inject(o, xs, gate_logits, self.g_norm.weight, self.l_norm.weight, self.g_norm.eps, self.use_out_act)
         return self.o_proj(y)
 

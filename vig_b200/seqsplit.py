@@ -83,3 +83,56 @@ def bi_gla_sequence_parallel(q, k, v, g_fwd, g_bwd, group=None, summary_fn=cuda_
     summaries = exchange(msg, group)
     s_f, s_b = fold(summaries, rank, dk, dv)
     return scan_fn(q, k, v, g_fwd, g_bwd, s_f, s_b, **kw)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Whole-model sequence parallelism: the token grid is split by image rows.  Everything in a block is token-local
+# except (1) the depthwise 3x3 conv, which needs one row of halo from each neighbour, and (2) the scan, which
+# needs the boundary states; both are one small all-gather per block.  The final average pool is one all-reduce.
+
+def row_range(h, rank, world):
+    """Rows [r0, r1) of an h-row token grid owned by ``rank`` (as even as possible, earlier ranks get the extra)."""
+    base, extra = divmod(h, world)
+    r0 = rank * base + min(rank, extra)
+    return r0, r0 + base + (1 if rank < extra else 0)
+
+
+def _halo_local_fn(group, rank, world):
+    """Depthwise conv over this rank's rows with one row of halo gathered from the neighbours."""
+    from . import ops
+
+    def local_fn(x, taps, bias, hw, act):
+        rows, w = hw
+        B, L, C = x.shape
+        edges = torch.stack([x[:, :w], x[:, L - w:]], dim=0).contiguous()          # my first and last row
+        gathered = [torch.empty_like(edges) for _ in range(world)]
+        dist.all_gather(gathered, edges, group=group)
+        top = gathered[rank - 1][1] if rank > 0 else torch.zeros_like(edges[0])        # zero rows = the conv's padding
+        bot = gathered[rank + 1][0] if rank + 1 < world else torch.zeros_like(edges[0])
+        padded = torch.cat([top, x, bot], dim=1)
+        y = ops.dwconv3x3(padded, taps, bias, (rows + 2, w), act)
+        return y[:, w:L + w].contiguous()
+    return local_fn
+
+
+def vig_forward_sequence_parallel(model, images, group=None):
+    """Logits of ``model`` (a ``vig_b200.ViG`` in eval mode) with the token sequence of every image split across
+    the ranks of ``group`` by rows of the patch grid.  Every rank passes the same ``images`` and gets the same
+    logits.  The stem is computed redundantly on every rank (about 4 % of the model's work)."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    tokens, (h, w) = model.patch_embed(images)
+    if h < world:
+        raise ValueError("more ranks than rows in the patch grid")
+    B, _, C = tokens.shape
+    x = tokens + model._pos((h, w))
+    r0, r1 = row_range(h, rank, world)
+    x = x.view(B, h, w, C)[:, r0:r1].reshape(B, (r1 - r0) * w, C).contiguous()
+    hooks = dict(patch_resolution=(r1 - r0, w), local_fn=_halo_local_fn(group, rank, world),
+                 scan_fn=lambda q, k, v, gf, gb, **kw: bi_gla_sequence_parallel(q, k, v, gf, gb, group=group, **kw))
+    hidden, residual = x, None
+    for blk in model.blocks:
+        hidden, residual = blk.forward_deferred(hidden, residual, **hooks)
+    x = model.norm(hidden, residual)
+    pooled = x.float().sum(dim=1)
+    dist.all_reduce(pooled, group=group)
+    return model.head((pooled / (h * w)).to(x.dtype))
