@@ -28,6 +28,9 @@ WORKLOADS = {
     "vig_t_1024": ("vig_t_dk64", 1024, 64),
     "vig_s_224": ("vig_s_dk64", 224, 128),
     "vig_t_224": ("vig_t_dk64", 224, 128),
+    # the reference's shipped head size (EXPAND_K 0.5 -> dk = 32, classification/configs/vig/vig-t.yaml:13)
+    "vig_t_1024_dk32": ("vig_t", 1024, 64),
+    "vig_s_224_dk32": ("vig_s", 224, 128),
     # ViG-B at 2048x2048 (L = 16384): under torchrun the token sequence of every image is split across the ranks
     # (boundary states + one conv halo row per block over NCCL); the batch is the same on every rank
     "vig_b_2048_seq": ("vig_b_dk64", 2048, 8),
@@ -145,8 +148,9 @@ def run_reference(args, rank):
 
 def workload_config(args, batch):
     preset, size, _ = WORKLOADS[args.workload]
+    dk = 64 if preset.endswith("dk64") else 32
     return {"workload": f"{args.workload}: ViG {preset} forward, {size}x{size} images, patch 16 (L={(size // 16) ** 2}), "
-                        f"batch {batch} per GPU, 12 blocks, dk=dv=64",
+                        f"batch {batch} per GPU, 12 blocks, dk={dk}, dv=64",
             "per_gpu_batch": batch, "image_size": size,
             "sharding": ("token sequence across GPUs by image rows (all-gather of boundary states and conv halo rows per block)"
                          if args.workload in SEQ_SPLIT else "images across GPUs, no collective"),

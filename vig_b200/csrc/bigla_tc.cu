@@ -220,9 +220,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const int cp = lane % CPW;
     const int grp = warp * RPW + lane / CPW;
     // state rows: an M=64 accumulator puts row r in TMEM lane (r % 16) + 32 * (r / 16)
-    const bool st_thread = lane < 16 && (16 * (warp & 3) + lane) < DK;
-    const int st_row = 16 * (warp & 3) + lane;    // key channel
-    const int st_col0 = 32 * (warp >> 2);         // first of 32 value columns
+    // (16 TMEM lanes of each warp's quadrant).  A warp reads 32 columns of its 16 rows; lanes 0-15 keep columns
+    // 0-15 of them and hand columns 16-31 to lanes 16-31, so every thread carries 16 state values.
+    const int st_row = 16 * (warp & 3) + (lane & 15);         // key channel
+    const bool st_thread = st_row < DK;
+    const int st_ld0 = 32 * (warp >> 2);                      // first of the 32 value columns my warp reads
+    const int st_col0 = st_ld0 + 16 * (lane >> 4);            // first of my 16 value columns
     const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
     const bool raw_logits = p.gate_norm > 0.f;
     const float inv_norm = raw_logits ? 1.f / p.gate_norm : 1.f;
@@ -261,7 +264,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     };
     if (tid == 0) { issue_gk(0); issue_qv(0); }
 
-    float S[32];                                  // my 32 columns of state row st_row (state threads only)
+    float S[16];                                  // my 16 columns of state row st_row
     const uint32_t* sq = reinterpret_cast<const uint32_t*>(smem + OFF_RQ);
     const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + OFF_RK);
     const uint32_t* sg = reinterpret_cast<const uint32_t*>(smem + OFF_RG);
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                     else if (dir ? p.init_b : p.init_f) src = (dir ? p.init_b : p.init_f) + (size_t)bh * DK * DV;
                 }
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
+                for (int j = 0; j < 16; j += 4) {
                     const float4 t4 = src ? __ldg(reinterpret_cast<const float4*>(src + st_row * DV + st_col0 + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
                     S[j] = t4.x; S[j + 1] = t4.y; S[j + 2] = t4.z; S[j + 3] = t4.w;
                 }
@@ -333,23 +336,40 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 glast.x += s2.x; glast.y += s2.y;
             }
             off.x -= gref.x; off.y -= gref.y;
+            // Each tile in two batches -- read all raw values, then write all operands: the compiler cannot prove
+            // that the operand tiles do not alias the raw tiles and would otherwise serialise
+            // load -> scale -> store token by token.
             auto scale_tiles = [&](auto clamp_c) {
                 constexpr bool CLAMP = decltype(clamp_c)::value != 0;
-#pragma unroll
-                for (int u = 0; u < TPG; ++u) {
-                    const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
-                    float ex = off.x + gl[u].x, ey = off.y + gl[u].y;
+                auto exponents = [&](int u, float& ex, float& ey) {
+                    ex = off.x + gl[u].x; ey = off.y + gl[u].y;
                     if (CLAMP) {
                         out_of_range |= fmaxf(fabsf(ex), fabsf(ey)) > MAX_EXPONENT2;
                         ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
                         ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
                     }
-                    const uint32_t o = swz(tok, cp * 4);
-                    const float2 kk = Pack2<T>::unpack(sk[tok * CPW + cp]);
-                    *reinterpret_cast<uint32_t*>(smem + OFF_KT + o) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
-                    if (!STATES_ONLY) {
-                        const float2 qq = Pack2<T>::unpack(sq[tok * CPW + cp]);
-                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + o) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                };
+                uint32_t raw[TPG];
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) raw[u] = sk[(grp * TPG + (DIR ? TPG - 1 - u : u)) * CPW + cp];
+#pragma unroll
+                for (int u = 0; u < TPG; ++u) {
+                    const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
+                    float ex, ey;
+                    exponents(u, ex, ey);
+                    const float2 kk = Pack2<T>::unpack(raw[u]);
+                    *reinterpret_cast<uint32_t*>(smem + OFF_KT + swz(tok, cp * 4)) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                }
+                if (!STATES_ONLY) {
+#pragma unroll
+                    for (int u = 0; u < TPG; ++u) raw[u] = sq[(grp * TPG + (DIR ? TPG - 1 - u : u)) * CPW + cp];
+#pragma unroll
+                    for (int u = 0; u < TPG; ++u) {
+                        const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
+                        float ex, ey;
+                        exponents(u, ex, ey);
+                        const float2 qq = Pack2<T>::unpack(raw[u]);
+                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + swz(tok, cp * 4)) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
                     }
                 }
             };
@@ -375,7 +395,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             for (int g2 = 0; g2 < NG / 2; ++g2) gr += part[(dir ? g2 + NG / 2 : g2) * DK + st_row];
             const float eg = ex2(gr);
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
+            for (int j = 0; j < 16; j += 8) {
                 uint4 w;
                 w.x = Pack2<T>::pack(S[j] * eg, S[j + 1] * eg); w.y = Pack2<T>::pack(S[j + 2] * eg, S[j + 3] * eg);
                 w.z = Pack2<T>::pack(S[j + 4] * eg, S[j + 5] * eg); w.w = Pack2<T>::pack(S[j + 6] * eg, S[j + 7] * eg);
@@ -480,12 +500,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         tc_fence_after();
         {
             float u[32];
-            tc_ld32(tmem + lane_base + TM_U + st_col0, u);            // warp-wide; only state threads use the result
+            tc_ld32(tmem + lane_base + TM_U + st_ld0, u);             // rows live in lanes 0-15 of the warp
             tc_wait_ld();
-            if (st_thread) {
-                const float e_last = vec[st_row], e_rel = vec[64 + st_row];
+            const float e_last = vec[st_row & 63], e_rel = vec[64 + (st_row & 63)];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) S[j] = fmaf(S[j], e_last, e_rel * u[j]);
+            for (int j = 0; j < 16; ++j) {
+                const float hi = __shfl_sync(0xffffffffu, u[16 + j], lane & 15);   // columns 16-31 go to lanes 16-31
+                const float mine = lane < 16 ? u[j] : hi;
+                S[j] = fmaf(S[j], e_last, e_rel * mine);
             }
         }
         TC_STAMP(10);
@@ -505,7 +527,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
             if (dst && st_thread) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4)
+                for (int j = 0; j < 16; j += 4)
                     *reinterpret_cast<float4*>(dst + st_row * DV + st_col0 + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
             }
             if (gdst && tid < DK) gdst[tid] = gtot[tid] * LN2;          // back to natural-log units
