@@ -50,6 +50,9 @@ extern "C" {
 #define VIG_IMPL_AUTO 0
 #define VIG_IMPL_SIMT 1
 #define VIG_IMPL_TC 2
+#define VIG_IMPL_TC_SINGLE 3 /* tensor-core path as ONE persistent launch for multi-segment sequences (experimental:
+                               needs ~20 MB more workspace and as many co-resident CTAs as a sequence has segments;
+                               falls back to the three-launch form when either is missing) */
 
 VIG_API int vig_version(void);
 VIG_API const char* vig_strerror(int status);

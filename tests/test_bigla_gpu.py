@@ -150,3 +150,24 @@ def test_empty_batch_and_errors():
     bad = torch.zeros(1, 1, 8, 48, device="cuda")
     with pytest.raises(RuntimeError):
         vig_b200.bi_gla(bad, bad, bad, bad, bad)
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 1300, 64), (1, 2, 4096, 32), (3, 1, 700, 64)])
+def test_single_launch_form_matches_oracle_and_three_launch_form(shape):
+    """The persistent single-launch form of the tensor-core path (impl 3): same result as the default form up to
+    bf16 rounding of the cross-segment term, final states and total decay included, with initial states."""
+    import vig_b200
+    from vig_b200 import _lib
+    B, H, L, dk = shape
+    ins = oracle.make_bigla_inputs(B, H, L, dk, 64, seed=L)
+    g = torch.Generator().manual_seed(3)
+    i_f, i_b = torch.randn(B, H, dk, 64, generator=g), torch.randn(B, H, dk, 64, generator=g)
+    dev = _cuda(ins, torch.bfloat16)
+    kw = dict(init_state_fwd=i_f.cuda(), init_state_bwd=i_b.cuda(), output_final_state=True, output_logdecay=True)
+    o1, ex1 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_SINGLE, **kw)
+    o0, ex0 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC, **kw)
+    ref, s_f, s_b = oracle.naive_bi_gla(*[t.float().cpu() for t in dev], init_fwd=i_f, init_bwd=i_b, return_states=True)
+    assert rel_err(o1.float(), ref) < 2e-2
+    assert rel_err(o1.float(), o0.float()) < 1e-2
+    assert rel_err(ex1["final_fwd"], s_f) < 2e-2 and rel_err(ex1["final_bwd"], s_b) < 2e-2
+    assert rel_err(ex1["logdecay_fwd"], ex0["logdecay_fwd"]) < 1e-5

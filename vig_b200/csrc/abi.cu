@@ -29,7 +29,7 @@ static bool dims_ok(int dk, int dv) {
 extern "C" size_t vig_bigla_workspace_bytes(int B, int H, int L, int dk, int dv, int dtype, int impl) {
     if (B <= 0 || H <= 0 || L <= 0 || !dims_ok(dk, dv)) return 0;
     size_t simt = bigla_simt_workspace(B, H, L, dk, dv);
-    size_t tc = (dtype != VIG_DTYPE_F32 && impl != VIG_IMPL_SIMT) ? bigla_tc_workspace(B, H, L, dk, dv) : 0;
+    size_t tc = (dtype != VIG_DTYPE_F32 && impl != VIG_IMPL_SIMT) ? bigla_tc_workspace(B, H, L, dk, dv, impl != VIG_IMPL_TC_SINGLE) : 0;
     return simt > tc ? simt : tc;
 }
 
@@ -51,7 +51,7 @@ extern "C" int vig_bigla_fwd(const void* q, const void* k, const void* v, const 
     if (dtype < 0 || dtype > 2) return VIG_ERR_DTYPE;
     if (B < 0 || H <= 0 || L < 0 || !dims_ok(dk, dv)) return VIG_ERR_SHAPE;
     if (dir_mask < 1 || dir_mask > 3) return VIG_ERR_ARG;
-    if (impl < VIG_IMPL_AUTO || impl > VIG_IMPL_TC) return VIG_ERR_ARG;
+    if (impl < VIG_IMPL_AUTO || impl > VIG_IMPL_TC_SINGLE) return VIG_ERR_ARG;
     if (B == 0 || L == 0) return VIG_OK;
     if (!k || !v) return VIG_ERR_NULL;
     if (o && !q) return VIG_ERR_NULL;
@@ -76,16 +76,18 @@ extern "C" int vig_bigla_fwd(const void* q, const void* k, const void* v, const 
     p.dir_mask = dir_mask; p.status = status_dev;
 
     bool use_tc = false;
-    if (impl == VIG_IMPL_TC) {
+    if (impl == VIG_IMPL_TC || impl == VIG_IMPL_TC_SINGLE) {
         if (!bigla_tc_supported(p)) return VIG_ERR_SHAPE;
         use_tc = true;
     } else if (impl == VIG_IMPL_AUTO) {
         use_tc = bigla_tc_supported(p);
     }
     if (use_tc) {
-        const size_t need = bigla_tc_workspace(B, H, L, dk, dv);
+        // the single-launch form (on request) needs the larger workspace; with only the states' worth it runs as three launches
+        const size_t need = bigla_tc_workspace(B, H, L, dk, dv, true);
         if (need && (!workspace || workspace_bytes < need)) return VIG_ERR_WORKSPACE;
-        return bigla_tc_launch(p, workspace, workspace_bytes, (cudaStream_t)stream);
+        if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return VIG_ERR_ALIGN;
+        return bigla_tc_launch(p, workspace, workspace_bytes, impl == VIG_IMPL_TC_SINGLE, (cudaStream_t)stream);
     }
     const size_t need = bigla_simt_workspace(B, H, L, dk, dv);
     const bool needs_ws = need_states || L > 64;

@@ -50,9 +50,11 @@ constexpr int OFF_ST = OFF_KT + TILE_B;                      // bf16 state opera
 constexpr int OFF_PART = OFF_ST + 64 * 128;                  // fp32 [16][64] group sums of log-gates
 constexpr int OFF_VEC = OFF_PART + 16 * 64 * 4;              // fp32 [2][64]: exp(G_last), exp(G_last - G_ref)
 constexpr int OFF_GTOT = OFF_VEC + 2 * 64 * 4;               // fp32 [64] summed log-gates of the segment
-constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: gk, q, v, p, o
-constexpr int OFF_MISC = OFF_BAR + 8 * 8;                    // tmem base, abort flag
-constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;             // + slack for the manual 1024-byte alignment
+constexpr int OFF_BAR = OFF_GTOT + 64 * 4;                   // mbarriers: gk, q, v, p, o, x
+constexpr int OFF_MISC = OFF_BAR + 8 * 8;                    // tmem base, abort flag, current work item
+constexpr int OFF_CVEC = OFF_PART + 2048;                    // fp32 [4][64]: log2 scale of the deferred cross-segment term
+                                                             // (the group sums use only the first 2 KB of their 4 KB)
+constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;             // + slack for the manual 1024-byte alignment             // + slack for the manual 1024-byte alignment
 
 // ---------------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -158,8 +160,10 @@ struct TcMaps { CUtensorMap q, k, v, gf, gb; };
 #ifdef VIG_TC_TIMING
 __device__ long long g_tc_timing[64 * 16];
 #define TC_STAMP(slot) do { if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 1 && n < 4) g_tc_timing[(STATES_ONLY ? 0 : 512) + n * 16 + (slot)] = clock64(); } while (0)
+#define TC_STAMP2(slot) do { if (tid == 0 && blockIdx.x == 1 && item_count < 8) g_tc_timing[512 + item_count * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TC_STAMP(slot) do { } while (0)
+#define TC_STAMP2(slot) do { } while (0)
 #endif
 
 // ---------------------------------------------------------------------------------------------------
@@ -177,19 +181,39 @@ __device__ __forceinline__ float fast_gate2(float x, bool raw_logits, float inv_
     return raw_logits ? (fminf(y, 0.f) - lg2(1.f + ex2(-fabsf(y)))) * inv_norm : y;
 }
 
-template <int DK, typename T, bool STATES_ONLY>
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// MODE 0: one segment per CTA, entering states from the workspace (or the caller's initial states).
+// MODE 1: states only -- local end states of every segment from a zero state, no q, no output.
+// MODE 2: single launch for long sequences.  Persistent CTAs draw (b*h, segment) items from a ticket counter; an
+//         item is swept from a ZERO state, which yields its local end states (published for the other segments
+//         of the sequence) and the output without the term that comes from the state entering the segment:
+//             o_i += (q_i * 2^{G_i}) . S_enter        (G_i = cumulative gate from the segment's edge to token i)
+//         The scaled q operand tiles are parked in a per-CTA scratch (L2-resident); when all segments of the
+//         sequence have published, the CTA folds the other segments' states into S_enter and adds the missing
+//         term with four small MMAs on the parked tiles, while the output accumulators are still in tensor memory.
+//         Tickets are handed out in order, so the oldest unfinished sequence always has all its segments in
+//         flight provided the grid holds at least as many resident CTAs as a sequence has segments (host check).
+template <int DK, typename T, int MODE>
 __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_constant__ TcMaps maps, BiglaParams p, int use_ws) {
+    constexpr bool STATES_ONLY = MODE == 1;
+    constexpr bool FUSED = MODE == 2;
     extern __shared__ uint8_t smem_raw[];
     // align by an integer offset (not by casting through an integer) so that accesses stay shared-space loads
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-    const int seg_t0 = seg * SEG;
-    const int nch = min(SEG_CHUNKS, (p.L - seg_t0 + CHUNK - 1) / CHUNK);
-    const int nseg = gridDim.x;
+    const int nseg = FUSED ? p.nseg : (int)gridDim.x;
+    int seg = blockIdx.x, bh = blockIdx.y, b = 0, h = 0, seg_t0 = 0, nch = 0, n_iter = 0;   // the current work item
 
     const uint32_t bar_gk = sbase + OFF_BAR, bar_q = bar_gk + 8, bar_v = bar_gk + 16, bar_p0 = bar_gk + 24, bar_o = bar_gk + 32;
+    const uint32_t bar_x = bar_gk + 40;
+    float* cvec = reinterpret_cast<float*>(smem + OFF_CVEC);
+    volatile int* item_slot = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
     float* part = reinterpret_cast<float*>(smem + OFF_PART);
@@ -198,7 +222,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const Waiter waiter{abort_flag, p.status};
 
     if (tid == 0) {
-        mbar_init(bar_gk, 1); mbar_init(bar_q, 1); mbar_init(bar_v, 1); mbar_init(bar_p0, 1); mbar_init(bar_o, 1);
+        mbar_init(bar_gk, 1); mbar_init(bar_q, 1); mbar_init(bar_v, 1); mbar_init(bar_p0, 1); mbar_init(bar_o, 1); mbar_init(bar_x, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -238,7 +262,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     constexpr uint32_t IDESC_U = make_idesc(Pack2<T>::FMT, 1, 1, 64, 64);
 
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, dir_last = (p.dir_mask & 2) ? 1 : 0;
-    const int n_iter = (dir_last - dir_first + 1) * nch;      // iterations: sweeps x chunks
 
     // Tiles of iteration n (thread 0 only).  Three groups with their own barriers, because their buffers become
     // free at different times: k and the gates right after the operand tiles are written, q and v only when
@@ -262,23 +285,43 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         mbar_expect_tx(bar_v, CHUNK * DV * 2);
         tma_load_4d(sbase + OFF_V, &maps.v, 0, t0, h, b, bar_v);
     };
-    if (tid == 0) { issue_gk(0); issue_qv(0); }
-
     float S[16];                                  // my 16 columns of state row st_row
     const uint32_t* sq = reinterpret_cast<const uint32_t*>(smem + OFF_RQ);
     const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + OFF_RK);
     const uint32_t* sg = reinterpret_cast<const uint32_t*>(smem + OFF_RG);
 
-    for (int n = 0; n < n_iter; ++n) {
+    uint32_t it_count = 0;                        // iterations done by this CTA: parity of the per-iteration barriers
+    uint32_t item_count = 0;                      // items done by this CTA: parity of bar_x
+    long long last_arrival_dbg = 0; (void)last_arrival_dbg;
+    for (;;) {                                    // work items (exactly one unless FUSED)
+    if (FUSED) {
+        if (tid == 0) *item_slot = (int)atomicAdd(p.ticket, 1u);
+        __syncthreads();
+        const int item = *item_slot;
+        __syncthreads();                          // everyone has read the slot before it is written again
+        if (item >= p.B * p.H * nseg) break;
+        bh = item / nseg; seg = item % nseg;
+    }
+    TC_STAMP2(0);
+    b = bh / p.H; h = bh % p.H;
+    seg_t0 = seg * SEG;
+    nch = min(SEG_CHUNKS, (p.L - seg_t0 + CHUNK - 1) / CHUNK);
+    n_iter = (dir_last - dir_first + 1) * nch;    // iterations: sweeps x chunks
+    if (tid == 0) { issue_gk(0); issue_qv(0); }
+
+    for (int n = 0; n < n_iter; ++n, ++it_count) {
         const int dir = dir_first + n / nch, ci = n % nch;
         const int c = dir ? nch - 1 - ci : ci;
         const int t0 = seg_t0 + c * CHUNK;
-        const uint32_t par = (uint32_t)(n & 1);
+        const uint32_t par = it_count & 1u;
 
         if (ci == 0) {                            // a sweep starts: entering state of the segment, zeroed gate total
             if (st_thread) {
                 const float* src = nullptr;
-                if (!STATES_ONLY) {
+                if (FUSED) {                      // only the sequence's own initial state is known at this point
+                    const float* init = dir ? p.init_b : p.init_f;
+                    if (init && seg == (dir ? nseg - 1 : 0)) src = init + (size_t)bh * DK * DV;
+                } else if (!STATES_ONLY) {
                     if (use_ws) src = p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV;
                     else if (dir ? p.init_b : p.init_f) src = (dir ? p.init_b : p.init_f) + (size_t)bh * DK * DV;
                 }
@@ -369,7 +412,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                         float ex, ey;
                         exponents(u, ex, ey);
                         const float2 qq = Pack2<T>::unpack(raw[u]);
-                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + swz(tok, cp * 4)) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                        const uint32_t qw = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + swz(tok, cp * 4)) = qw;
+                        if (FUSED)                // park the operand tile (same swizzled image) for the deferred term
+                            *reinterpret_cast<uint32_t*>(p.qscratch + ((size_t)blockIdx.x * 4 + n) * TILE_B + swz(tok, cp * 4)) = qw;
                     }
                 }
             };
@@ -386,6 +432,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         if (grp == 0) {
             vec[2 * cp] = ex2(glast.x); vec[2 * cp + 1] = ex2(glast.y);
             vec[64 + 2 * cp] = ex2(glast.x - gref.x); vec[64 + 2 * cp + 1] = ex2(glast.y - gref.y);
+            if (FUSED) {                          // log2 of (decay from the segment's edge to this chunk's reference token)
+                cvec[n * 64 + 2 * cp] = gtot[2 * cp] + gref.x; cvec[n * 64 + 2 * cp + 1] = gtot[2 * cp + 1] + gref.y;
+            }
             gtot[2 * cp] += glast.x; gtot[2 * cp + 1] += glast.y;
         }
         // state operand for the inter-chunk product: bf16(exp(G_ref) * S_in), MN-major [channel][value]
@@ -517,7 +566,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         if (ci == nch - 1) {                      // a sweep ends: hand the state out
             float* dst = nullptr;
             float* gdst = nullptr;
-            if (STATES_ONLY) {
+            if (STATES_ONLY || FUSED) {
                 const size_t slot = ((size_t)bh * nseg + seg) * 2 + dir;
                 dst = p.ws_state + slot * DK * DV;
                 gdst = p.ws_decay + slot * DK;
@@ -532,6 +581,138 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
             if (gdst && tid < DK) gdst[tid] = gtot[tid] * LN2;          // back to natural-log units
         }
+    }
+
+    if (FUSED) {
+        // ---- publish: my local end states are in the workspace; count me in for my sequence ------------------
+        TC_STAMP2(1);
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) atomicAdd(p.group_cnt + bh, 1u);
+        // bring my parked q operand tiles back meanwhile (plain loads that bypass L1: the scratch slot was read by
+        // the previous item of this CTA); every tile buffer is free at this point
+        {
+            const uint8_t* src = p.qscratch + (size_t)blockIdx.x * 4 * TILE_B;
+            const uint32_t dst_off[4] = {(uint32_t)OFF_QT, (uint32_t)OFF_KT, (uint32_t)OFF_RQ, (uint32_t)OFF_RK};
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                if (n < n_iter) {
+#pragma unroll
+                    for (int r = 0; r < TILE_B / (NTHREADS * 16); ++r) {
+                        const int o16 = (r * NTHREADS + tid) * 16;
+                        *reinterpret_cast<uint4*>(smem + dst_off[n] + o16) = __ldcg(reinterpret_cast<const uint4*>(src + n * TILE_B + o16));
+                    }
+                }
+            }
+        }
+        TC_STAMP2(2);
+        // Bounded wait until `count` of the sequence's segments have passed a point (one warp polls).
+        auto group_wait = [&](const uint32_t* counter) {
+            if (warp == 0) {
+                bool ok = false;
+                for (uint32_t i = 0; i < (1u << 21); ++i) {
+                    if (ld_acquire_u32(counter) >= (uint32_t)nseg) { ok = true; break; }
+                    if (*abort_flag) break;
+                    __nanosleep(64);
+                }
+                if (!ok) { *abort_flag = 1; if (p.status) atomicOr(p.status, 1); }
+            }
+            __threadfence();
+            __syncthreads();
+        };
+        group_wait(p.group_cnt + bh);             // every segment's local end state is in the workspace
+        // ---- scan over the segments, split by state element across the sequence's CTAs: each CTA turns, for its
+        //      slice of the dk x dv elements, every segment's local end state into the state that ENTERS that
+        //      segment (in place), and delivers the sequence's final state / total decay for that slice ----------
+        {
+            constexpr int NE = DK * DV;
+            const int slice = (NE + nseg - 1) / nseg;
+            const int e_end = min(NE, (seg + 1) * slice);
+            for (int dir = dir_first; dir <= dir_last; ++dir) {
+                const int first = dir ? nseg - 1 : 0, step = dir ? -1 : 1;
+                float* fin = dir ? p.final_b : p.final_f;
+                float* ld = dir ? p.logdecay_b : p.logdecay_f;
+                for (int e = seg * slice + tid; e < e_end; e += NTHREADS) {
+                    const int row = e / DV;
+                    float E = 0.f, gsum = 0.f;
+                    constexpr int PF = 16;        // loads of PF segments are in flight before the dependent chain runs
+                    for (int i0 = 0; i0 < nseg; i0 += PF) {
+                        float u[PF], g[PF];
+#pragma unroll
+                        for (int i = 0; i < PF; ++i) {
+                            const bool in = i0 + i < nseg;
+                            const size_t slot = ((size_t)bh * nseg + (first + (in ? i0 + i : 0) * step)) * 2 + dir;
+                            u[i] = in ? __ldcg(p.ws_state + slot * NE + e) : 0.f;
+                            g[i] = in ? __ldcg(p.ws_decay + slot * DK + row) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < PF; ++i) {
+                            if (i0 + i < nseg) {
+                                const size_t slot = ((size_t)bh * nseg + (first + (i0 + i) * step)) * 2 + dir;
+                                p.ws_state[slot * NE + e] = E;
+                                E = fmaf(E, __expf(g[i]), u[i]);
+                                gsum += g[i];
+                            }
+                        }
+                    }
+                    if (fin) fin[(size_t)bh * NE + e] = E;
+                    if (ld && (e % DV) == 0) ld[(size_t)bh * DK + row] = gsum;
+                }
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        uint32_t* scanned = p.group_cnt + (size_t)p.B * p.H + bh;
+        if (tid == 0) atomicAdd(scanned, 1u);
+        group_wait(scanned);                      // every slice of the entering states is in place
+        TC_STAMP2(3);
+        // ---- state operand of every chunk: bf16(2^{cvec} * S_enter), MN-major [channel][value] -------------------
+        const uint32_t st_off[4] = {(uint32_t)OFF_ST, (uint32_t)OFF_RG, (uint32_t)(OFF_RG + 64 * 128), (uint32_t)OFF_V};
+        for (int dir = dir_first; dir <= dir_last; ++dir) {
+            if (st_thread) {
+                const float4* src = reinterpret_cast<const float4*>(p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV + st_row * DV + st_col0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 t4 = __ldcg(src + j);
+                    S[4 * j] = t4.x; S[4 * j + 1] = t4.y; S[4 * j + 2] = t4.z; S[4 * j + 3] = t4.w;
+                }
+            }
+            for (int ci = 0; ci < nch; ++ci) {
+                const int n = (dir - dir_first) * nch + ci;
+                if (st_thread) {
+                    const float eg = ex2(cvec[n * 64 + st_row]);
+#pragma unroll
+                    for (int j = 0; j < 16; j += 8) {
+                        uint4 w;
+                        w.x = Pack2<T>::pack(S[j] * eg, S[j + 1] * eg); w.y = Pack2<T>::pack(S[j + 2] * eg, S[j + 3] * eg);
+                        w.z = Pack2<T>::pack(S[j + 4] * eg, S[j + 5] * eg); w.w = Pack2<T>::pack(S[j + 6] * eg, S[j + 7] * eg);
+                        *reinterpret_cast<uint4*>(smem + st_off[n] + swz(st_row, (st_col0 + j) * 2)) = w;
+                    }
+                }
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        // ---- the deferred term: O_chunk += (parked q operand) x (entering state operand) ---------------------
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t q_off[4] = {(uint32_t)OFF_QT, (uint32_t)OFF_KT, (uint32_t)OFF_RQ, (uint32_t)OFF_RK};
+            for (int n = 0; n < n_iter; ++n) {
+                const int dir = dir_first + n / nch, ci = n % nch;
+                const int c = dir ? nch - 1 - ci : ci;
+#pragma unroll
+                for (int k4 = 0; k4 < DK / 16; ++k4)
+                    tc_mma(tmem + TM_O + c * 64, make_desc(sbase + q_off[n] + k4 * 32), make_desc(sbase + st_off[n] + k4 * 2048), IDESC_OV, 1);
+            }
+            tc_commit(bar_x);
+        }
+        __syncwarp();
+        if (warp == 0) waiter.wait(bar_x, item_count & 1u);
+        __syncthreads();
+        TC_STAMP2(4);
+        if (tid == 0 && blockIdx.x == 1 && item_count < 8) { TC_STAMP2(5); }
+        ++item_count;
     }
 
     // ---- epilogue: output accumulators -> global -----------------------------------------------------
@@ -556,6 +737,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
         }
     }
+    if (!FUSED) break;
+#ifdef VIG_TC_TIMING
+    if (tid == 0 && blockIdx.x == 1 && item_count >= 1 && item_count <= 8) g_tc_timing[512 + (item_count - 1) * 16 + 6] = clock64();
+    if (tid == 0 && blockIdx.x == 1 && item_count >= 1 && item_count <= 8) g_tc_timing[512 + (item_count - 1) * 16 + 7] = last_arrival_dbg;
+#endif
+    tc_fence_before();                            // the accumulators are read out before the next item overwrites them
+    __syncthreads();
+    }                                             // work items
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -609,17 +798,60 @@ bool tma_ok(const void* base, const int64_t* s, int B, int H) {
     return true;
 }
 
+constexpr int MAX_SLOTS = 320;                 // scratch slots of the single-launch path (>= resident CTAs of a B200)
+
+size_t states_bytes(int B, int H, int L, int dk, int dv) {
+    const size_t nseg = (L + SEG - 1) / SEG;
+    return (size_t)B * H * nseg * 2 * ((size_t)dk * dv + dk) * sizeof(float);
+}
+size_t counter_bytes(int B, int H) { return ((2 * (size_t)B * H + 1) * sizeof(uint32_t) + 255) & ~(size_t)255; }   // ticket, arrivals, ready flags
+
 template <int DK, typename T>
-int launch_tc(const BiglaParams& p_in, const TcMaps& maps, cudaStream_t stream) {
+int launch_tc(const BiglaParams& p_in, const TcMaps& maps, bool allow_fused, cudaStream_t stream) {
     BiglaParams p = p_in;
     const int nseg = (p.L + SEG - 1) / SEG;
     const int BH = p.B * p.H;
     const bool need_states = p.final_f || p.final_b || p.logdecay_f || p.logdecay_b;
     const int use_ws = nseg > 1;
     dim3 grid(nseg, BH);
-    auto kA = bigla_tc_kernel<DK, T, true>;
-    auto kC = bigla_tc_kernel<DK, T, false>;
+    auto kA = bigla_tc_kernel<DK, T, 1>;
+    auto kC = bigla_tc_kernel<DK, T, 0>;
+    auto kF = bigla_tc_kernel<DK, T, 2>;
     cudaError_t e;
+    if (use_ws && p.o && allow_fused) {
+        // Single launch: persistent CTAs, as many as are resident at once.  A sequence's segments wait for one
+        // another, so the grid must hold at least nseg CTAs that run concurrently; otherwise use three launches.
+        static int resident[64] = {};             // per device; 0 = not queried yet
+        static int sm_count[64] = {};
+        int dev = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) {
+            if ((e = cudaFuncSetAttribute(kF, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
+            if ((e = cudaFuncSetAttribute(kF, cudaFuncAttributePreferredSharedMemoryCarveout, 100)) != cudaSuccess) return (int)e;
+            if (!resident[dev]) {
+                int per_sm = 0, sms = 0;
+                if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kF, NTHREADS, SMEM_BYTES)) != cudaSuccess) return (int)e;
+                if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+                resident[dev] = per_sm * sms > 0 ? per_sm * sms : -1;
+                sm_count[dev] = sms;
+            }
+            // The occupancy query is conservative about the shared-memory carve-out (it reports one CTA per SM where
+            // two run): it is used for the safety condition below, while the grid is sized for the two CTAs per SM
+            // the kernel is built for.  CTAs that are not resident at first simply start later and find no work.
+            const int items = BH * nseg;
+            const int safe = resident[dev];
+            int ctas = 2 * sm_count[dev] < MAX_SLOTS ? 2 * sm_count[dev] : MAX_SLOTS;
+            if (ctas > items) ctas = items;
+            if (ctas < safe) ctas = safe < MAX_SLOTS ? safe : MAX_SLOTS;
+            const int running = ctas < safe ? ctas : safe;    // CTAs guaranteed to run concurrently
+            if (running >= nseg) {
+                if ((e = cudaMemsetAsync(p.ticket, 0, counter_bytes(p.B, p.H), stream)) != cudaSuccess) return (int)e;
+                p.nseg = nseg;
+                kF<<<ctas, NTHREADS, SMEM_BYTES, stream>>>(maps, p, 1);
+                return (int)cudaGetLastError();
+            }
+        }
+    }
     if (use_ws || (need_states && !p.o)) {
         if ((e = cudaFuncSetAttribute(kA, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
         kA<<<grid, NTHREADS, SMEM_BYTES, stream>>>(maps, p, 1);
@@ -651,17 +883,28 @@ bool bigla_tc_supported(const BiglaParams& p) {
     return encode_fn() != nullptr;
 }
 
-size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv) {
-    const size_t nseg = (L + SEG - 1) / SEG;
-    return (size_t)B * H * nseg * 2 * ((size_t)dk * dv + dk) * sizeof(float);
+// Workspace: [segment states | summed log-gates] for every path; the single-launch path adds
+// [ticket + per-(b,h) counters | MAX_SLOTS x 4 parked operand tiles].
+size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv, bool split_only) {
+    const size_t st = states_bytes(B, H, L, dk, dv);
+    if (split_only || L <= SEG) return st;
+    return ((st + 255) & ~(size_t)255) + counter_bytes(B, H) + (size_t)MAX_SLOTS * 4 * TILE_B;
 }
 
-int bigla_tc_launch(const BiglaParams& p_in, void* ws, size_t ws_bytes, cudaStream_t stream) {
+int bigla_tc_launch(const BiglaParams& p_in, void* ws, size_t ws_bytes, bool allow_fused, cudaStream_t stream) {
     BiglaParams p = p_in;
     const size_t nseg = (p.L + SEG - 1) / SEG;
-    if (ws_bytes < bigla_tc_workspace(p.B, p.H, p.L, p.dk, p.dv)) return VIG_ERR_WORKSPACE;
+    const size_t st = states_bytes(p.B, p.H, p.L, p.dk, p.dv);
+    if (ws_bytes < st) return VIG_ERR_WORKSPACE;
+    if (ws_bytes < bigla_tc_workspace(p.B, p.H, p.L, p.dk, p.dv, false)) allow_fused = false;
     p.ws_state = reinterpret_cast<float*>(ws);
     p.ws_decay = p.ws_state + (size_t)p.B * p.H * nseg * 2 * p.dk * p.dv;
+    if (allow_fused && nseg > 1) {
+        uint8_t* extra = reinterpret_cast<uint8_t*>(ws) + ((st + 255) & ~(size_t)255);
+        p.ticket = reinterpret_cast<uint32_t*>(extra);
+        p.group_cnt = p.ticket + 1;
+        p.qscratch = extra + counter_bytes(p.B, p.H);
+    }
     TcMaps maps;
     const void* qsrc = p.q ? p.q : p.k;           // states-only calls pass no q; the map is then never used
     const int64_t* qs = p.q ? p.sq : p.sk;
@@ -675,7 +918,7 @@ int bigla_tc_launch(const BiglaParams& p_in, void* ws, size_t ws_bytes, cudaStre
         !make_map(&maps.gf, gfs, gfst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
         !make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false))
         return VIG_ERR_DEVICE;
-#define VIG_TC(DKV, TT) if (p.dk == DKV) return launch_tc<DKV, TT>(p, maps, stream);
+#define VIG_TC(DKV, TT) if (p.dk == DKV) return launch_tc<DKV, TT>(p, maps, allow_fused, stream);
     if (p.dtype == VIG_DTYPE_BF16) { VIG_TC(64, __nv_bfloat16) VIG_TC(32, __nv_bfloat16) }
     else { VIG_TC(64, __half) VIG_TC(32, __half) }
 #undef VIG_TC

@@ -65,6 +65,11 @@ struct BiglaParams {
     float* ws_decay;    // [B*H][nchunk][2][dk]
     int nchunk;
     int32_t* status;
+    // single-launch tensor-core path: work tickets, per-(b,h) arrival counters, per-CTA scratch for operand tiles
+    uint32_t* ticket;
+    uint32_t* group_cnt;
+    uint8_t* qscratch;
+    int nseg;
 };
 
 __device__ __forceinline__ float gate_transform(float x, float gate_norm, float clamp_min) {
@@ -77,8 +82,8 @@ int bigla_simt_launch(const BiglaParams& p, cudaStream_t stream);
 size_t bigla_simt_workspace(int B, int H, int L, int dk, int dv);
 // scan over p.nchunk per-chunk (or per-segment) local states in the workspace, in place (phase B)
 int bigla_scan_launch(const BiglaParams& p, cudaStream_t stream);
-int bigla_tc_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream);
-size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv);
+int bigla_tc_launch(const BiglaParams& p, void* ws, size_t ws_bytes, bool allow_fused, cudaStream_t stream);
+size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv, bool split_only);
 bool bigla_tc_supported(const BiglaParams& p);
 
 }  // namespace vig

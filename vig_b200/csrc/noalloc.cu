@@ -48,6 +48,7 @@ extern "C" int vig_bigla_fwd_noalloc(const void* q, const void* k, const void* v
                                      float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
                                      int impl, int32_t* status_dev, void* stream) {
     if (!o) return VIG_ERR_NULL;
+    if (impl == VIG_IMPL_TC_SINGLE) impl = VIG_IMPL_TC;   // the single-launch form needs more scratch than this array holds
     const size_t need = vig_bigla_workspace_bytes(B, H, L, dk, dv, dtype, impl);
     if (need > VIG_NOALLOC_SCRATCH_BYTES) return VIG_ERR_SCRATCH_LIMIT;
     void* scratch = nullptr;
