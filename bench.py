@@ -169,7 +169,6 @@ def main():
     import oracle
     import vig_b200
     from vig_b200 import ops as vops
-    from vig_b200 import modules as vmods
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
     torch.cuda.set_device(local)

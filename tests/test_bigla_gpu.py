@@ -171,3 +171,50 @@ def test_single_launch_form_matches_oracle_and_three_launch_form(shape):
     assert rel_err(o1.float(), o0.float()) < 1e-2
     assert rel_err(ex1["final_fwd"], s_f) < 2e-2 and rel_err(ex1["final_bwd"], s_b) < 2e-2
     assert rel_err(ex1["logdecay_fwd"], ex0["logdecay_fwd"]) < 1e-5
+
+
+def _strong_gate_inputs(per_token, L=300, seed=2):
+    q, k, v, _, _ = oracle.make_bigla_inputs(1, 2, L, 64, 64, seed=seed)
+    gen = torch.Generator().manual_seed(seed + 100)
+    gf = -per_token * (0.5 + torch.rand(1, 2, L, 64, generator=gen))
+    gb = -per_token * (0.5 + torch.rand(1, 2, L, 64, generator=gen))
+    return q, k, v, gf, gb
+
+
+def test_strong_gates_inside_the_factorisation_range():
+    """Gates of about -0.8 per token: the CTA-wide vote takes the clamped code path, nothing is clamped."""
+    import vig_b200
+    from vig_b200 import _lib
+    ins = [t.bfloat16() for t in _strong_gate_inputs(0.8)]
+    ref = oracle.naive_bi_gla(*[t.float() for t in ins])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o = vig_b200.bi_gla(*[t.cuda() for t in ins], impl=_lib.IMPL_TC, status=status)
+    assert rel_err(o.float(), ref) < 2e-2
+    assert int(status.item()) == 0
+
+
+def test_gates_beyond_the_range_are_flagged_and_exact_on_the_simt_path():
+    import vig_b200
+    from vig_b200 import _lib
+    ins = [t.bfloat16() for t in _strong_gate_inputs(4.0)]
+    ref = oracle.naive_bi_gla(*[t.float() for t in ins])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o = vig_b200.bi_gla(*[t.cuda() for t in ins], impl=_lib.IMPL_TC, status=status)
+    assert int(status.item()) & 2                                  # reported, not trapped
+    assert torch.isfinite(o.float()).all()
+    o_simt = vig_b200.bi_gla(*[t.cuda() for t in ins], impl=_lib.IMPL_SIMT, status=status)
+    assert rel_err(o_simt.float(), ref) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_clamp_min_and_raw_logits(dtype):
+    """vig.py:439-441: g = clamp_min(logsigmoid(x) / 16, c)."""
+    import vig_b200
+    q, k, v, _, _ = oracle.make_bigla_inputs(2, 2, 200, 32, 64, seed=4)
+    gen = torch.Generator().manual_seed(9)
+    xf, xb = 8 * torch.randn(2, 2, 200, 32, generator=gen), 8 * torch.randn(2, 2, 200, 32, generator=gen)
+    ins = [t.to(dtype) for t in (q, k, v, xf, xb)]
+    lf = lambda t: torch.clamp_min(torch.nn.functional.logsigmoid(t.float()) / 16, -0.3)
+    ref = oracle.naive_bi_gla(ins[0].float(), ins[1].float(), ins[2].float(), lf(ins[3]), lf(ins[4]))
+    o = vig_b200.bi_gla(*[t.cuda() for t in ins], gate_logit_normalizer=16.0, clamp_min=-0.3)
+    assert rel_err(o.float(), ref) < TOL[dtype]

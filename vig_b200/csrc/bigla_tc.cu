@@ -160,10 +160,8 @@ struct TcMaps { CUtensorMap q, k, v, gf, gb; };
 #ifdef VIG_TC_TIMING
 __device__ long long g_tc_timing[64 * 16];
 #define TC_STAMP(slot) do { if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 1 && n < 4) g_tc_timing[(STATES_ONLY ? 0 : 512) + n * 16 + (slot)] = clock64(); } while (0)
-#define TC_STAMP2(slot) do { if (tid == 0 && blockIdx.x == 1 && item_count < 8) g_tc_timing[512 + item_count * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TC_STAMP(slot) do { } while (0)
-#define TC_STAMP2(slot) do { } while (0)
 #endif
 
 // ---------------------------------------------------------------------------------------------------
@@ -292,7 +290,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
 
     uint32_t it_count = 0;                        // iterations done by this CTA: parity of the per-iteration barriers
     uint32_t item_count = 0;                      // items done by this CTA: parity of bar_x
-    long long last_arrival_dbg = 0; (void)last_arrival_dbg;
     for (;;) {                                    // work items (exactly one unless FUSED)
     if (FUSED) {
         if (tid == 0) *item_slot = (int)atomicAdd(p.ticket, 1u);
@@ -302,7 +299,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         if (item >= p.B * p.H * nseg) break;
         bh = item / nseg; seg = item % nseg;
     }
-    TC_STAMP2(0);
     b = bh / p.H; h = bh % p.H;
     seg_t0 = seg * SEG;
     nch = min(SEG_CHUNKS, (p.L - seg_t0 + CHUNK - 1) / CHUNK);
@@ -585,7 +581,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
 
     if (FUSED) {
         // ---- publish: my local end states are in the workspace; count me in for my sequence ------------------
-        TC_STAMP2(1);
         __threadfence();
         __syncthreads();
         if (tid == 0) atomicAdd(p.group_cnt + bh, 1u);
@@ -605,7 +600,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 }
             }
         }
-        TC_STAMP2(2);
         // Bounded wait until `count` of the sequence's segments have passed a point (one warp polls).
         auto group_wait = [&](const uint32_t* counter) {
             if (warp == 0) {
@@ -665,7 +659,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         uint32_t* scanned = p.group_cnt + (size_t)p.B * p.H + bh;
         if (tid == 0) atomicAdd(scanned, 1u);
         group_wait(scanned);                      // every slice of the entering states is in place
-        TC_STAMP2(3);
         // ---- state operand of every chunk: bf16(2^{cvec} * S_enter), MN-major [channel][value] -------------------
         const uint32_t st_off[4] = {(uint32_t)OFF_ST, (uint32_t)OFF_RG, (uint32_t)(OFF_RG + 64 * 128), (uint32_t)OFF_V};
         for (int dir = dir_first; dir <= dir_last; ++dir) {
@@ -710,8 +703,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         __syncwarp();
         if (warp == 0) waiter.wait(bar_x, item_count & 1u);
         __syncthreads();
-        TC_STAMP2(4);
-        if (tid == 0 && blockIdx.x == 1 && item_count < 8) { TC_STAMP2(5); }
         ++item_count;
     }
 
@@ -738,10 +729,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         }
     }
     if (!FUSED) break;
-#ifdef VIG_TC_TIMING
-    if (tid == 0 && blockIdx.x == 1 && item_count >= 1 && item_count <= 8) g_tc_timing[512 + (item_count - 1) * 16 + 6] = clock64();
-    if (tid == 0 && blockIdx.x == 1 && item_count >= 1 && item_count <= 8) g_tc_timing[512 + (item_count - 1) * 16 + 7] = last_arrival_dbg;
-#endif
     tc_fence_before();                            // the accumulators are read out before the next item overwrites them
     __syncthreads();
     }                                             // work items

@@ -31,9 +31,11 @@ def _workspace(nbytes, device):
 
 def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_logit_normalizer=0.0, clamp_min=None,
            init_state_fwd=None, init_state_bwd=None, output_final_state=False, output_logdecay=False,
-           dir_mask=3, impl=_lib.IMPL_AUTO, want_output=True):
+           dir_mask=3, impl=_lib.IMPL_AUTO, want_output=True, status=None):
     """o_t = out_scale * scale * q_t (S^f_t + S^b_t) with separate forward / backward log-gates.
 
+    ``status``: optional int32 CUDA tensor of one element; kernels OR error bits into it (bit 0: a bounded wait
+    ran out, bit 1: a chunk's cumulative gate left the range of the tensor-core factorisation).
     Returns ``o`` or ``(o, extras)`` where ``extras`` holds ``final_fwd/final_bwd`` ([B,H,dk,dv] fp32) and
     ``logdecay_fwd/logdecay_bwd`` ([B,H,dk] fp32) when requested.
     """
@@ -79,7 +81,7 @@ def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_log
         _lib.ptr(init_state_fwd), _lib.ptr(init_state_bwd),
         _lib.ptr(extras.get("final_fwd")), _lib.ptr(extras.get("final_bwd")),
         _lib.ptr(extras.get("logdecay_fwd")), _lib.ptr(extras.get("logdecay_bwd")),
-        dir_mask, impl, _lib.ptr(ws), ws.numel() if ws is not None else 0, None, _lib.stream_ptr())
+        dir_mask, impl, _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.ptr(status), _lib.stream_ptr())
     _lib.check(st, "vig_bigla_fwd")
     if extras:
         return out, extras
