@@ -102,6 +102,26 @@ VIG_API int vig_bigla_fwd(const void* q, const void* k, const void* v, const voi
                   void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
 
 /*
+ * Backward of vig_bigla_fwd with log-space gates, no initial states: gradients of q, k, v and, per direction,
+ * e = dq*q - dk*k, from which the gate gradients follow by a cumulative sum over the tokens
+ * (dg_fwd[t] = sum_{s >= t} e_fwd[s], dg_bwd[t] = sum_{s <= t} e_bwd[s]; the reference takes the same sum in
+ * PyTorch, flash-linear-attention/fla/ops/gla/chunk_fuse.py:506-516).  Replaces FusedChunkGLAFunction.backward
+ * (chunk_fuse.py:413-518) for the merged bidirectional operator, i.e. the training path of
+ * classification/models/vig.py:407-426 without the flipped copies.  fp32 arithmetic for every dtype.
+ * q, k, g_*: [B,H,L,dk], v, d_out: [B,H,L,dv] with (b,h,l) element strides (NULL = contiguous); dq, dk, dv
+ * (input dtype) and e_fwd, e_bwd (fp32) are contiguous [B,H,L,d].  dk in {16,32,64}, dv in {32,64,128}
+ * (dk = 64 with dv = 128 included, dk = 16 only with dv = 32).
+ */
+VIG_API size_t vig_bigla_bwd_workspace_bytes(int B, int H, int L, int dk, int dv);
+VIG_API int vig_bigla_bwd(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, const void* d_out,
+                  void* dq, void* dk_out, void* dv_out, float* e_fwd, float* e_bwd,
+                  int B, int H, int L, int dk, int dv, int dtype,
+                  const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
+                  const int64_t* strides_gf, const int64_t* strides_gb, const int64_t* strides_do,
+                  float scale, float out_scale, int dir_mask,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Bi-GLA forward for callers that cannot allocate device memory (no counterpart in the reference: its
  * operators allocate their temporaries through PyTorch on every call).
  *

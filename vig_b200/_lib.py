@@ -23,6 +23,8 @@ _SIGNATURES = {
     "vig_bigla_workspace_bytes": (c_size_t, [c_int] * 7),
     "vig_bigla_fwd": (c_int, [c_void_p] * 6 + [c_int] * 6 + [_P64] * 6 + [c_float] * 4 + [c_void_p] * 6 +
                       [c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "vig_bigla_bwd_workspace_bytes": (c_size_t, [c_int] * 5),
+    "vig_bigla_bwd": (c_int, [c_void_p] * 11 + [c_int] * 6 + [_P64] * 6 + [c_float, c_float, c_int, c_void_p, c_size_t, c_void_p]),
     "vig_bigla_noalloc_scratch_bytes": (c_size_t, []),
     "vig_bigla_fwd_noalloc": (c_int, [c_void_p] * 6 + [c_int] * 6 + [_P64] * 6 + [c_float] * 4 + [c_int, c_void_p, c_void_p]),
     "vig_dwconv3x3_fwd": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_void_p]),

@@ -4,7 +4,8 @@
 ``fused_chunk_gla`` mirrors ``fla/ops/gla/chunk_fuse.py:554-572`` and ``chunk_gla``
 ``fla/ops/gla/chunk.py:561-580``; ``bi_gla`` is the explicit form of the merged operator.
 Tensors are ``[B, H, L, d]`` views with a contiguous last dimension; no copies are made.
-Forward only (inference): the autograd backward of the reference is not part of this path.
+``bi_gla`` and the one-direction entry points are differentiable (``vig_bigla_bwd``); the block's other kernels
+are inference-only.
 """
 import math
 
@@ -40,6 +41,12 @@ def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_log
     ``logdecay_fwd/logdecay_bwd`` ([B,H,dk] fp32) when requested.
     """
     _lib.require_cuda(q, k, v, g_fwd, g_bwd)
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g_fwd, g_bwd)):
+        if (init_state_fwd is not None or init_state_bwd is not None or output_final_state or output_logdecay
+                or out is not None or not want_output):
+            raise NotImplementedError("the differentiable form takes no states and allocates its own output")
+        return _BiGLAFunction.apply(q, k, v, g_fwd, g_bwd, float(scale if scale is not None else -1), float(out_scale),
+                                    float(gate_logit_normalizer), clamp_min, dir_mask, impl)
     B, H, L, dk = k.shape
     dv = v.shape[-1]
     code = _lib.dtype_code(k)
@@ -86,6 +93,70 @@ def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_log
     if extras:
         return out, extras
     return out
+
+
+def bi_gla_backward(q, k, v, g_fwd, g_bwd, d_out, scale=-1, out_scale=1.0, dir_mask=3):
+    """Gradients of ``bi_gla`` with log-space gates: ``(dq, dk, dv, dg_fwd, dg_bwd)`` (``None`` for a direction that
+    is masked out).  The kernels deliver ``e = dq*q - dk*k`` per direction; the gate gradients are its cumulative
+    sums over the tokens (``fla/ops/gla/chunk_fuse.py:506-516`` does the same in PyTorch)."""
+    _lib.require_cuda(q, k, v, d_out)
+    B, H, L, dk = k.shape
+    dv = v.shape[-1]
+    dev = k.device
+    dq, dk_, dv_ = (torch.empty(B, H, L, d, dtype=k.dtype, device=dev) for d in (dk, dk, dv))
+    e_f = torch.empty(B, H, L, dk, dtype=torch.float32, device=dev) if dir_mask & 1 else None
+    e_b = torch.empty(B, H, L, dk, dtype=torch.float32, device=dev) if dir_mask & 2 else None
+    L_ = _lib.lib()
+    nbytes = L_.vig_bigla_bwd_workspace_bytes(B, H, L, dk, dv)
+    ws = _workspace(nbytes, dev)
+    s3 = lambda t: None if t is None else _lib.strides3(t)
+    st = L_.vig_bigla_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(d_out),
+                          _lib.ptr(dq), _lib.ptr(dk_), _lib.ptr(dv_), _lib.ptr(e_f), _lib.ptr(e_b),
+                          B, H, L, dk, dv, _lib.dtype_code(k), s3(q), s3(k), s3(v), s3(g_fwd), s3(g_bwd), s3(d_out),
+                          float(scale if scale is not None else -1), float(out_scale), dir_mask,
+                          _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream_ptr())
+    _lib.check(st, "vig_bigla_bwd")
+    dg_f = e_f.flip(2).cumsum(2).flip(2) if e_f is not None else None
+    dg_b = e_b.cumsum(2) if e_b is not None else None
+    return dq, dk_, dv_, dg_f, dg_b
+
+
+class _BiGLAFunction(torch.autograd.Function):
+    """Differentiable ``bi_gla``: forward through ``vig_bigla_fwd``, backward through ``vig_bigla_bwd``.  Raw gate
+    logits are turned into log-gates here so that one backward kernel serves both forms."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g_fwd, g_bwd, scale, out_scale, gate_norm, clamp_min, dir_mask, impl):
+        def to_log(x):
+            if x is None:
+                return None, None
+            g = torch.nn.functional.logsigmoid(x.float()) / gate_norm if gate_norm > 0 else x.float()
+            if clamp_min is not None:
+                g = torch.clamp_min(g, clamp_min)
+            return g.to(x.dtype), g
+        gf, gf32 = to_log(g_fwd)
+        gb, gb32 = to_log(g_bwd)
+        with torch.no_grad():
+            o = bi_gla(q, k, v, gf, gb, scale=scale, out_scale=out_scale, dir_mask=dir_mask, impl=impl)
+        ctx.save_for_backward(q, k, v, g_fwd, g_bwd, gf, gb)
+        ctx.cfg = (scale, out_scale, gate_norm, clamp_min, dir_mask)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, x_f, x_b, gf, gb = ctx.saved_tensors
+        scale, out_scale, gate_norm, clamp_min, dir_mask = ctx.cfg
+        dq, dk, dv, dg_f, dg_b = bi_gla_backward(q, k, v, gf, gb, d_out.contiguous(), scale, out_scale, dir_mask)
+
+        def through_gate(dg, x, g):
+            if dg is None or x is None:
+                return None
+            if clamp_min is not None:
+                dg = dg * (g.float() > clamp_min)
+            if gate_norm > 0:                                       # d logsigmoid(x) / dx = sigmoid(-x)
+                dg = dg * torch.sigmoid(-x.float()) / gate_norm
+            return dg.to(x.dtype)
+        return dq, dk, dv, through_gate(dg_f, x_f, gf), through_gate(dg_b, x_b, gb), None, None, None, None, None, None
 
 
 def bi_gla_noalloc(q, k, v, g_fwd, g_bwd, out, scale=-1, out_scale=1.0, gate_logit_normalizer=0.0, clamp_min=None,
