@@ -194,7 +194,8 @@ def main():
     timing = {"on": False}
     orig = {n: getattr(vops, n) for n in ("bi_gla", "dwconv3x3", "gate_inject", "add_rmsnorm", "swiglu")}
     L = (size // 16) ** 2
-    scan_launches = 3 if L > 64 else 1
+    nseg = (L + 255) // 256                       # 256-token segments of the tensor-core scan
+    scan_launches = 1 if nseg == 1 or 8 <= nseg <= 32 else 3   # one persistent launch, or states + scan + outputs
 
     def wrap(name, n_launch):
         fn = orig[name]

@@ -50,9 +50,11 @@ extern "C" {
 #define VIG_IMPL_AUTO 0
 #define VIG_IMPL_SIMT 1
 #define VIG_IMPL_TC 2
-#define VIG_IMPL_TC_SINGLE 3 /* tensor-core path as ONE persistent launch for multi-segment sequences (experimental:
-                               needs ~20 MB more workspace and as many co-resident CTAs as a sequence has segments;
-                               falls back to the three-launch form when either is missing) */
+#define VIG_IMPL_TC_SINGLE 3 /* tensor-core path as ONE persistent launch for multi-segment sequences: half the DRAM
+                               traffic, ~20 MB more workspace, needs as many co-resident CTAs as a sequence has
+                               256-token segments (falls back to three launches when either is missing).  AUTO and TC
+                               pick it for sequences of 2048..8192 tokens, where it is the faster form. */
+#define VIG_IMPL_TC_SPLIT 4  /* tensor-core path as three launches (segment states, scan, outputs) at every length */
 
 VIG_API int vig_version(void);
 VIG_API const char* vig_strerror(int status);

@@ -26,10 +26,26 @@ static bool dims_ok(int dk, int dv) {
     return (dk == 16 || dk == 32 || dk == 64 || dk == 128) && (dv == 32 || dv == 64 || dv == 128);
 }
 
+namespace vig {
+size_t bigla_workspace_internal(int B, int H, int L, int dk, int dv, int dtype, int impl, bool no_single);
+int bigla_fwd_internal(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, void* o,
+                       int B, int H, int L, int dk, int dv, int dtype,
+                       const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
+                       const int64_t* strides_gf, const int64_t* strides_gb, const int64_t* strides_o,
+                       float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
+                       const float* init_state_fwd, const float* init_state_bwd, float* final_state_fwd, float* final_state_bwd,
+                       float* total_logdecay_fwd, float* total_logdecay_bwd, int dir_mask, int impl, bool no_single,
+                       void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+}
+
 extern "C" size_t vig_bigla_workspace_bytes(int B, int H, int L, int dk, int dv, int dtype, int impl) {
+    return bigla_workspace_internal(B, H, L, dk, dv, dtype, impl, false);
+}
+
+size_t vig::bigla_workspace_internal(int B, int H, int L, int dk, int dv, int dtype, int impl, bool no_single) {
     if (B <= 0 || H <= 0 || L <= 0 || !dims_ok(dk, dv)) return 0;
     size_t simt = bigla_simt_workspace(B, H, L, dk, dv);
-    size_t tc = (dtype != VIG_DTYPE_F32 && impl != VIG_IMPL_SIMT) ? bigla_tc_workspace(B, H, L, dk, dv, impl != VIG_IMPL_TC_SINGLE) : 0;
+    size_t tc = (dtype != VIG_DTYPE_F32 && impl != VIG_IMPL_SIMT) ? bigla_tc_workspace(B, H, L, dk, dv, no_single || !(impl == VIG_IMPL_TC_SINGLE || (impl != VIG_IMPL_TC_SPLIT && bigla_tc_prefers_single(L)))) : 0;
     return simt > tc ? simt : tc;
 }
 
@@ -48,10 +64,24 @@ extern "C" int vig_bigla_fwd(const void* q, const void* k, const void* v, const 
                              float* total_logdecay_fwd, float* total_logdecay_bwd,
                              int dir_mask, int impl,
                              void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream) {
+    return bigla_fwd_internal(q, k, v, g_fwd, g_bwd, o, B, H, L, dk, dv, dtype, strides_q, strides_k, strides_v, strides_gf,
+                              strides_gb, strides_o, scale, out_scale, gate_logit_normalizer, clamp_min, init_state_fwd,
+                              init_state_bwd, final_state_fwd, final_state_bwd, total_logdecay_fwd, total_logdecay_bwd,
+                              dir_mask, impl, false, workspace, workspace_bytes, status_dev, stream);
+}
+
+int vig::bigla_fwd_internal(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, void* o,
+                            int B, int H, int L, int dk, int dv, int dtype,
+                            const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
+                            const int64_t* strides_gf, const int64_t* strides_gb, const int64_t* strides_o,
+                            float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
+                            const float* init_state_fwd, const float* init_state_bwd, float* final_state_fwd, float* final_state_bwd,
+                            float* total_logdecay_fwd, float* total_logdecay_bwd, int dir_mask, int impl, bool no_single,
+                            void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream) {
     if (dtype < 0 || dtype > 2) return VIG_ERR_DTYPE;
     if (B < 0 || H <= 0 || L < 0 || !dims_ok(dk, dv)) return VIG_ERR_SHAPE;
     if (dir_mask < 1 || dir_mask > 3) return VIG_ERR_ARG;
-    if (impl < VIG_IMPL_AUTO || impl > VIG_IMPL_TC_SINGLE) return VIG_ERR_ARG;
+    if (impl < VIG_IMPL_AUTO || impl > VIG_IMPL_TC_SPLIT) return VIG_ERR_ARG;
     if (B == 0 || L == 0) return VIG_OK;
     if (!k || !v) return VIG_ERR_NULL;
     if (o && !q) return VIG_ERR_NULL;
@@ -76,18 +106,19 @@ extern "C" int vig_bigla_fwd(const void* q, const void* k, const void* v, const 
     p.dir_mask = dir_mask; p.status = status_dev;
 
     bool use_tc = false;
-    if (impl == VIG_IMPL_TC || impl == VIG_IMPL_TC_SINGLE) {
+    if (impl == VIG_IMPL_TC || impl == VIG_IMPL_TC_SINGLE || impl == VIG_IMPL_TC_SPLIT) {
         if (!bigla_tc_supported(p)) return VIG_ERR_SHAPE;
         use_tc = true;
     } else if (impl == VIG_IMPL_AUTO) {
         use_tc = bigla_tc_supported(p);
     }
     if (use_tc) {
-        // the single-launch form (on request) needs the larger workspace; with only the states' worth it runs as three launches
+        // the single-launch form (on request, or by default where it is the faster one) needs the larger workspace;
+        // with only the states' worth of workspace the call runs as three launches
         const size_t need = bigla_tc_workspace(B, H, L, dk, dv, true);
         if (need && (!workspace || workspace_bytes < need)) return VIG_ERR_WORKSPACE;
         if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return VIG_ERR_ALIGN;
-        return bigla_tc_launch(p, workspace, workspace_bytes, impl == VIG_IMPL_TC_SINGLE, (cudaStream_t)stream);
+        return bigla_tc_launch(p, workspace, workspace_bytes, !no_single && (impl == VIG_IMPL_TC_SINGLE || (impl != VIG_IMPL_TC_SPLIT && bigla_tc_prefers_single(L))), (cudaStream_t)stream);
     }
     const size_t need = bigla_simt_workspace(B, H, L, dk, dv);
     const bool needs_ws = need_states || L > 64;

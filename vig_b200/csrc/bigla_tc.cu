@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 for (uint32_t i = 0; i < (1u << 21); ++i) {
                     if (ld_acquire_u32(counter) >= (uint32_t)nseg) { ok = true; break; }
                     if (*abort_flag) break;
-                    __nanosleep(64);
+                    __nanosleep(32);
                 }
                 if (!ok) { *abort_flag = 1; if (p.status) atomicOr(p.status, 1); }
             }
@@ -661,25 +661,27 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         group_wait(scanned);                      // every slice of the entering states is in place
         // ---- state operand of every chunk: bf16(2^{cvec} * S_enter), MN-major [channel][value] -------------------
         const uint32_t st_off[4] = {(uint32_t)OFF_ST, (uint32_t)OFF_RG, (uint32_t)(OFF_RG + 64 * 128), (uint32_t)OFF_V};
-        for (int dir = dir_first; dir <= dir_last; ++dir) {
-            if (st_thread) {
-                const float4* src = reinterpret_cast<const float4*>(p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV + st_row * DV + st_col0);
+        float4 enter[2][4];                       // both directions' entering states are requested before either is used
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float4 t4 = __ldcg(src + j);
-                    S[4 * j] = t4.x; S[4 * j + 1] = t4.y; S[4 * j + 2] = t4.z; S[4 * j + 3] = t4.w;
-                }
-            }
+        for (int dir = 0; dir < 2; ++dir) {
+            const float4* src = reinterpret_cast<const float4*>(p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV + (st_row & (DK - 1)) * DV + st_col0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) enter[dir][j] = (p.dir_mask & (1 << dir)) ? __ldcg(src + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int dir = 0; dir < 2; ++dir) {
+            if (!(p.dir_mask & (1 << dir))) continue;
             for (int ci = 0; ci < nch; ++ci) {
                 const int n = (dir - dir_first) * nch + ci;
                 if (st_thread) {
                     const float eg = ex2(cvec[n * 64 + st_row]);
 #pragma unroll
-                    for (int j = 0; j < 16; j += 8) {
+                    for (int j = 0; j < 4; j += 2) {
+                        const float4 a = enter[dir][j], b2 = enter[dir][j + 1];
                         uint4 w;
-                        w.x = Pack2<T>::pack(S[j] * eg, S[j + 1] * eg); w.y = Pack2<T>::pack(S[j + 2] * eg, S[j + 3] * eg);
-                        w.z = Pack2<T>::pack(S[j + 4] * eg, S[j + 5] * eg); w.w = Pack2<T>::pack(S[j + 6] * eg, S[j + 7] * eg);
-                        *reinterpret_cast<uint4*>(smem + st_off[n] + swz(st_row, (st_col0 + j) * 2)) = w;
+                        w.x = Pack2<T>::pack(a.x * eg, a.y * eg); w.y = Pack2<T>::pack(a.z * eg, a.w * eg);
+                        w.z = Pack2<T>::pack(b2.x * eg, b2.y * eg); w.w = Pack2<T>::pack(b2.z * eg, b2.w * eg);
+                        *reinterpret_cast<uint4*>(smem + st_off[n] + swz(st_row, (st_col0 + 4 * j) * 2)) = w;
                     }
                 }
             }
@@ -859,6 +861,14 @@ extern "C" __attribute__((visibility("default"))) int vig_dbg_tc_timing(long lon
     return (int)cudaMemcpyFromSymbol(host_out, g_tc_timing, sizeof(long long) * 64 * 16);
 }
 #endif
+
+// Measured on B200: the single-launch form wins for sequences of 8..32 segments (2048..8192 tokens) and halves
+// the DRAM traffic there; shorter sequences have too few segments to amortise the two group barriers, longer
+// ones make every CTA wait for too many others.
+bool bigla_tc_prefers_single(int L) {
+    const int nseg = (L + SEG - 1) / SEG;
+    return nseg >= 8 && nseg <= 32;
+}
 
 bool bigla_tc_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;

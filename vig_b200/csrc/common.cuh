@@ -85,5 +85,6 @@ int bigla_scan_launch(const BiglaParams& p, cudaStream_t stream);
 int bigla_tc_launch(const BiglaParams& p, void* ws, size_t ws_bytes, bool allow_fused, cudaStream_t stream);
 size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv, bool split_only);
 bool bigla_tc_supported(const BiglaParams& p);
+bool bigla_tc_prefers_single(int L);
 
 }  // namespace vig

@@ -11,6 +11,18 @@
 
 using namespace vig;
 
+namespace vig {
+size_t bigla_workspace_internal(int B, int H, int L, int dk, int dv, int dtype, int impl, bool no_single);
+int bigla_fwd_internal(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, void* o,
+                       int B, int H, int L, int dk, int dv, int dtype,
+                       const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
+                       const int64_t* strides_gf, const int64_t* strides_gb, const int64_t* strides_o,
+                       float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
+                       const float* init_state_fwd, const float* init_state_bwd, float* final_state_fwd, float* final_state_bwd,
+                       float* total_logdecay_fwd, float* total_logdecay_bwd, int dir_mask, int impl, bool no_single,
+                       void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+}
+
 // The per-segment states and summed log-gates of one call (what `workspace` holds in vig_bigla_fwd).
 static __device__ __align__(256) unsigned char g_bigla_scratch[VIG_NOALLOC_SCRATCH_BYTES];
 
@@ -48,15 +60,15 @@ extern "C" int vig_bigla_fwd_noalloc(const void* q, const void* k, const void* v
                                      float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
                                      int impl, int32_t* status_dev, void* stream) {
     if (!o) return VIG_ERR_NULL;
-    if (impl == VIG_IMPL_TC_SINGLE) impl = VIG_IMPL_TC;   // the single-launch form needs more scratch than this array holds
-    const size_t need = vig_bigla_workspace_bytes(B, H, L, dk, dv, dtype, impl);
+    // the single-launch form of the tensor-core path needs more scratch than this array holds: it is ruled out here
+    const size_t need = bigla_workspace_internal(B, H, L, dk, dv, dtype, impl, true);
     if (need > VIG_NOALLOC_SCRATCH_BYTES) return VIG_ERR_SCRATCH_LIMIT;
     void* scratch = nullptr;
     if (int st = scratch_for_current_device(&scratch)) return st;
     // Every workspace slot a call reads is written earlier in the same call, so nothing needs clearing
     // between calls; what the previous call left behind is simply overwritten.
-    return vig_bigla_fwd(q, k, v, g_fwd, g_bwd, o, B, H, L, dk, dv, dtype, strides_q, strides_k, strides_v, strides_gf,
-                         strides_gb, strides_o, scale, out_scale, gate_logit_normalizer, clamp_min,
-                         nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 3, impl,
-                         scratch, VIG_NOALLOC_SCRATCH_BYTES, status_dev, stream);
+    return bigla_fwd_internal(q, k, v, g_fwd, g_bwd, o, B, H, L, dk, dv, dtype, strides_q, strides_k, strides_v, strides_gf,
+                              strides_gb, strides_o, scale, out_scale, gate_logit_normalizer, clamp_min,
+                              nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 3, impl, true,
+                              scratch, VIG_NOALLOC_SCRATCH_BYTES, status_dev, stream);
 }
