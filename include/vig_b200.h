@@ -202,6 +202,19 @@ VIG_API int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const voi
 VIG_API int vig_swiglu_fwd(const void* gate, const void* y, void* out, int64_t rows, int I,
                    int64_t ld_in, int64_t ld_out, int dtype, void* stream);
 
+/*
+ * Gate projection of the SwiGLU MLP fused with its activation (tcgen05 GEMM, bf16 / fp16):
+ *   out[M, I] = silu(x Wg^T) * (x Wy^T),   W = [Wg ; Wy] of shape [2I, K] (row-major, rows contiguous)
+ * Replaces `gate_proj` -> chunk(2) -> `swiglu` of GLAMLP.forward (classification/models/vig.py:494-497,
+ * flash-linear-attention/fla/modules/activations.py:109-113) so that the [M, 2I] intermediate is never written.
+ * x: [M, K] with row stride ldx, out: [M, I] with row stride ldo (elements).  K % 64 == 0, I % 64 == 0,
+ * K <= 384 (one 128-row tile of x stays resident in shared memory); vig_linear_swiglu_supported tells.
+ */
+VIG_API int vig_linear_swiglu_supported(int64_t M, int K, int I, int dtype);
+VIG_API int vig_linear_swiglu_preferred(int64_t M, int K, int I, int dtype);   /* supported AND faster than GEMM + SwiGLU */
+VIG_API int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo,
+                          int64_t M, int K, int I, int dtype, int32_t* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

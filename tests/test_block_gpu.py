@@ -106,6 +106,21 @@ def test_swiglu(dtype):
     assert rel_err(out.float(), ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,I", [(392, 192, 512), (1000, 384, 1024), (128, 64, 64), (70, 192, 128), (5000, 192, 512)])
+def test_linear_swiglu_fused_gemm(dtype, M, K, I):
+    import vig_b200
+    g = torch.Generator().manual_seed(M + K)
+    x = torch.randn(2, M // 2, K, generator=g).to(dtype)
+    w = (torch.randn(2 * I, K, generator=g) / K ** 0.5).to(dtype)
+    gy = x.float() @ w.float().t()
+    ref = oracle.swiglu(*gy.chunk(2, -1))
+    assert vig_b200.ops.linear_swiglu_supported(x.cuda(), w.cuda())
+    out = vig_b200.linear_swiglu(x.cuda(), w.cuda())
+    assert out.shape == (2, M // 2, I)
+    assert rel_err(out.float(), ref) < TOL[dtype]
+
+
 def _shape(preset):
     base = oracle.PRESETS[preset]
     return oracle.ViGShape(**{**base.__dict__, "depth": 2, "num_classes": 16})

@@ -117,6 +117,9 @@ class GLAMLP(nn.Module):
         self.down_proj = nn.Linear(intermediate_size, hidden_size, bias=False)
 
     def forward(self, x):
+        if ops.linear_swiglu_supported(x, self.gate_proj.weight, preferred=True):
+            # gate projection and SwiGLU in one tensor-core kernel: the [.., 2I] intermediate never reaches HBM
+            return F.linear(ops.linear_swiglu(x, self.gate_proj.weight), self.down_proj.weight, self.down_proj.bias)
         y = self.gate_proj(x)
         gate, y = y.chunk(2, -1)
         return ops.swiglu_linear(gate, y, self.down_proj.weight, self.down_proj.bias)

@@ -300,6 +300,32 @@ def swiglu(gate, y):
     return out
 
 
+def linear_swiglu_supported(x, weight, preferred=False):
+    """True when ``linear_swiglu`` has a fused kernel for this input (bf16 / fp16, K % 64 == 0, K <= 384, I % 64 == 0);
+    with ``preferred`` also that it beats the library GEMM followed by the SwiGLU kernel (K <= 192)."""
+    if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or weight.dtype != x.dtype:
+        return False
+    K, I = x.shape[-1], weight.shape[0] // 2
+    L_ = _lib.lib()
+    fn = L_.vig_linear_swiglu_preferred if preferred else L_.vig_linear_swiglu_supported
+    return weight.is_contiguous() and bool(fn(x.numel() // K, K, I, _lib.dtype_code(x)))
+
+
+def linear_swiglu(x, weight):
+    """``swiglu(*F.linear(x, weight).chunk(2, -1))`` in one tensor-core kernel (``GLAMLP.forward``, ``vig.py:494-497``):
+    ``weight`` is the ``[2I, K]`` gate projection, the result is ``[..., I]``."""
+    _lib.require_cuda(x, weight)
+    K, I = x.shape[-1], weight.shape[0] // 2
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty(*x.shape[:-1], I, dtype=x.dtype, device=x.device)
+    st = _lib.lib().vig_linear_swiglu_fwd(_lib.ptr(x2), x2.stride(0), _lib.ptr(weight), _lib.ptr(out), I, x2.shape[0], K, I,
+                                          _lib.dtype_code(x), None, _lib.stream_ptr())
+    _lib.check(st, "vig_linear_swiglu_fwd")
+    return out
+
+
 def swiglu_linear(x, y, weight, bias):
     """``fla/modules/activations.py:150-174``: ``F.linear(swiglu(x, y), weight, bias)``."""
     return torch.nn.functional.linear(swiglu(x, y), weight, bias)
