@@ -195,6 +195,14 @@ VIG_API int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const voi
                           int64_t rows, int N, float eps, int act_swish, int dtype, void* stream);
 
 /*
+ * Space-to-depth of the input image for the stem's first convolution (`V2PatchEmbed`, classification/models/vig.py:
+ * 650-651: kernel s+1, stride s, padding 1), which is then a 2x2 convolution over s x s pixel blocks:
+ * cells[b, cy, cx, (dy*s + dx)*Cin + ic] = x[b, ic, s*cy + dy - 1, s*cx + dx - 1], zero outside the image.
+ * x: [B, Cin, H, W] contiguous, cells: [B, H/s + 1, W/s + 1, s*s*Cin] contiguous; H, W multiples of s; s*Cin = 24.
+ */
+VIG_API int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream);
+
+/*
  * SwiGLU: out = gate * sigmoid(gate) * y (fla/modules/activations.py:109-113, the `swiglu` half of
  * `swiglu_linear`).  gate, y: [rows, I] with row stride ld_in elements (gate and y are the two halves of
  * one [rows, 2I] projection in the reference, vig.py:494-497); out: [rows, I] with row stride ld_out.

@@ -78,6 +78,22 @@ def test_layernorm_act(dtype, N, act):
     assert rel_err(y.float(), ref) < TOL[dtype]
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("B,H,W", [(2, 32, 48), (1, 8, 8), (3, 224, 224)])
+def test_stem_unfold(dtype, B, H, W):
+    """Pad + space-to-depth gather against the same rearrangement written with pad / view / permute."""
+    import torch.nn.functional as F
+    import vig_b200
+    s, Cin = 8, 3
+    g = torch.Generator().manual_seed(H + W)
+    x = torch.randn(B, Cin, H, W, generator=g).to(dtype)
+    xp = F.pad(x.permute(0, 2, 3, 1), (0, 0, 1, s - 1, 1, s - 1))
+    ref = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
+    got = vig_b200.ops.stem_unfold(x.cuda(), s).cpu()
+    assert torch.equal(got, ref)
+
+
 def test_patch_embed_matches_oracle():
     import vig_b200
     shape = oracle.ViGShape(192, 3, 1, 0.5, 1.0, True, True, num_classes=16)

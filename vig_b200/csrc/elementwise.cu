@@ -161,6 +161,69 @@ __global__ void __launch_bounds__(EW_THREADS) add_rmsnorm_kernel(const T* __rest
 // ---------------------------------------------------------------------------------------------------
 // LayerNorm over the last dimension with affine parameters and an optional swish: the two LayerNorm2d
 // stages of the patch-embedding stem on channels-last activations.  One warp per row, row in registers.
+// Rows of at most 16 vectors (N <= 128 for 2-byte types): LPR = 8 or 16 lanes per row, several rows per warp.
+template <typename T, int LPR>
+__global__ void __launch_bounds__(EW_THREADS) layernorm_act_short_kernel(const T* __restrict__ x, const T* __restrict__ pre_bias,
+                                                                         const T* __restrict__ w, const T* __restrict__ bias,
+                                                                         T* __restrict__ y, int64_t rows, int N, float eps, int act) {
+    constexpr int V = DType<T>::VEC;
+    const int sub = threadIdx.x % LPR;
+    const int nv = N / V;
+    const int64_t g0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+    const int64_t ng = ((int64_t)gridDim.x * blockDim.x) / LPR;
+    const bool active = sub < nv;
+    float wf[V], bf[V], pf[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { wf[i] = 0.f; bf[i] = 0.f; pf[i] = 0.f; }
+    if (active) {
+        Vec16<T> t; t.load_nc(w + sub * V); t.to_float(wf); t.load_nc(bias + sub * V); t.to_float(bf);
+        if (pre_bias) { t.load_nc(pre_bias + sub * V); t.to_float(pf); }
+    }
+    constexpr int U = 2;                                                   // rows in flight per lane group
+    for (int64_t r0 = g0; r0 < rows; r0 += U * ng) {
+        float val[U][V];
+        Vec16<T> xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (active && r0 + u * ng < rows) xv[u].load_nc(x + (r0 + u * ng) * N + sub * V);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t r = r0 + u * ng;
+            const bool on = active && r < rows;
+            float sum = 0.f;
+            if (on) {
+                xv[u].to_float(val[u]);
+                if (pre_bias) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[u][i] = DType<T>::to_f(DType<T>::from_f(val[u][i] + pf[i]));
+                }
+#pragma unroll
+                for (int i = 0; i < V; ++i) sum += val[u][i];
+            }
+#pragma unroll
+            for (int m = LPR / 2; m >= 1; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+            const float mean = sum / (float)N;
+            float ss = 0.f;
+            if (on) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) { const float d = val[u][i] - mean; ss = fmaf(d, d, ss); }
+            }
+#pragma unroll
+            for (int m = LPR / 2; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
+            const float rstd = rsqrtf(ss / (float)N + eps);
+            if (on) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    float t = (val[u][i] - mean) * rstd * wf[i] + bf[i];
+                    if (act) t = __fdividef(t, 1.f + __expf(-t));
+                    val[u][i] = t;
+                }
+                Vec16<T> ov; ov.from_float(val[u]); ov.store(y + r * N + sub * V);
+            }
+        }
+    }
+}
+
 template <typename T, int MAXV>
 __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __restrict__ x, const T* __restrict__ pre_bias,
                                                                    const T* __restrict__ w, const T* __restrict__ bias,
@@ -242,6 +305,55 @@ __global__ void __launch_bounds__(EW_THREADS) swiglu_kernel(const T* __restrict_
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Space-to-depth of the input image for the stem's first convolution (kernel s+1, stride s, padding 1, evaluated
+// as a 2x2 convolution over s x s pixel blocks): x [B, Cin, H, W]  ->  cells [B, H/s + 1, W/s + 1, s*s*Cin] with
+// cells[b, cy, cx, (dy*s + dx)*Cin + ic] = x[b, ic, s*cy + dy - 1, s*cx + dx - 1] (zero outside the image).
+// A block owns up to UNFOLD_CELLS consecutive cells of one cell row: it stages the 8 image rows x Cin planes that
+// those cells cover in shared memory with aligned 16-byte loads (each image byte is read once, apart from one
+// 8-pixel overlap between neighbouring blocks), then writes the cells, which are contiguous in memory, as 16-byte
+// vectors gathered from the staged tile.
+constexpr int UNFOLD_S = 8, UNFOLD_CIN = 3, UNFOLD_CELLS = 32;
+constexpr int UNFOLD_TW = UNFOLD_S * (UNFOLD_CELLS + 1);                 // staged pixels per row: 8 before the first cell
+
+template <typename T>
+__global__ void __launch_bounds__(EW_THREADS) stem_unfold_kernel(const T* __restrict__ x, T* __restrict__ cells,
+                                                                 int H, int W, int nseg) {
+    constexpr int V = DType<T>::VEC, S = UNFOLD_S, C = UNFOLD_CIN;
+    constexpr int CELL = S * S * C;                                       // 192 values per cell
+    __shared__ __align__(16) T tile[S][C][UNFOLD_TW];
+    const int ch = H / S + 1, cw = W / S + 1;
+    int blk = blockIdx.x;
+    const int seg = blk % nseg; blk /= nseg;
+    const int cy = blk % ch;
+    const int b = blk / ch;
+    const int cx0 = seg * UNFOLD_CELLS;
+    const int ncell = min(UNFOLD_CELLS, cw - cx0);
+    const int px0 = S * cx0 - S;                                          // image x of staged column 0
+    constexpr int VPR = UNFOLD_TW / V;                                    // vectors per staged row
+    for (int i = threadIdx.x; i < S * C * VPR; i += EW_THREADS) {
+        const int j = i % VPR, ic = (i / VPR) % C, dy = i / (VPR * C);
+        const int y = S * cy + dy - 1, xx = px0 + j * V;
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (y >= 0 && y < H && xx >= 0 && xx < W)                         // W is a multiple of 8: a vector is all in or all out
+            val = __ldg(reinterpret_cast<const uint4*>(x + (((size_t)b * C + ic) * H + y) * W + xx));
+        *reinterpret_cast<uint4*>(&tile[dy][ic][j * V]) = val;
+    }
+    __syncthreads();
+    T* dst = cells + (((size_t)b * ch + cy) * cw + cx0) * CELL;
+    for (int vi = threadIdx.x; vi < ncell * CELL / V; vi += EW_THREADS) {
+        alignas(16) T vals[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const int e = vi * V + i;
+            const int cell = e / CELL, r = e % CELL;
+            const int dy = r / (S * C), dx = (r % (S * C)) / C, ic = r % C;
+            vals[i] = tile[dy][ic][S * cell + dx + S - 1];
+        }
+        reinterpret_cast<uint4*>(dst)[vi] = *reinterpret_cast<const uint4*>(vals);
+    }
+}
+
 inline int grid_for(int64_t items, int per_block) {
     int64_t g = (items + per_block - 1) / per_block;
     const int64_t cap = 148 * 16;       // 148 SMs x resident CTAs; the kernels are grid-stride
@@ -294,6 +406,13 @@ int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b,
     constexpr int V = DType<T>::VEC;
     if (N % V) return VIG_ERR_SHAPE;
     const int nv = N / V;
+    if (nv <= 16) {
+        const int lpr = nv <= 8 ? 8 : 16;
+        const int g = grid_for(rows * lpr, EW_THREADS);
+        if (lpr == 8) layernorm_act_short_kernel<T, 8><<<g, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act);
+        else layernorm_act_short_kernel<T, 16><<<g, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act);
+        return (int)cudaGetLastError();
+    }
     const int grid = grid_for(rows * 32, EW_THREADS);
 #define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act)
     if (nv <= 32) VIG_LN(1); else if (nv <= 64) VIG_LN(2); else if (nv <= 128) VIG_LN(4);
@@ -366,6 +485,26 @@ extern "C" int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const 
     if (rows == 0) return VIG_OK;
     if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y)) return VIG_ERR_ALIGN;
     VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, y, rows, N, eps, act_swish, (cudaStream_t)stream))
+}
+
+extern "C" int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream) {
+    if (!x || !cells) return VIG_ERR_NULL;
+    if (B < 0 || Cin <= 0 || H <= 0 || W <= 0 || s <= 0 || H % s || W % s) return VIG_ERR_SHAPE;
+    if (s != UNFOLD_S || Cin != UNFOLD_CIN) return VIG_ERR_SHAPE;      // the ViG stem: 8 x 8 pixel blocks of RGB
+    if (B == 0) return VIG_OK;
+    if (!aligned16(cells) || !aligned16(x)) return VIG_ERR_ALIGN;
+    const int ch = H / s + 1, cw = W / s + 1;
+    const int nseg = (cw + UNFOLD_CELLS - 1) / UNFOLD_CELLS;
+    const int64_t blocks = (int64_t)B * ch * nseg;
+    if (blocks >= (1ll << 31)) return VIG_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case VIG_DTYPE_F32: stem_unfold_kernel<float><<<(int)blocks, EW_THREADS, 0, st>>>((const float*)x, (float*)cells, H, W, nseg); break;
+        case VIG_DTYPE_BF16: stem_unfold_kernel<__nv_bfloat16><<<(int)blocks, EW_THREADS, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)cells, H, W, nseg); break;
+        case VIG_DTYPE_F16: stem_unfold_kernel<__half><<<(int)blocks, EW_THREADS, 0, st>>>((const __half*)x, (__half*)cells, H, W, nseg); break;
+        default: return VIG_ERR_DTYPE;
+    }
+    return (int)cudaGetLastError();
 }
 
 extern "C" int vig_swiglu_fwd(const void* gate, const void* y, void* out, int64_t rows, int I, int64_t ld_in, int64_t ld_out,

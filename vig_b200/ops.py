@@ -286,6 +286,18 @@ def layernorm_act(x, weight, bias, eps=1e-5, act_swish=False, pre_bias=None):
     return y
 
 
+def stem_unfold(x, s):
+    """Space-to-depth with the first stem convolution's padding: ``[B,Cin,H,W] -> [B, H/s+1, W/s+1, s*s*Cin]``
+    (see ``vig_stem_unfold_fwd``)."""
+    _lib.require_cuda(x)
+    B, Cin, H, W = x.shape
+    x = x.contiguous()
+    cells = torch.empty(B, H // s + 1, W // s + 1, s * s * Cin, dtype=x.dtype, device=x.device)
+    st = _lib.lib().vig_stem_unfold_fwd(_lib.ptr(x), _lib.ptr(cells), B, Cin, H, W, s, _lib.dtype_code(x), _lib.stream_ptr())
+    _lib.check(st, "vig_stem_unfold_fwd")
+    return cells
+
+
 def swiglu(gate, y):
     """``fla/modules/activations.py:109-113``: ``gate * sigmoid(gate) * y``; inputs may be the two halves of one projection."""
     _lib.require_cuda(gate, y)

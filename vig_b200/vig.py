@@ -61,9 +61,13 @@ class V2PatchEmbed(nn.Module):
         B, Cin, H, W = x.shape
         if H % s or W % s or Cin * s * s % 8:
             return F.conv2d(x.contiguous(memory_format=torch.channels_last), conv.weight, None, conv.stride, conv.padding)
-        # pad one pixel before (the conv's padding) and s-1 after, then fold s x s pixels into channels
-        xp = F.pad(x.permute(0, 2, 3, 1), (0, 0, 1, s - 1, 1, s - 1))                     # [B, H+s, W+s, Cin]
-        cells = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
+        if s * Cin == 24:
+            from . import ops
+            cells = ops.stem_unfold(x, s)                                  # one gather kernel: pad + fold in a single pass
+        else:
+            # pad one pixel before (the conv's padding) and s-1 after, then fold s x s pixels into channels
+            xp = F.pad(x.permute(0, 2, 3, 1), (0, 0, 1, s - 1, 1, s - 1))                 # [B, H+s, W+s, Cin]
+            cells = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
         return F.conv2d(cells.permute(0, 3, 1, 2), self._block_weight(), None)
 
     def forward(self, x):
