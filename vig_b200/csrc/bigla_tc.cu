@@ -76,6 +76,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+// untiled bulk copies: a 16 KB operand tile to / from its parking slot in global memory
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -159,9 +166,12 @@ struct TcMaps { CUtensorMap q, k, v, gf, gb; };
 
 #ifdef VIG_TC_TIMING
 __device__ long long g_tc_timing[64 * 16];
-#define TC_STAMP(slot) do { if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 1 && n < 4) g_tc_timing[(STATES_ONLY ? 0 : 512) + n * 16 + (slot)] = clock64(); } while (0)
+#define TC_STAMP(slot) do { if (FUSED) { if (tid == 0 && blockIdx.x == 1 && item_count < 4 && n < 4) g_tc_timing[(item_count * 4 + n) * 16 + (slot)] = clock64(); } \
+    else if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 1 && n < 4) g_tc_timing[(STATES_ONLY ? 0 : 512) + n * 16 + (slot)] = clock64(); } while (0)
+#define TC_STAMPX(slot) do { if (FUSED && tid == 0 && blockIdx.x == 1 && item_count < 4) g_tc_timing[(item_count * 4 + 3) * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TC_STAMP(slot) do { } while (0)
+#define TC_STAMPX(slot) do { } while (0)
 #endif
 
 // ---------------------------------------------------------------------------------------------------
@@ -220,8 +230,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const Waiter waiter{abort_flag, p.status};
 
     if (tid == 0) {
-        mbar_init(bar_gk, 1); mbar_init(bar_q, 1); mbar_init(bar_v, 1); mbar_init(bar_p0, 1); mbar_init(bar_o, 1); mbar_init(bar_x, 1);
+        // the tensor-core barriers count two arrivals: the MMAs of a step are issued by two threads (see `issuer`)
+        mbar_init(bar_gk, 1); mbar_init(bar_q, 1); mbar_init(bar_v, 1); mbar_init(bar_p0, 2); mbar_init(bar_o, 2); mbar_init(bar_x, 2);
         *abort_flag = 0;
+        if (FUSED) *item_slot = (int)atomicAdd(p.ticket, 1u);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -288,14 +300,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
     const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + OFF_RK);
     const uint32_t* sg = reinterpret_cast<const uint32_t*>(smem + OFF_RG);
 
+    // The MMAs of a step go to two disjoint accumulators each; they are issued by two threads of different warps
+    // (issuing costs ~100 cycles per instruction), each of which commits to the step's barrier.
+    const int issuer = tid == 0 ? 0 : (tid == 128 ? 1 : -1);
+    bool s_zero = true;                           // the state entering the current chunk is exactly zero
     uint32_t it_count = 0;                        // iterations done by this CTA: parity of the per-iteration barriers
     uint32_t item_count = 0;                      // items done by this CTA: parity of bar_x
+    int next_item = 0;
     for (;;) {                                    // work items (exactly one unless FUSED)
     if (FUSED) {
-        if (tid == 0) *item_slot = (int)atomicAdd(p.ticket, 1u);
-        __syncthreads();
-        const int item = *item_slot;
-        __syncthreads();                          // everyone has read the slot before it is written again
+        const int item = *item_slot;              // drawn during the previous item (or at kernel start); the slot is
+                                                  // rewritten only after several CTA barriers
         if (item >= p.B * p.H * nseg) break;
         bh = item / nseg; seg = item % nseg;
     }
@@ -312,15 +327,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         const uint32_t par = it_count & 1u;
 
         if (ci == 0) {                            // a sweep starts: entering state of the segment, zeroed gate total
+            const float* src = nullptr;
+            if (FUSED) {                          // only the sequence's own initial state is known at this point
+                const float* init = dir ? p.init_b : p.init_f;
+                if (init && seg == (dir ? nseg - 1 : 0)) src = init + (size_t)bh * DK * DV;
+            } else if (!STATES_ONLY) {
+                if (use_ws) src = p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV;
+                else if (dir ? p.init_b : p.init_f) src = (dir ? p.init_b : p.init_f) + (size_t)bh * DK * DV;
+            }
+            s_zero = src == nullptr;              // a zero state contributes nothing: its product is not issued
             if (st_thread) {
-                const float* src = nullptr;
-                if (FUSED) {                      // only the sequence's own initial state is known at this point
-                    const float* init = dir ? p.init_b : p.init_f;
-                    if (init && seg == (dir ? nseg - 1 : 0)) src = init + (size_t)bh * DK * DV;
-                } else if (!STATES_ONLY) {
-                    if (use_ws) src = p.ws_state + (((size_t)bh * nseg + seg) * 2 + dir) * DK * DV;
-                    else if (dir ? p.init_b : p.init_f) src = (dir ? p.init_b : p.init_f) + (size_t)bh * DK * DV;
-                }
 #pragma unroll
                 for (int j = 0; j < 16; j += 4) {
                     const float4 t4 = src ? __ldg(reinterpret_cast<const float4*>(src + st_row * DV + st_col0 + j)) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -410,8 +426,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                         const float2 qq = Pack2<T>::unpack(raw[u]);
                         const uint32_t qw = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
                         *reinterpret_cast<uint32_t*>(smem + OFF_QT + swz(tok, cp * 4)) = qw;
-                        if (FUSED)                // park the operand tile (same swizzled image) for the deferred term
-                            *reinterpret_cast<uint32_t*>(p.qscratch + ((size_t)blockIdx.x * 4 + n) * TILE_B + swz(tok, cp * 4)) = qw;
+
                     }
                 }
             };
@@ -434,7 +449,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             gtot[2 * cp] += glast.x; gtot[2 * cp + 1] += glast.y;
         }
         // state operand for the inter-chunk product: bf16(exp(G_ref) * S_in), MN-major [channel][value]
-        if (!STATES_ONLY && st_thread) {
+        if (!STATES_ONLY && st_thread && !s_zero) {
             float gr = 0.f;
 #pragma unroll
             for (int g2 = 0; g2 < NG / 2; ++g2) gr += part[(dir ? g2 + NG / 2 : g2) * DK + st_row];
@@ -454,19 +469,29 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         TC_STAMP(3);
 
         const uint32_t kt = sbase + OFF_KT, v_addr = sbase + OFF_V;
+        bool o_has = dir != dir_first;            // the chunk's output accumulator already has content (issuer 0's view)
         if (!STATES_ONLY) {
-            // ---- MMA issue 1: inter-chunk product, then the 128x128 scores ---------------------------------
-            if (tid == 0) {
+            // ---- MMA issue 1: inter-chunk product (issuer 0) and the 128x128 scores (issuer 1) ----------------
+            const uint32_t qt = sbase + OFF_QT;
+            if (issuer == 0) {
                 tc_fence_after();
-                const uint32_t qt = sbase + OFF_QT, st = sbase + OFF_ST;
-                const bool first_touch = dir == dir_first;            // the chunk's accumulator has no content yet
+                if (FUSED)                                // park the operand tile (same swizzled image) for the deferred term
+                    bulk_store(p.qscratch + ((size_t)blockIdx.x * 4 + n) * TILE_B, qt, TILE_B);
+                if (!s_zero) {
+                    const uint32_t st = sbase + OFF_ST;
 #pragma unroll
-                for (int k4 = 0; k4 < DK / 16; ++k4)
-                    tc_mma(tmem + TM_O + c * 64, make_desc(qt + k4 * 32), make_desc(st + k4 * 2048), IDESC_OV, !(first_touch && k4 == 0));
+                    for (int k4 = 0; k4 < DK / 16; ++k4)
+                        tc_mma(tmem + TM_O + c * 64, make_desc(qt + k4 * 32), make_desc(st + k4 * 2048), IDESC_OV, o_has || k4 > 0);
+                    o_has = true;
+                }
+                if (FUSED) bulk_store_wait_read();        // the scores overwrite the tile once bar_p0 completes
+                tc_commit(bar_p0);
+            } else if (issuer == 1) {
+                tc_fence_after();
 #pragma unroll
                 for (int k4 = 0; k4 < DK / 16; ++k4)      // all 128 key columns at once: TM_P0 and TM_P1 are adjacent
                     tc_mma(tmem + TM_P0, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
-                tc_commit(bar_p0);                        // MMAs complete in order: both readers of the scaled q tile are done
+                tc_commit(bar_p0);                        // with issuer 0's commit: both readers of the scaled q tile are done
             }
             __syncwarp();
             TC_STAMP(4);
@@ -517,16 +542,20 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             __syncthreads();
             TC_STAMP(7);
         }
-        // ---- MMA issue 2: P V into the output accumulator, state update into the second score buffer ----
-        if (tid == 0) {
-            waiter.wait(bar_v, par);              // only the tensor core reads v, so only the issuing thread waits for it
-            tc_fence_after();
+        // ---- MMA issue 2: P V into the output accumulator (issuer 0), K^T V into the second score buffer (issuer 1)
+        if (issuer == 0) {
             if (!STATES_ONLY) {
+                waiter.wait(bar_v, par);          // only the tensor core reads v, so only the issuing threads wait for it
+                tc_fence_after();
 #pragma unroll
                 for (int k8 = 0; k8 < CHUNK / 16; ++k8)
                     tc_mma(tmem + TM_O + c * 64, make_desc(sbase + (k8 < 4 ? OFF_RQ : OFF_QT) + (k8 & 3) * 32),
-                           make_desc(v_addr + k8 * 2048), IDESC_OV, 1);
+                           make_desc(v_addr + k8 * 2048), IDESC_OV, o_has || k8 > 0);
             }
+            tc_commit(bar_o);
+        } else if (issuer == 1) {
+            waiter.wait(bar_v, par);
+            tc_fence_after();
 #pragma unroll
             for (int k8 = 0; k8 < CHUNK / 16; ++k8)
                 tc_mma(tmem + TM_U, make_desc(kt + k8 * 2048), make_desc(v_addr + k8 * 2048), IDESC_U, k8 > 0);
@@ -555,6 +584,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 S[j] = fmaf(S[j], e_last, e_rel * mine);
             }
         }
+        s_zero = false;
         TC_STAMP(10);
         tc_fence_before();                        // ordered before the next tensor-core write of this buffer by the
                                                   // CTA barriers of the next iteration
@@ -583,9 +613,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         // ---- publish: my local end states are in the workspace; count me in for my sequence ------------------
         __threadfence();
         __syncthreads();
-        if (tid == 0) atomicAdd(p.group_cnt + bh, 1u);
-        // bring my parked q operand tiles back meanwhile (plain loads that bypass L1: the scratch slot was read by
-        // the previous item of this CTA); every tile buffer is free at this point
+        if (tid == 0) {
+            atomicAdd(p.group_cnt + bh, 1u);
+            bulk_store_wait_all();                // the parking copies have landed
+        }
+        __syncthreads();
+        // bring my parked q operand tiles back meanwhile (plain loads that bypass L1; measured faster here than bulk
+        // copies issued by one thread); every tile buffer is free at this point
         {
             const uint8_t* src = p.qscratch + (size_t)blockIdx.x * 4 * TILE_B;
             const uint32_t dst_off[4] = {(uint32_t)OFF_QT, (uint32_t)OFF_KT, (uint32_t)OFF_RQ, (uint32_t)OFF_RK};
@@ -614,7 +648,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             __threadfence();
             __syncthreads();
         };
+        TC_STAMPX(11);
         group_wait(p.group_cnt + bh);             // every segment's local end state is in the workspace
+        TC_STAMPX(12);
         // ---- scan over the segments, split by state element across the sequence's CTAs: each CTA turns, for its
         //      slice of the dk x dv elements, every segment's local end state into the state that ENTERS that
         //      segment (in place), and delivers the sequence's final state / total decay for that slice ----------
@@ -622,35 +658,47 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             constexpr int NE = DK * DV;
             const int slice = (NE + nseg - 1) / nseg;
             const int e_end = min(NE, (seg + 1) * slice);
-            for (int dir = dir_first; dir <= dir_last; ++dir) {
-                const int first = dir ? nseg - 1 : 0, step = dir ? -1 : 1;
-                float* fin = dir ? p.final_b : p.final_f;
-                float* ld = dir ? p.logdecay_b : p.logdecay_f;
-                for (int e = seg * slice + tid; e < e_end; e += NTHREADS) {
-                    const int row = e / DV;
-                    float E = 0.f, gsum = 0.f;
-                    constexpr int PF = 16;        // loads of PF segments are in flight before the dependent chain runs
-                    for (int i0 = 0; i0 < nseg; i0 += PF) {
-                        float u[PF], g[PF];
+            const bool on[2] = {(p.dir_mask & 1) != 0, (p.dir_mask & 2) != 0};
+            for (int e = seg * slice + tid; e < e_end; e += NTHREADS) {
+                const int row = e / DV;
+                float E[2] = {0.f, 0.f}, gsum[2] = {0.f, 0.f};
+                constexpr int PF = 8;             // both directions' loads of PF segments are in flight before the chains run
+                for (int i0 = 0; i0 < nseg; i0 += PF) {
+                    float u[2][PF], a[2][PF];
+#pragma unroll
+                    for (int d = 0; d < 2; ++d) {
 #pragma unroll
                         for (int i = 0; i < PF; ++i) {
-                            const bool in = i0 + i < nseg;
-                            const size_t slot = ((size_t)bh * nseg + (first + (in ? i0 + i : 0) * step)) * 2 + dir;
-                            u[i] = in ? __ldcg(p.ws_state + slot * NE + e) : 0.f;
-                            g[i] = in ? __ldcg(p.ws_decay + slot * DK + row) : 0.f;
+                            const bool in = on[d] && i0 + i < nseg;
+                            const int sg_i = in ? i0 + i : 0;
+                            const size_t slot = ((size_t)bh * nseg + (d ? nseg - 1 - sg_i : sg_i)) * 2 + d;
+                            u[d][i] = in ? __ldcg(p.ws_state + slot * NE + e) : 0.f;
+                            a[d][i] = in ? __ldcg(p.ws_decay + slot * DK + row) : 0.f;
                         }
+                    }
 #pragma unroll
-                        for (int i = 0; i < PF; ++i) {
-                            if (i0 + i < nseg) {
-                                const size_t slot = ((size_t)bh * nseg + (first + (i0 + i) * step)) * 2 + dir;
-                                p.ws_state[slot * NE + e] = E;
-                                E = fmaf(E, __expf(g[i]), u[i]);
-                                gsum += g[i];
+                    for (int d = 0; d < 2; ++d) {
+#pragma unroll
+                        for (int i = 0; i < PF; ++i) { gsum[d] += a[d][i]; a[d][i] = __expf(a[d][i]); }
+                    }
+#pragma unroll
+                    for (int i = 0; i < PF; ++i) {
+#pragma unroll
+                        for (int d = 0; d < 2; ++d) {
+                            if (on[d] && i0 + i < nseg) {
+                                const size_t slot = ((size_t)bh * nseg + (d ? nseg - 1 - (i0 + i) : i0 + i)) * 2 + d;
+                                p.ws_state[slot * NE + e] = E[d];
+                                E[d] = fmaf(E[d], a[d][i], u[d][i]);
                             }
                         }
                     }
-                    if (fin) fin[(size_t)bh * NE + e] = E;
-                    if (ld && (e % DV) == 0) ld[(size_t)bh * DK + row] = gsum;
+                }
+#pragma unroll
+                for (int d = 0; d < 2; ++d) {
+                    float* fin = d ? p.final_b : p.final_f;
+                    float* ld = d ? p.logdecay_b : p.logdecay_f;
+                    if (on[d] && fin) fin[(size_t)bh * NE + e] = E[d];
+                    if (on[d] && ld && (e % DV) == 0) ld[(size_t)bh * DK + row] = gsum[d];
                 }
             }
         }
@@ -658,7 +706,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         __syncthreads();
         uint32_t* scanned = p.group_cnt + (size_t)p.B * p.H + bh;
         if (tid == 0) atomicAdd(scanned, 1u);
+        TC_STAMPX(13);
         group_wait(scanned);                      // every slice of the entering states is in place
+        // Draw the next item and keep it in a register until the end of this one, so that the round trip of the
+        // atomic costs no stall.  Not earlier: a CTA that holds a ticket of a sequence it is still waiting for
+        // could never be released.
+        if (tid == 0) next_item = (int)atomicAdd(p.ticket, 1u);
+        TC_STAMPX(14);
         // ---- state operand of every chunk: bf16(2^{cvec} * S_enter), MN-major [channel][value] -------------------
         const uint32_t st_off[4] = {(uint32_t)OFF_ST, (uint32_t)OFF_RG, (uint32_t)(OFF_RG + 64 * 128), (uint32_t)OFF_V};
         float4 enter[2][4];                       // both directions' entering states are requested before either is used
@@ -689,13 +743,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        // ---- the deferred term: O_chunk += (parked q operand) x (entering state operand) ---------------------
-        if (tid == 0) {
+        // ---- the deferred term: O_chunk += (parked q operand) x (entering state operand); issuer i owns chunk i --
+        if (issuer >= 0) {
             tc_fence_after();
             const uint32_t q_off[4] = {(uint32_t)OFF_QT, (uint32_t)OFF_KT, (uint32_t)OFF_RQ, (uint32_t)OFF_RK};
             for (int n = 0; n < n_iter; ++n) {
                 const int dir = dir_first + n / nch, ci = n % nch;
                 const int c = dir ? nch - 1 - ci : ci;
+                if (c != issuer) continue;
 #pragma unroll
                 for (int k4 = 0; k4 < DK / 16; ++k4)
                     tc_mma(tmem + TM_O + c * 64, make_desc(sbase + q_off[n] + k4 * 32), make_desc(sbase + st_off[n] + k4 * 2048), IDESC_OV, 1);
@@ -705,6 +760,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         __syncwarp();
         if (warp == 0) waiter.wait(bar_x, item_count & 1u);
         __syncthreads();
+        TC_STAMPX(15);
         ++item_count;
     }
 
@@ -731,6 +787,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         }
     }
     if (!FUSED) break;
+    if (tid == 0) *item_slot = next_item;
     tc_fence_before();                            // the accumulators are read out before the next item overwrites them
     __syncthreads();
     }                                             // work items
