@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("VIG_B200_LIB") or os.path.join(_HERE, "libvig_b200.so")
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
-IMPL_AUTO, IMPL_SIMT, IMPL_TC, IMPL_TC_SINGLE, IMPL_TC_SPLIT = 0, 1, 2, 3, 4
+IMPL_AUTO, IMPL_SIMT, IMPL_TC, IMPL_TC_SINGLE, IMPL_TC_SPLIT, IMPL_TC_WAVE = 0, 1, 2, 3, 4, 5
 
 _lib = None
 

@@ -46,7 +46,11 @@ size_t vig::bigla_workspace_internal(int B, int H, int L, int dk, int dv, int dt
     if (B <= 0 || H <= 0 || L <= 0 || !dims_ok(dk, dv)) return 0;
     size_t simt = bigla_simt_workspace(B, H, L, dk, dv);
     size_t tc = (dtype != VIG_DTYPE_F32 && impl != VIG_IMPL_SIMT) ? bigla_tc_workspace(B, H, L, dk, dv, no_single || !(impl == VIG_IMPL_TC_SINGLE || (impl != VIG_IMPL_TC_SPLIT && bigla_tc_prefers_single(L)))) : 0;
-    return simt > tc ? simt : tc;
+    size_t wave = (dtype != VIG_DTYPE_F32 && (impl == VIG_IMPL_TC_WAVE || impl == VIG_IMPL_AUTO) && dk == 64 && dv == 64) ? bigla_wave_workspace(B, H, L, dk, dv) : 0;
+    if (impl == VIG_IMPL_TC_WAVE) return wave;
+    if (no_single) wave = 0;
+    size_t m = simt > tc ? simt : tc;
+    return m > wave ? m : wave;
 }
 
 static void fill_strides(int64_t* dst, const int64_t* src, int H, int L, int d) {
@@ -81,7 +85,7 @@ int vig::bigla_fwd_internal(const void* q, const void* k, const void* v, const v
     if (dtype < 0 || dtype > 2) return VIG_ERR_DTYPE;
     if (B < 0 || H <= 0 || L < 0 || !dims_ok(dk, dv)) return VIG_ERR_SHAPE;
     if (dir_mask < 1 || dir_mask > 3) return VIG_ERR_ARG;
-    if (impl < VIG_IMPL_AUTO || impl > VIG_IMPL_TC_SPLIT) return VIG_ERR_ARG;
+    if (impl < VIG_IMPL_AUTO || impl > VIG_IMPL_TC_WAVE) return VIG_ERR_ARG;
     if (B == 0 || L == 0) return VIG_OK;
     if (!k || !v) return VIG_ERR_NULL;
     if (o && !q) return VIG_ERR_NULL;
@@ -105,6 +109,11 @@ int vig::bigla_fwd_internal(const void* q, const void* k, const void* v, const v
     p.logdecay_f = total_logdecay_fwd; p.logdecay_b = total_logdecay_bwd;
     p.dir_mask = dir_mask; p.status = status_dev;
 
+    if (impl == VIG_IMPL_TC_WAVE) {
+        if (!bigla_wave_supported(p) || need_states && !o) return VIG_ERR_SHAPE;
+        if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return VIG_ERR_ALIGN;
+        return bigla_wave_launch(p, workspace, workspace_bytes, (cudaStream_t)stream);
+    }
     bool use_tc = false;
     if (impl == VIG_IMPL_TC || impl == VIG_IMPL_TC_SINGLE || impl == VIG_IMPL_TC_SPLIT) {
         if (!bigla_tc_supported(p)) return VIG_ERR_SHAPE;

@@ -86,5 +86,9 @@ int bigla_tc_launch(const BiglaParams& p, void* ws, size_t ws_bytes, bool allow_
 size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv, bool split_only);
 bool bigla_tc_supported(const BiglaParams& p);
 bool bigla_tc_prefers_single(int L);
+// warp-specialised wavefront form (large batches): one persistent CTA per SM, state hand-off between segments
+bool bigla_wave_supported(const BiglaParams& p);
+size_t bigla_wave_workspace(int B, int H, int L, int dk, int dv);
+int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream);
 
 }  // namespace vig

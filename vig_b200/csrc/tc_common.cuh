@@ -1,0 +1,188 @@
+// Device-side PTX wrappers (mbarrier, TMA, tcgen05, TMEM) and host-side tensor-map helpers shared by the
+// tensor-core bi-GLA kernels.
+#pragma once
+#include <cuda.h>
+#include <mutex>
+#include <type_traits>
+#include "common.cuh"
+
+namespace vig {
+namespace tc {
+
+constexpr int CHUNK = 128;            // tokens per chunk = rows of one MMA tile
+constexpr float MAX_EXPONENT = 80.f;  // exp() arguments of the factorisation are clamped to +-80
+
+struct TcMaps { CUtensorMap q, k, v, gf, gb; };
+
+// ---------------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+// untiled bulk copies: a 16 KB operand tile to / from its parking slot in global memory
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Low word: start address (bits 0-13, in 16-byte units) and leading byte offset 1 (bits 16-29; unused for one
+// 128-byte atom column).  High word: stride byte offset 1024 >> 4 (bits 32-45), descriptor version 1 (bit 46),
+// SWIZZLE_128B (bits 61-63).
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t make_desc(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+// a_lo / b_lo: low words of the shared-memory descriptors (see make_desc_lo); the high word is the same constant
+// for every tile of this kernel, so an MMA costs one integer add per operand to set up.
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets lane (base lane + i)
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (both for K-major
+// tiles with 128-byte rows along K and for MN-major tiles with 128-byte rows along M/N).
+// Instruction descriptor: fp32 accumulate, A/B format (0 fp16, 1 bf16), major-ness (0 K, 1 MN), N, M.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t a_mn, uint32_t b_mn, uint32_t M, uint32_t N) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// Byte offset of bf16 element (row, col) in a K-major / MN-major tile with 128-byte rows and 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t col_bytes) {
+    return row * 128 + ((((col_bytes >> 4) ^ (row & 7)) << 4) | (col_bytes & 15));
+}
+
+template <typename T> struct Pack2;
+template <> struct Pack2<__nv_bfloat16> {
+    static constexpr uint32_t FMT = 1;
+    __device__ static uint32_t pack(float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
+    __device__ static float2 unpack(uint32_t u) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u)); }
+};
+template <> struct Pack2<__half> {
+    static constexpr uint32_t FMT = 0;
+    __device__ static uint32_t pack(float a, float b) { __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
+    __device__ static float2 unpack(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
+};
+
+struct Waiter {
+    volatile int* abort_flag;
+    int32_t* status;
+    // Bounded wait: ~0.3 s at most, then flag the CTA as aborted so that no later wait spins.  The polling loop must
+    // stay rolled: a kernel has dozens of wait sites and the instruction cache is a bottleneck of these kernels.
+    __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
+        if (mbar_try_wait(bar, parity)) return;
+#pragma unroll 1
+        for (uint32_t i = 0; i < (1u << 22); ++i) {
+            if (mbar_try_wait(bar, parity)) return;
+            if (i > 128) {
+                if (*abort_flag) return;
+                __nanosleep(64);
+            }
+        }
+        *abort_flag = 1;
+        if (status) atomicOr(status, 1);
+    }
+};
+
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+// single-instruction exp2 / log2 (flush-to-zero forms: no denormal fix-up code around the MUFU)
+__device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float lg2(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+constexpr float MAX_EXPONENT2 = MAX_EXPONENT * LOG2E;   // the exponent bound in log2 units
+
+// Log-gate in LOG2 units.  From a raw logit: logsigmoid(x) = min(x,0) - log(1 + exp(-|x|)), here with y = x log2(e):
+// min(y,0) - log2(1 + 2^-|y|), times 1/normalizer.  From a log-gate: x log2(e).
+__device__ __forceinline__ float fast_gate2(float x, bool raw_logits, float inv_norm) {
+    const float y = x * LOG2E;
+    return raw_logits ? (fminf(y, 0.f) - lg2(1.f + ex2(-fabsf(y)))) * inv_norm : y;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Host side: tensor maps through the driver entry point (no link-time dependency on libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// [B,H,L,d] view with element strides s = (b, h, l): box of 128 tokens x d channels of one (b, h).
+inline bool make_map(CUtensorMap* m, const void* base, const int64_t* s, int B, int H, int L, int d, int dtype, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)s[2] * 2, (cuuint64_t)s[1] * 2, (cuuint64_t)s[0] * 2};
+    cuuint32_t box[4] = {(cuuint32_t)d, CHUNK, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, dtype == VIG_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+inline bool tma_ok(const void* base, const int64_t* s, int B, int H) {
+    if (!base) return true;
+    if (reinterpret_cast<uintptr_t>(base) & 15) return false;
+    for (int i = 0; i < 3; ++i) {
+        const bool unused = (i == 0 && B == 1) || (i == 1 && H == 1);
+        if (s[i] <= 0 && !unused) return false;
+        if ((s[i] * 2) % 16) return false;
+    }
+    return true;
+}
+
+
+}  // namespace tc
+}  // namespace vig
