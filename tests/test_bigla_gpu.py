@@ -173,6 +173,51 @@ def test_single_launch_form_matches_oracle_and_three_launch_form(shape):
     assert rel_err(ex1["logdecay_fwd"], ex0["logdecay_fwd"]) < 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,dir_mask,init", [((2, 3, 1300), 3, True), ((1, 1, 128), 3, False), ((3, 2, 196), 3, False),
+                                                 ((2, 2, 1024), 1, True), ((2, 2, 700), 2, False), ((30, 3, 1000), 3, False)])
+def test_wavefront_form_matches_oracle(shape, dir_mask, init, dtype):
+    """The warp-specialised wavefront form (impl 5): every state passes from segment to segment through the
+    mailbox, the two directions of a chunk meet in the output tensor (store, then vector reduction)."""
+    import vig_b200
+    from vig_b200 import _lib
+    B, H, L = shape
+    ins = oracle.make_bigla_inputs(B, H, L, 64, 64, seed=L + dir_mask)
+    g = torch.Generator().manual_seed(5)
+    i_f, i_b = torch.randn(B, H, 64, 64, generator=g), torch.randn(B, H, 64, 64, generator=g)
+    dev = _cuda(ins, dtype)
+    kw = dict(output_final_state=True, output_logdecay=True, dir_mask=dir_mask)
+    if init:
+        kw.update(init_state_fwd=i_f.cuda(), init_state_bwd=i_b.cuda())
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o1, ex1 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_WAVE, status=status, **kw)
+    o0, ex0 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_SPLIT, **kw)
+    assert int(status.item()) == 0
+    assert rel_err(o1.float(), o0.float()) < 1e-2
+    for name in ex0:
+        assert rel_err(ex1[name], ex0[name]) < 1e-4, name
+    if B * L <= 4096:                                  # the naive oracle is a token loop
+        f32 = [t.float().cpu() for t in dev]
+        if dir_mask == 3:
+            ref = oracle.naive_bi_gla(*f32, init_fwd=i_f if init else None, init_bwd=i_b if init else None)
+            assert rel_err(o1.float(), ref) < 2e-2
+
+
+def test_wavefront_form_is_the_default_for_large_batches():
+    """Enough (sequence, direction) chains to fill the GPU and more than one segment: the default routes to the
+    wavefront form; results agree with the three-launch form and a second call gives the same bits."""
+    import vig_b200
+    from vig_b200 import _lib
+    B, H, L = 40, 3, 768
+    dev = _cuda(oracle.make_bigla_inputs(B, H, L, 64, 64, seed=11), torch.bfloat16)
+    o_auto = vig_b200.bi_gla(*dev)
+    o_wave = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_WAVE)
+    o_split = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_SPLIT)
+    assert torch.equal(o_auto, o_wave)
+    assert torch.equal(o_auto, vig_b200.bi_gla(*dev))
+    assert rel_err(o_auto.float(), o_split.float()) < 1e-2
+
+
 def _strong_gate_inputs(per_token, L=300, seed=2):
     q, k, v, _, _ = oracle.make_bigla_inputs(1, 2, L, 64, 64, seed=seed)
     gen = torch.Generator().manual_seed(seed + 100)

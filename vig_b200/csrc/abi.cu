@@ -114,6 +114,9 @@ int vig::bigla_fwd_internal(const void* q, const void* k, const void* v, const v
         if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return VIG_ERR_ALIGN;
         return bigla_wave_launch(p, workspace, workspace_bytes, (cudaStream_t)stream);
     }
+    if (impl == VIG_IMPL_AUTO && !no_single && o && bigla_wave_supported(p) && bigla_wave_preferred(p) && workspace &&
+        !(reinterpret_cast<uintptr_t>(workspace) & 255) && workspace_bytes >= bigla_wave_workspace(B, H, L, dk, dv))
+        return bigla_wave_launch(p, workspace, workspace_bytes, (cudaStream_t)stream);
     bool use_tc = false;
     if (impl == VIG_IMPL_TC || impl == VIG_IMPL_TC_SINGLE || impl == VIG_IMPL_TC_SPLIT) {
         if (!bigla_tc_supported(p)) return VIG_ERR_SHAPE;

@@ -280,18 +280,27 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const uint32_t tok = (uint32_t)(grp * TPG + (u ^ dmask));
                 return tok * 128 + ((c4 ^ (tok & 7)) << 4) + lane_off;
             };
-            float2 gl[TPG];
+            // The 16 tokens of a thread are handled as two halves by loops that run twice; the cumulative gates of
+            // the halves rotate through two register arrays, so the loop bodies are half the code of a full unroll
+            // while eight tokens still overlap their latencies.
+            constexpr int HT = TPG / 2;
+            float2 glA[HT], glB[HT];
             {
                 float2 run = make_float2(0.f, 0.f);
+#pragma unroll 1
+                for (int hh = 0; hh < 2; ++hh) {
 #pragma unroll
-                for (int u = 0; u < TPG; ++u) {
-                    const int tok = grp * TPG + (u ^ dmask);
-                    float2 g = Pack2<T>::unpack(sg[tok * 32 + cp]);
-                    g.x = fmaxf(fast_gate2(g.x, raw_logits, inv_norm), clamp_lo);
-                    g.y = fmaxf(fast_gate2(g.y, raw_logits, inv_norm), clamp_lo);
-                    if (tok >= n_valid) g = make_float2(0.f, 0.f);
-                    run.x += g.x; run.y += g.y;
-                    gl[u] = run;                              // inclusive cumulative sum
+                    for (int i = 0; i < HT; ++i) glA[i] = glB[i];
+#pragma unroll
+                    for (int i = 0; i < HT; ++i) {
+                        const int tok = grp * TPG + ((hh * HT + i) ^ dmask);
+                        float2 g = Pack2<T>::unpack(sg[tok * 32 + cp]);
+                        g.x = fmaxf(fast_gate2(g.x, raw_logits, inv_norm), clamp_lo);
+                        g.y = fmaxf(fast_gate2(g.y, raw_logits, inv_norm), clamp_lo);
+                        if (tok >= n_valid) g = make_float2(0.f, 0.f);
+                        run.x += g.x; run.y += g.y;
+                        glB[i] = run;                         // inclusive cumulative sum
+                    }
                 }
                 reinterpret_cast<float2*>(part)[grp * 32 + cp] = run;
             }
@@ -300,7 +309,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             if (lane == 0) { mbar_arrive(bar(B_PART)); WT(1, waiter.wait(bar(B_PART), m & 1)); }
             __syncwarp();
             float2 off = make_float2(0.f, 0.f), gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
-#pragma unroll
+#pragma unroll 2
             for (int g2 = 0; g2 < NG; ++g2) {
                 const float2 s2 = reinterpret_cast<const float2*>(part)[g2 * 32 + cp];
                 const bool before = dir ? g2 > grp : g2 < grp;            // scanned before my group
@@ -311,25 +320,27 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             off.x -= gref.x; off.y -= gref.y;
             float worst = 0.f;                                // largest |exponent| before clamping
-            uint32_t raw[TPG];
+#pragma unroll 1
+            for (int hh = 0; hh < 2; ++hh) {
+                uint32_t rk[HT], rq[HT], offs[HT];
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) raw[u] = *reinterpret_cast<const uint32_t*>(stg + WS_K + tile_off(u));
+                for (int i = 0; i < HT; ++i) {                // all reads of the half before its writes: the tiles alias for the compiler
+                    offs[i] = tile_off(hh * HT + i);
+                    rk[i] = *reinterpret_cast<const uint32_t*>(stg + WS_K + offs[i]);
+                    rq[i] = *reinterpret_cast<const uint32_t*>(stg + WS_Q + offs[i]);
+                }
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) {
-                float ex = off.x + gl[u].x, ey = off.y + gl[u].y;
-                worst = fmaxf(worst, fmaxf(fabsf(ex), fabsf(ey)));
-                ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
-                ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
-                gl[u] = make_float2(ex, ey);                  // kept for the q tile
-                const float2 kk = Pack2<T>::unpack(raw[u]);
-                *reinterpret_cast<uint32_t*>(stg + WS_K + tile_off(u)) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
-            }
+                for (int i = 0; i < HT; ++i) {
+                    float ex = off.x + glA[i].x, ey = off.y + glA[i].y;
+                    worst = fmaxf(worst, fmaxf(fabsf(ex), fabsf(ey)));
+                    ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
+                    ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
+                    const float2 kk = Pack2<T>::unpack(rk[i]), qq = Pack2<T>::unpack(rq[i]);
+                    *reinterpret_cast<uint32_t*>(stg + WS_K + offs[i]) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                    *reinterpret_cast<uint32_t*>(stg + WS_Q + offs[i]) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                }
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) raw[u] = *reinterpret_cast<const uint32_t*>(stg + WS_Q + tile_off(u));
-#pragma unroll
-            for (int u = 0; u < TPG; ++u) {
-                const float2 qq = Pack2<T>::unpack(raw[u]);
-                *reinterpret_cast<uint32_t*>(stg + WS_Q + tile_off(u)) = Pack2<T>::pack(qq.x * ex2(gl[u].x + lq), qq.y * ex2(gl[u].y + lq));
+                for (int i = 0; i < HT; ++i) glA[i] = glB[i];
             }
             if (grp == 0) {                                   // per-channel factors of this iteration for the state warps
                 float* ve = vec + (m & 3) * 256;
@@ -612,6 +623,22 @@ bool bigla_wave_supported(const BiglaParams& p) {
     if ((p.dir_mask & 2) && (!p.gb || !tc::tma_ok(p.gb, p.sgb, p.B, p.H))) return false;
     if ((reinterpret_cast<uintptr_t>(p.o) & 15) || (p.so[0] * 2) % 16 || (p.so[1] * 2) % 16 || (p.so[2] * 2) % 16) return false;
     return tc::encode_fn() != nullptr;
+}
+
+// Measured on B200: with at least as many (sequence, direction) chains as SMs and two or more segments per sequence the
+// wavefront form beats the segment-parallel forms (0.46 against 0.58 ms at 64 x 3 sequences of 4096 tokens); with
+// fewer chains its CTAs idle, and a single segment has nothing to hand on.
+bool bigla_wave_preferred(const BiglaParams& p) {
+    static int sm_count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!sm_count[dev]) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
+        sm_count[dev] = sms;
+    }
+    const int ndir = p.dir_mask == 3 ? 2 : 1;
+    return p.L > W_SEG && (long long)p.B * p.H * ndir >= sm_count[dev];
 }
 
 // Counters (ticket, chain progress, chunk flags) followed by the state mailboxes.

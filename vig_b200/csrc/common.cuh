@@ -88,6 +88,7 @@ bool bigla_tc_supported(const BiglaParams& p);
 bool bigla_tc_prefers_single(int L);
 // warp-specialised wavefront form (large batches): one persistent CTA per SM, state hand-off between segments
 bool bigla_wave_supported(const BiglaParams& p);
+bool bigla_wave_preferred(const BiglaParams& p);
 size_t bigla_wave_workspace(int B, int H, int L, int dk, int dv);
 int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream);
 
