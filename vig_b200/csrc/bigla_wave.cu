@@ -75,6 +75,32 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// raw pair * (sx, sy) in the tile's own 16-bit format: one conversion of the two scales, one packed multiply
+template <typename T> struct ScalePair;
+template <> struct ScalePair<__nv_bfloat16> {
+    __device__ static uint32_t mul(uint32_t raw, float sx, float sy) {
+        const __nv_bfloat162 sc = __floats2bfloat162_rn(sx, sy);
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&raw), sc);
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+};
+template <> struct ScalePair<__half> {
+    __device__ static uint32_t mul(uint32_t raw, float sx, float sy) {
+        const __half2 sc = __floats2half2_rn(sx, sy);
+        const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&raw), sc);
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+};
+
+// Log-gate in log2 units, branch-free and short: from a raw logit x, logsigmoid(x) / norm = -log2(1 + 2^(-x log2 e)) / norm
+// (for very negative x the power overflows to +inf and the gate to -inf, which the exponent clamp catches and flags
+// like any other gate beyond the factorisation range); from a log-gate, x log2 e.
+__device__ __forceinline__ float gate2_short(float x, bool raw_logits, float neg_inv_norm) {
+    const float y = x * LOG2E;
+    const float sp = lg2(1.f + ex2(-y)) * neg_inv_norm;
+    return raw_logits ? sp : y;
+}
+
 template <typename T> struct RedAdd;
 template <> struct RedAdd<__nv_bfloat16> {
     __device__ static void v4(void* p, uint4 w) {
@@ -295,8 +321,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     for (int i = 0; i < HT; ++i) {
                         const int tok = grp * TPG + ((hh * HT + i) ^ dmask);
                         float2 g = Pack2<T>::unpack(sg[tok * 32 + cp]);
-                        g.x = fmaxf(fast_gate2(g.x, raw_logits, inv_norm), clamp_lo);
-                        g.y = fmaxf(fast_gate2(g.y, raw_logits, inv_norm), clamp_lo);
+                        g.x = fmaxf(gate2_short(g.x, raw_logits, -inv_norm), clamp_lo);
+                        g.y = fmaxf(gate2_short(g.y, raw_logits, -inv_norm), clamp_lo);
                         if (tok >= n_valid) g = make_float2(0.f, 0.f);
                         run.x += g.x; run.y += g.y;
                         glB[i] = run;                         // inclusive cumulative sum
@@ -335,9 +361,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     worst = fmaxf(worst, fmaxf(fabsf(ex), fabsf(ey)));
                     ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
                     ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
-                    const float2 kk = Pack2<T>::unpack(rk[i]), qq = Pack2<T>::unpack(rq[i]);
-                    *reinterpret_cast<uint32_t*>(stg + WS_K + offs[i]) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
-                    *reinterpret_cast<uint32_t*>(stg + WS_Q + offs[i]) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                    *reinterpret_cast<uint32_t*>(stg + WS_K + offs[i]) = ScalePair<T>::mul(rk[i], ex2(-ex), ex2(-ey));
+                    *reinterpret_cast<uint32_t*>(stg + WS_Q + offs[i]) = ScalePair<T>::mul(rq[i], ex2(ex + lq), ex2(ey + lq));
                 }
 #pragma unroll
                 for (int i = 0; i < HT; ++i) glA[i] = glB[i];
