@@ -75,23 +75,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// raw pair * (sx, sy) in the tile's own 16-bit format: one conversion of the two scales, one packed multiply
-template <typename T> struct ScalePair;
-template <> struct ScalePair<__nv_bfloat16> {
-    __device__ static uint32_t mul(uint32_t raw, float sx, float sy) {
-        const __nv_bfloat162 sc = __floats2bfloat162_rn(sx, sy);
-        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&raw), sc);
-        return *reinterpret_cast<const uint32_t*>(&r);
-    }
-};
-template <> struct ScalePair<__half> {
-    __device__ static uint32_t mul(uint32_t raw, float sx, float sy) {
-        const __half2 sc = __floats2half2_rn(sx, sy);
-        const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&raw), sc);
-        return *reinterpret_cast<const uint32_t*>(&r);
-    }
-};
-
 // Log-gate in log2 units, branch-free and short: from a raw logit x, logsigmoid(x) / norm = -log2(1 + 2^(-x log2 e)) / norm
 // (for very negative x the power overflows to +inf and the gate to -inf, which the exponent clamp catches and flags
 // like any other gate beyond the factorisation range); from a log-gate, x log2 e.
@@ -361,8 +344,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     worst = fmaxf(worst, fmaxf(fabsf(ex), fabsf(ey)));
                     ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
                     ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
-                    *reinterpret_cast<uint32_t*>(stg + WS_K + offs[i]) = ScalePair<T>::mul(rk[i], ex2(-ex), ex2(-ey));
-                    *reinterpret_cast<uint32_t*>(stg + WS_Q + offs[i]) = ScalePair<T>::mul(rq[i], ex2(ex + lq), ex2(ey + lq));
+                    // fp32 products, one rounding to the 16-bit operand (a packed 16-bit multiply would round the scale too)
+                    const float2 kk = Pack2<T>::unpack(rk[i]), qq = Pack2<T>::unpack(rq[i]);
+                    *reinterpret_cast<uint32_t*>(stg + WS_K + offs[i]) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                    *reinterpret_cast<uint32_t*>(stg + WS_Q + offs[i]) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
                 }
 #pragma unroll
                 for (int i = 0; i < HT; ++i) glA[i] = glB[i];
