@@ -30,6 +30,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+// The same test, but the hardware may park the thread for up to `ns` nanoseconds while the phase is pending and
+// wakes it when the phase completes: a waiting warp then issues almost no instructions.
+__device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok;
+}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
@@ -100,17 +108,15 @@ template <> struct Pack2<__half> {
 struct Waiter {
     volatile int* abort_flag;
     int32_t* status;
-    // Bounded wait: ~0.3 s at most, then flag the CTA as aborted so that no later wait spins.  The polling loop must
-    // stay rolled: a kernel has dozens of wait sites and the instruction cache is a bottleneck of these kernels.
+    // Bounded wait: about a second at most, then flag the CTA as aborted so that no later wait spins.  The polling
+    // loop must stay rolled (a kernel has dozens of wait sites and the instruction cache is a bottleneck of these
+    // kernels) and parks the thread in hardware between polls (spinning warps would take issue slots from the others).
     __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
         if (mbar_try_wait(bar, parity)) return;
 #pragma unroll 1
-        for (uint32_t i = 0; i < (1u << 22); ++i) {
-            if (mbar_try_wait(bar, parity)) return;
-            if (i > 128) {
-                if (*abort_flag) return;
-                __nanosleep(64);
-            }
+        for (uint32_t i = 0; i < (1u << 19); ++i) {
+            if (mbar_try_wait_parked(bar, parity, 2000u)) return;
+            if (*abort_flag) return;
         }
         *abort_flag = 1;
         if (status) atomicOr(status, 1);
