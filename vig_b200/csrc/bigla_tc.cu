@@ -225,92 +225,78 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         TC_STAMP(1);
 
         // ---- phase 1: cumulative gates (log2 units) and the scaled operand tiles ------------------------
-        // Instantiated per direction so that token indices, and with them the swizzled addresses, are static.
+        // One code path for both directions and for clamped / padded chunks (runtime selects, not template variants),
+        // token loops in halves of 8 with the cumulative gates rotating through two register arrays: the instruction
+        // cache, not the arithmetic, bounds this kernel.
         float2 gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
         bool out_of_range = false;
-        // PLAIN: full chunk and no lower clamp of the gates -- the common case skips the padding select and the clamp.
-        const bool plain = !(p.clamp_min == p.clamp_min) && (p.L - t0 >= CHUNK);
-        auto phase1 = [&](auto dir_c, auto plain_c) {
-            constexpr int DIR = decltype(dir_c)::value;
-            constexpr bool PLAIN = decltype(plain_c)::value != 0;
+        {
             const int n_valid = p.L - t0;                             // rows at or past it are padding: decay 1
-            float2 gl[TPG];
+            const int dmask = dir ? TPG - 1 : 0;                      // scan order inside the group: token grp*TPG + (u ^ dmask)
+            constexpr int HT = TPG < 8 ? TPG : 8, NH = TPG / HT;
+            float2 glA[HT], glB[HT];
             float2 run = make_float2(0.f, 0.f);
+#pragma unroll 1
+            for (int hh = 0; hh < NH; ++hh) {
 #pragma unroll
-            for (int u = 0; u < TPG; ++u) {                           // u runs in scan order inside the group
-                const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
-                float2 g = Pack2<T>::unpack(sg[tok * CPW + cp]);
-                g.x = fast_gate2(g.x, raw_logits, inv_norm);
-                g.y = fast_gate2(g.y, raw_logits, inv_norm);
-                if (!PLAIN) {
-                    g.x = fmaxf(g.x, clamp_lo); g.y = fmaxf(g.y, clamp_lo);
+                for (int i = 0; i < HT; ++i) glA[i] = glB[i];
+#pragma unroll
+                for (int i = 0; i < HT; ++i) {
+                    const int tok = grp * TPG + ((hh * HT + i) ^ dmask);
+                    float2 g = Pack2<T>::unpack(sg[tok * CPW + cp]);
+                    g.x = fmaxf(gate2_short(g.x, raw_logits, -inv_norm), clamp_lo);
+                    g.y = fmaxf(gate2_short(g.y, raw_logits, -inv_norm), clamp_lo);
                     if (tok >= n_valid) g = make_float2(0.f, 0.f);
+                    run.x += g.x; run.y += g.y;
+                    glB[i] = run;                                     // inclusive cumulative sum
                 }
-                run.x += g.x; run.y += g.y;
-                gl[u] = run;                                          // inclusive cumulative sum
+            }
+            if (NH == 1) {
+#pragma unroll
+                for (int i = 0; i < HT; ++i) glA[i] = glB[i];
             }
             reinterpret_cast<float2*>(part)[grp * CPW + cp] = run;
             if (!STATES_ONLY && warp == 0) waiter.wait(bar_q, par);   // q is first read after the barrier below
-            // If no group of the chunk decays by more than MAX/NG, no exponent below can leave +-MAX and the
-            // clamps are skipped for the whole CTA (the vote doubles as the barrier that publishes `part`).
-            const int risky = __syncthreads_or(fmaxf(fabsf(run.x), fabsf(run.y)) > MAX_EXPONENT2 / NG);
+            __syncthreads();                                          // publishes `part`
             float2 off = make_float2(0.f, 0.f);
-#pragma unroll
+#pragma unroll 2
             for (int g2 = 0; g2 < NG; ++g2) {
                 const float2 s2 = reinterpret_cast<const float2*>(part)[g2 * CPW + cp];
-                const bool before = DIR ? g2 > grp : g2 < grp;        // scanned before my group
-                const bool in_ref = DIR ? g2 >= NG / 2 : g2 < NG / 2; // part of the cumulative gate at the middle token
+                const bool before = dir ? g2 > grp : g2 < grp;        // scanned before my group
+                const bool in_ref = dir ? g2 >= NG / 2 : g2 < NG / 2; // part of the cumulative gate at the middle token
                 if (before) { off.x += s2.x; off.y += s2.y; }
                 if (in_ref) { gref.x += s2.x; gref.y += s2.y; }
                 glast.x += s2.x; glast.y += s2.y;
             }
             off.x -= gref.x; off.y -= gref.y;
-            // Each tile in two batches -- read all raw values, then write all operands: the compiler cannot prove
-            // that the operand tiles do not alias the raw tiles and would otherwise serialise
-            // load -> scale -> store token by token.
-            auto scale_tiles = [&](auto clamp_c) {
-                constexpr bool CLAMP = decltype(clamp_c)::value != 0;
-                auto exponents = [&](int u, float& ex, float& ey) {
-                    ex = off.x + gl[u].x; ey = off.y + gl[u].y;
-                    if (CLAMP) {
-                        out_of_range |= fmaxf(fabsf(ex), fabsf(ey)) > MAX_EXPONENT2;
-                        ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
-                        ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
-                    }
-                };
-                uint32_t raw[TPG];
+            float worst = 0.f;                                        // largest |exponent| before clamping
+#pragma unroll 1
+            for (int hh = 0; hh < NH; ++hh) {
+                uint32_t rk[HT], rq[HT], offs[HT];
 #pragma unroll
-                for (int u = 0; u < TPG; ++u) raw[u] = sk[(grp * TPG + (DIR ? TPG - 1 - u : u)) * CPW + cp];
-#pragma unroll
-                for (int u = 0; u < TPG; ++u) {
-                    const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
-                    float ex, ey;
-                    exponents(u, ex, ey);
-                    const float2 kk = Pack2<T>::unpack(raw[u]);
-                    *reinterpret_cast<uint32_t*>(smem + OFF_KT + swz(tok, cp * 4)) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                for (int i = 0; i < HT; ++i) {                        // all reads of the half before its writes
+                    const uint32_t tok = (uint32_t)(grp * TPG + ((hh * HT + i) ^ dmask));
+                    offs[i] = swz(tok, cp * 4);
+                    rk[i] = sk[tok * CPW + cp];
+                    if (!STATES_ONLY) rq[i] = sq[tok * CPW + cp];
                 }
-                if (!STATES_ONLY) {
 #pragma unroll
-                    for (int u = 0; u < TPG; ++u) raw[u] = sq[(grp * TPG + (DIR ? TPG - 1 - u : u)) * CPW + cp];
-#pragma unroll
-                    for (int u = 0; u < TPG; ++u) {
-                        const int tok = grp * TPG + (DIR ? TPG - 1 - u : u);
-                        float ex, ey;
-                        exponents(u, ex, ey);
-                        const float2 qq = Pack2<T>::unpack(raw[u]);
-                        const uint32_t qw = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
-                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + swz(tok, cp * 4)) = qw;
-
+                for (int i = 0; i < HT; ++i) {
+                    float ex = off.x + glA[i].x, ey = off.y + glA[i].y;
+                    worst = fmaxf(worst, fmaxf(fabsf(ex), fabsf(ey)));
+                    ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
+                    ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
+                    const float2 kk = Pack2<T>::unpack(rk[i]);
+                    *reinterpret_cast<uint32_t*>(smem + OFF_KT + offs[i]) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
+                    if (!STATES_ONLY) {
+                        const float2 qq = Pack2<T>::unpack(rq[i]);
+                        *reinterpret_cast<uint32_t*>(smem + OFF_QT + offs[i]) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
                     }
                 }
-            };
-            if (risky) scale_tiles(std::integral_constant<int, 1>{}); else scale_tiles(std::integral_constant<int, 0>{});
-        };
-        {
-            using I0 = std::integral_constant<int, 0>;
-            using I1 = std::integral_constant<int, 1>;
-            if (dir) { if (plain) phase1(I1{}, I1{}); else phase1(I1{}, I0{}); }
-            else     { if (plain) phase1(I0{}, I1{}); else phase1(I0{}, I0{}); }
+#pragma unroll
+                for (int i = 0; i < HT; ++i) glA[i] = glB[i];
+            }
+            out_of_range = worst > MAX_EXPONENT2;
         }
         TC_STAMP(2);
         if (out_of_range && p.status) atomicOr(p.status, 2);
@@ -379,37 +365,37 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             half_bar_sync(half);
             TC_STAMP(5);
             tc_fence_after();
-            // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal; the test is warp-uniform.
-            auto convert = [&](auto dir_c) {
-                constexpr int DIR = decltype(dir_c)::value;
-#pragma unroll
+            // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test); on the
+            // diagonal, bit j of `dbits` says whether key j of the block is kept for my query row.
+            {
+                const uint32_t dbits = dir ? ~((1u << lane) - 1u) : (lane == 31 ? 0xffffffffu : (2u << lane) - 1u);
+#pragma unroll 1
                 for (int part32 = 0; part32 < 2; ++part32) {
                     const int cb = 2 * half + part32;                 // key block: keys 32*cb .. 32*cb+31
-                    const bool all_zero = DIR ? cb < quad : cb > quad;
-                    const bool diagonal = cb == quad;
-                    float a[32];
-                    if (!all_zero) {
+                    const bool all_zero = dir ? cb < quad : cb > quad;
+                    const uint32_t keep = cb == quad ? dbits : 0xffffffffu;
+                    uint8_t* prow = ptile + row * 128;
+                    const uint32_t chunk0 = (uint32_t)part32 * 4;     // first 16-byte chunk of this block in the 128-byte row
+                    if (all_zero) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(prow + (((chunk0 + j) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    } else {
+                        float a[32];
                         tc_ld32(tmem + lane_base + (half ? TM_P1 : TM_P0) + 32 * part32, a);
                         tc_wait_ld();
-                    }
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        uint4 w = make_uint4(0u, 0u, 0u, 0u);
-                        if (!all_zero) {
-                            float m[8];
+                        for (int j = 0; j < 4; ++j) {
+                            float mk[8];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const bool keep = !diagonal || (DIR ? j + e >= lane : j + e <= lane);
-                                m[e] = keep ? a[j + e] : 0.f;
-                            }
-                            w.x = Pack2<T>::pack(m[0], m[1]); w.y = Pack2<T>::pack(m[2], m[3]);
-                            w.z = Pack2<T>::pack(m[4], m[5]); w.w = Pack2<T>::pack(m[6], m[7]);
+                            for (int e = 0; e < 8; ++e) mk[e] = (keep >> (8 * j + e)) & 1u ? a[8 * j + e] : 0.f;
+                            uint4 w;
+                            w.x = Pack2<T>::pack(mk[0], mk[1]); w.y = Pack2<T>::pack(mk[2], mk[3]);
+                            w.z = Pack2<T>::pack(mk[4], mk[5]); w.w = Pack2<T>::pack(mk[6], mk[7]);
+                            *reinterpret_cast<uint4*>(prow + (((chunk0 + j) ^ (row & 7)) << 4)) = w;
                         }
-                        *reinterpret_cast<uint4*>(ptile + swz(row, (32 * part32 + j) * 2)) = w;
                     }
                 }
-            };
-            if (dir) convert(std::integral_constant<int, 1>{}); else convert(std::integral_constant<int, 0>{});
+            }
             TC_STAMP(6);
             fence_proxy_async();
             tc_fence_before();

@@ -75,15 +75,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Log-gate in log2 units, branch-free and short: from a raw logit x, logsigmoid(x) / norm = -log2(1 + 2^(-x log2 e)) / norm
-// (for very negative x the power overflows to +inf and the gate to -inf, which the exponent clamp catches and flags
-// like any other gate beyond the factorisation range); from a log-gate, x log2 e.
-__device__ __forceinline__ float gate2_short(float x, bool raw_logits, float neg_inv_norm) {
-    const float y = x * LOG2E;
-    const float sp = lg2(1.f + ex2(-y)) * neg_inv_norm;
-    return raw_logits ? sp : y;
-}
-
 template <typename T> struct RedAdd;
 template <> struct RedAdd<__nv_bfloat16> {
     __device__ static void v4(void* p, uint4 w) {

@@ -137,6 +137,15 @@ __device__ __forceinline__ float fast_gate2(float x, bool raw_logits, float inv_
     return raw_logits ? (fminf(y, 0.f) - lg2(1.f + ex2(-fabsf(y)))) * inv_norm : y;
 }
 
+// Log-gate in log2 units, branch-free and short: from a raw logit x, logsigmoid(x) / norm = -log2(1 + 2^(-x log2 e)) / norm
+// (for very negative x the power overflows to +inf and the gate to -inf, which the exponent clamp catches and flags
+// like any other gate beyond the factorisation range); from a log-gate, x log2 e.
+__device__ __forceinline__ float gate2_short(float x, bool raw_logits, float neg_inv_norm) {
+    const float y = x * LOG2E;
+    const float sp = lg2(1.f + ex2(-y)) * neg_inv_norm;
+    return raw_logits ? sp : y;
+}
+
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
