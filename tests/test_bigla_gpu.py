@@ -194,8 +194,8 @@ def test_wavefront_form_matches_oracle(shape, dir_mask, init, dtype):
     o0, ex0 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_SPLIT, **kw)
     assert int(status.item()) == 0
     assert rel_err(o1.float(), o0.float()) < 1e-2
-    for name in ex0:
-        assert rel_err(ex1[name], ex0[name]) < 1e-4, name
+    for name in ex0:                                   # same operand rounding, different summation order of the gates
+        assert rel_err(ex1[name], ex0[name]) < 1e-3, name
     if B * L <= 4096:                                  # the naive oracle is a token loop
         f32 = [t.float().cpu() for t in dev]
         if dir_mask == 3:

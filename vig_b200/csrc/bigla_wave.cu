@@ -248,12 +248,11 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     } else if (warp < W_PREP_WARPS) {
         // =============================== prep warps: gates and operand scaling, in place ===============================
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(W_REGS_PREP));
-        constexpr int TPG = 16, NG = 8;                       // tokens per group (one warp), groups per chunk
-        const int cp = lane, grp = warp;
+        constexpr int NG = 8;                                 // groups (of 16 tokens, one per warp) per chunk
+        const int grp = warp;
         const bool raw_logits = p.gate_norm > 0.f;
         const float inv_norm = raw_logits ? 1.f / p.gate_norm : 1.f;
         const float clamp_lo = (p.clamp_min == p.clamp_min) ? p.clamp_min * LOG2E : -INFINITY;
-        const float lq = __log2f(fabsf(p.qscale));           // |scale * out_scale| folded into the exponent of the q operand
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
         int items = 0, ci = 0;
         WT_DECL
@@ -273,82 +272,117 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // ONE code path for both directions and for clamped / padded chunks (runtime selects instead of template
             // variants): the five roles of this CTA run different code at the same time, and what does not fit the
             // instruction cache stalls all of them.
-            const int dmask = cur.dir ? TPG - 1 : 0;          // scan order inside the group: token grp*TPG + (u ^ dmask)
+            // A warp owns 16 tokens (one group); a half-warp covers one token row with 4 channels per lane (8-byte
+            // accesses), so a lane handles 8 consecutive scan positions x 4 channels and the per-token overhead
+            // (addresses, padding test) is paid once per 4 channels.  Scan position sp = 8*half + u is token
+            // 16*warp + (sp ^ dmask).
             const int dir = cur.dir;
-            const uint32_t lane_off = (uint32_t)(cp & 3) * 4, c4 = (uint32_t)cp >> 2;
-            auto tile_off = [&](int u) {                      // byte offset of (token, my channel pair) in a swizzled 128-byte-row tile
-                const uint32_t tok = (uint32_t)(grp * TPG + (u ^ dmask));
-                return tok * 128 + ((c4 ^ (tok & 7)) << 4) + lane_off;
-            };
-            // The 16 tokens of a thread are handled as two halves by loops that run twice; the cumulative gates of
-            // the halves rotate through two register arrays, so the loop bodies are half the code of a full unroll
-            // while eight tokens still overlap their latencies.
-            constexpr int HT = TPG / 2;
-            float2 glA[HT], glB[HT];
+            const int dmask = dir ? 15 : 0;
+            const int half = lane >> 4, c4l = lane & 15;      // my half of the group, my 4 channels: 4*c4l .. 4*c4l+3
+            const uint32_t sw_chunk = (uint32_t)c4l >> 1, sw_in = (uint32_t)(c4l & 1) * 8;
+            float4 half_off;                                  // sum of the other half-warp's tokens when they precede mine in the scan
+            // The 8 tokens of a lane are handled as two halves of 4 by loops that run twice; the cumulative gates of the
+            // halves rotate through two register arrays (glA = first half, glB = second), so the loop bodies are half the
+            // code of a full unroll while four tokens x four channels still overlap their latencies.
+            float4 glA[4], glB[4];
+#ifdef VIG_WAVE_TIMING
+            const long long wt_p0 = clock64();
+#endif
             {
-                float2 run = make_float2(0.f, 0.f);
+                float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
                 for (int hh = 0; hh < 2; ++hh) {
 #pragma unroll
-                    for (int i = 0; i < HT; ++i) glA[i] = glB[i];
+                    for (int i = 0; i < 4; ++i) glA[i] = glB[i];
 #pragma unroll
-                    for (int i = 0; i < HT; ++i) {
-                        const int tok = grp * TPG + ((hh * HT + i) ^ dmask);
-                        float2 g = Pack2<T>::unpack(sg[tok * 32 + cp]);
-                        g.x = fmaxf(gate2_short(g.x, raw_logits, -inv_norm), clamp_lo);
-                        g.y = fmaxf(gate2_short(g.y, raw_logits, -inv_norm), clamp_lo);
-                        if (tok >= n_valid) g = make_float2(0.f, 0.f);
-                        run.x += g.x; run.y += g.y;
-                        glB[i] = run;                         // inclusive cumulative sum
+                    for (int i = 0; i < 4; ++i) {
+                        const int tok = warp * 16 + ((half * 8 + hh * 4 + i) ^ dmask);
+                        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(sg) + tok * 128 + c4l * 8);
+                        const float2 a = Pack2<T>::unpack(raw.x), b2 = Pack2<T>::unpack(raw.y);
+                        float4 g;
+                        g.x = fmaxf(gate2_short(a.x, raw_logits, -inv_norm), clamp_lo);
+                        g.y = fmaxf(gate2_short(a.y, raw_logits, -inv_norm), clamp_lo);
+                        g.z = fmaxf(gate2_short(b2.x, raw_logits, -inv_norm), clamp_lo);
+                        g.w = fmaxf(gate2_short(b2.y, raw_logits, -inv_norm), clamp_lo);
+                        if (tok >= n_valid) g = make_float4(0.f, 0.f, 0.f, 0.f);
+                        run.x += g.x; run.y += g.y; run.z += g.z; run.w += g.w;
+                        glB[i] = run;
                     }
                 }
-                reinterpret_cast<float2*>(part)[grp * 32 + cp] = run;
+                // the second half-warp continues the first half-warp's sum; it also knows the group's total
+                float4 first;
+                first.x = __shfl_sync(0xffffffffu, run.x, c4l); first.y = __shfl_sync(0xffffffffu, run.y, c4l);
+                first.z = __shfl_sync(0xffffffffu, run.z, c4l); first.w = __shfl_sync(0xffffffffu, run.w, c4l);
+                if (half) reinterpret_cast<float4*>(part)[grp * 16 + c4l] = make_float4(run.x + first.x, run.y + first.y, run.z + first.z, run.w + first.w);
+                if (!half) first = make_float4(0.f, 0.f, 0.f, 0.f);
+                half_off = first;                             // joins the group offset below
             }
             // the prep warps meet on an mbarrier, not a named barrier: its wait is bounded like every other wait here
             __syncwarp();
+#ifdef VIG_WAVE_TIMING
+            wt_acc[3] += clock64() - wt_p0;
+#endif
             if (lane == 0) { mbar_arrive(bar(B_PART)); WT(1, waiter.wait(bar(B_PART), m & 1)); }
             __syncwarp();
-            float2 off = make_float2(0.f, 0.f), gref = make_float2(0.f, 0.f), glast = make_float2(0.f, 0.f);
+#ifdef VIG_WAVE_TIMING
+            const long long wt_p1 = clock64();
+#endif
+            float4 off = half_off, gref = make_float4(0.f, 0.f, 0.f, 0.f), glast = gref;
 #pragma unroll 2
             for (int g2 = 0; g2 < NG; ++g2) {
-                const float2 s2 = reinterpret_cast<const float2*>(part)[g2 * 32 + cp];
+                const float4 s4 = reinterpret_cast<const float4*>(part)[g2 * 16 + c4l];
                 const bool before = dir ? g2 > grp : g2 < grp;            // scanned before my group
                 const bool in_ref = dir ? g2 >= NG / 2 : g2 < NG / 2;     // part of the cumulative gate at the middle token
-                if (before) { off.x += s2.x; off.y += s2.y; }
-                if (in_ref) { gref.x += s2.x; gref.y += s2.y; }
-                glast.x += s2.x; glast.y += s2.y;
+                if (before) { off.x += s4.x; off.y += s4.y; off.z += s4.z; off.w += s4.w; }
+                if (in_ref) { gref.x += s4.x; gref.y += s4.y; gref.z += s4.z; gref.w += s4.w; }
+                glast.x += s4.x; glast.y += s4.y; glast.z += s4.z; glast.w += s4.w;
             }
-            off.x -= gref.x; off.y -= gref.y;
-            float worst = 0.f;                                // largest |exponent| before clamping
+            off.x -= gref.x; off.y -= gref.y; off.z -= gref.z; off.w -= gref.w;
+#ifdef VIG_WAVE_TIMING
+            wt_acc[4] += clock64() - wt_p1;
+            const long long wt_p2 = clock64();
+#endif
+            // Log-gates are <= 0, so a lane's exponents are monotone along its 8 tokens: the largest magnitude (for the
+            // status flag; every exponent is clamped regardless) is at one of the two ends.
+            float worst = fmaxf(fmaxf(fabsf(off.x + glA[0].x), fabsf(off.y + glA[0].y)), fmaxf(fabsf(off.z + glA[0].z), fabsf(off.w + glA[0].w)));
+            worst = fmaxf(worst, fmaxf(fmaxf(fabsf(off.x + glB[3].x), fabsf(off.y + glB[3].y)), fmaxf(fabsf(off.z + glB[3].z), fabsf(off.w + glB[3].w))));
+            auto clampx = [](float e) { return fminf(fmaxf(e, -MAX_EXPONENT2), MAX_EXPONENT2); };
 #pragma unroll 1
             for (int hh = 0; hh < 2; ++hh) {
-                uint32_t rk[HT], rq[HT], offs[HT];
+                uint2 rk[4], rq[4];
+                uint32_t offs[4];
 #pragma unroll
-                for (int i = 0; i < HT; ++i) {                // all reads of the half before its writes: the tiles alias for the compiler
-                    offs[i] = tile_off(hh * HT + i);
-                    rk[i] = *reinterpret_cast<const uint32_t*>(stg + WS_K + offs[i]);
-                    rq[i] = *reinterpret_cast<const uint32_t*>(stg + WS_Q + offs[i]);
+                for (int i = 0; i < 4; ++i) {                 // all reads before the writes: the tiles alias for the compiler
+                    const uint32_t tok = (uint32_t)(warp * 16 + ((half * 8 + hh * 4 + i) ^ dmask));
+                    offs[i] = tok * 128 + ((sw_chunk ^ (tok & 7)) << 4) + sw_in;
+                    rk[i] = *reinterpret_cast<const uint2*>(stg + WS_K + offs[i]);
+                    rq[i] = *reinterpret_cast<const uint2*>(stg + WS_Q + offs[i]);
                 }
 #pragma unroll
-                for (int i = 0; i < HT; ++i) {
-                    float ex = off.x + glA[i].x, ey = off.y + glA[i].y;
-                    worst = fmaxf(worst, fmaxf(fabsf(ex), fabsf(ey)));
-                    ex = fminf(fmaxf(ex, -MAX_EXPONENT2), MAX_EXPONENT2);
-                    ey = fminf(fmaxf(ey, -MAX_EXPONENT2), MAX_EXPONENT2);
-                    // fp32 products, one rounding to the 16-bit operand (a packed 16-bit multiply would round the scale too)
-                    const float2 kk = Pack2<T>::unpack(rk[i]), qq = Pack2<T>::unpack(rq[i]);
-                    *reinterpret_cast<uint32_t*>(stg + WS_K + offs[i]) = Pack2<T>::pack(kk.x * ex2(-ex), kk.y * ex2(-ey));
-                    *reinterpret_cast<uint32_t*>(stg + WS_Q + offs[i]) = Pack2<T>::pack(qq.x * ex2(ex + lq), qq.y * ex2(ey + lq));
+                for (int i = 0; i < 4; ++i) {
+                    const float ex = clampx(off.x + glA[i].x), ey = clampx(off.y + glA[i].y), ez = clampx(off.z + glA[i].z), ew = clampx(off.w + glA[i].w);
+                    // fp32 products, one rounding to the 16-bit operand; scale * out_scale is applied to the output instead
+                    const float2 k0 = Pack2<T>::unpack(rk[i].x), k1 = Pack2<T>::unpack(rk[i].y);
+                    const float2 q0 = Pack2<T>::unpack(rq[i].x), q1 = Pack2<T>::unpack(rq[i].y);
+                    uint2 ko, qo;
+                    ko.x = Pack2<T>::pack(k0.x * ex2(-ex), k0.y * ex2(-ey)); ko.y = Pack2<T>::pack(k1.x * ex2(-ez), k1.y * ex2(-ew));
+                    qo.x = Pack2<T>::pack(q0.x * ex2(ex), q0.y * ex2(ey)); qo.y = Pack2<T>::pack(q1.x * ex2(ez), q1.y * ex2(ew));
+                    *reinterpret_cast<uint2*>(stg + WS_K + offs[i]) = ko;
+                    *reinterpret_cast<uint2*>(stg + WS_Q + offs[i]) = qo;
                 }
 #pragma unroll
-                for (int i = 0; i < HT; ++i) glA[i] = glB[i];
+                for (int i = 0; i < 4; ++i) glA[i] = glB[i];
             }
-            if (grp == 0) {                                   // per-channel factors of this iteration for the state warps
-                float* ve = vec + (m & 3) * 256;
-                ve[2 * cp] = ex2(glast.x); ve[2 * cp + 1] = ex2(glast.y);
-                ve[64 + 2 * cp] = ex2(glast.x - gref.x); ve[64 + 2 * cp + 1] = ex2(glast.y - gref.y);
-                ve[128 + 2 * cp] = gref.x; ve[128 + 2 * cp + 1] = gref.y;
-                ve[192 + 2 * cp] = glast.x; ve[192 + 2 * cp + 1] = glast.y;
+#ifdef VIG_WAVE_TIMING
+            __syncwarp();
+            wt_acc[5] += clock64() - wt_p2;
+#endif
+            if (grp == 0 && half == 0) {                      // per-channel factors of this iteration for the state warps
+                float* ve = vec + (m & 3) * 256 + 4 * c4l;
+                *reinterpret_cast<float4*>(ve) = make_float4(ex2(glast.x), ex2(glast.y), ex2(glast.z), ex2(glast.w));
+                *reinterpret_cast<float4*>(ve + 64) = make_float4(ex2(glast.x - gref.x), ex2(glast.y - gref.y), ex2(glast.z - gref.z), ex2(glast.w - gref.w));
+                *reinterpret_cast<float4*>(ve + 128) = gref;
+                *reinterpret_cast<float4*>(ve + 192) = glast;
             }
             const bool out_of_range = worst > MAX_EXPONENT2;
             if (out_of_range && p.status) atomicOr(p.status, 2);
@@ -363,7 +397,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         const int quad = warp & 3;                            // my 32 query rows and TMEM lanes
         const int row = 32 * quad + lane;
         const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
-        const float o_sign = p.qscale < 0.f ? -1.f : 1.f;
+        const float o_sign = p.qscale;                        // scale * out_scale, applied to the finished accumulators
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
         Item prev = cur;
         int items = 0, ci = 0, prev_ci = 0;
