@@ -48,6 +48,14 @@ __device__ __forceinline__ float log_sigmoid(float x) {
 }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// Sigmoid for kernels whose result is rounded to a 16-bit type: one MUFU (tanh.approx, ~2^-11 relative) instead of two
+// (exp + reciprocal) -- these kernels are bound by the quarter-rate MUFU pipe, not by DRAM.  fp32 keeps the exact form.
+template <typename T> __device__ __forceinline__ float sigmoid_t(float x) {
+    if (sizeof(T) == 4) return sigmoidf_(x);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+    return fmaf(0.5f, t, 0.5f);
+}
 
 // Parameter block of the bi-GLA launchers (host fills it from the C ABI arguments).
 struct BiglaParams {
