@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(EW_THREADS) dwconv3x3_kernel(const T* __restri
 // of 9 loads + 9 tap loads + 144 unpacks.  (The 16-byte form above spends most of its time unpacking on the
 // half-rate integer pipe.)  Consecutive threads own consecutive channel groups, so loads and stores are coalesced.
 template <typename T, int RUN>
-__global__ void __launch_bounds__(EW_THREADS) dwconv3x3_rows_kernel(const T* __restrict__ x, const T* __restrict__ wt,
+__global__ void __launch_bounds__(EW_THREADS, 2) dwconv3x3_rows_kernel(const T* __restrict__ x, const T* __restrict__ wt,
                                                                     const T* __restrict__ bias, T* __restrict__ y,
                                                                     int B, int h, int w, int C, int act) {
     using P2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
@@ -118,14 +118,16 @@ __global__ void __launch_bounds__(EW_THREADS) dwconv3x3_rows_kernel(const T* __r
             raw[ky] = (rok[ky] && xx >= 0 && xx < w) ? __ldg(reinterpret_cast<const uint2*>(rowp[ky] + (size_t)xx * C)) : make_uint2(0u, 0u);
     };
     float win[3][3][4];                                       // [column slot][row][channel]; slot of image column xx is (xx - x0 + 1) % 3
-    uint2 raw[3];
-    load_col(x0 - 1, raw);
+    constexpr int PF = 3;                                     // columns in flight
+    uint2 raw[PF][3];
+    load_col(x0 - 1, raw[0]);
+    load_col(x0, raw[1]);
 #pragma unroll
-    for (int ky = 0; ky < 3; ++ky) unpack4(raw[ky], win[0][ky]);
-    load_col(x0, raw);
+    for (int ky = 0; ky < 3; ++ky) unpack4(raw[0][ky], win[0][ky]);
 #pragma unroll
-    for (int ky = 0; ky < 3; ++ky) unpack4(raw[ky], win[1][ky]);
-    load_col(x0 + 1, raw);
+    for (int ky = 0; ky < 3; ++ky) unpack4(raw[1][ky], win[1][ky]);
+#pragma unroll
+    for (int j = 0; j < PF; ++j) load_col(x0 + 1 + j, raw[j]);
     T* yp = y + (((size_t)b * h + yy) * w) * C + c0;
 #pragma unroll
     for (int i = 0; i < RUN; ++i) {
@@ -134,8 +136,8 @@ __global__ void __launch_bounds__(EW_THREADS) dwconv3x3_rows_kernel(const T* __r
         constexpr int dummy = 0; (void)dummy;
         const int sl = i % 3, sc = (i + 1) % 3, sr = (i + 2) % 3;     // slots of columns xx-1, xx, xx+1 (static: the loop is unrolled)
 #pragma unroll
-        for (int ky = 0; ky < 3; ++ky) unpack4(raw[ky], win[sr][ky]);
-        if (i + 1 < RUN) load_col(xx + 2, raw);               // next step's right column is in flight during this step's math
+        for (int ky = 0; ky < 3; ++ky) unpack4(raw[i % PF][ky], win[sr][ky]);
+        if (i + PF < RUN) load_col(xx + 1 + PF, raw[i % PF]); // the right columns of the next PF steps are in flight during this step's math
         float acc[4] = {bf[0], bf[1], bf[2], bf[3]};
 #pragma unroll
         for (int ky = 0; ky < 3; ++ky)
