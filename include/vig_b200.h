@@ -206,6 +206,20 @@ VIG_API int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const voi
 VIG_API int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream);
 
 /*
+ * Projection with the residual add and the next RMSNorm as its epilogue (bf16 / fp16): r = x W^T + residual (r = x W^T
+ * when residual is NULL), h = RMSNorm(r) * norm_weight -- `o_proj` followed by `mlp_norm(h, residual, prenorm=True)`,
+ * and `down_proj` followed by the next block's `attn_norm` / the model's final norm (classification/models/vig.py:463,
+ * 497, 596-606; fla/modules/rmsnorm.py:491-512).  One tcgen05 GEMM kernel; the projection output is not written.
+ * Same roundings as the unfused sequence (projection rounded to the tensor dtype, sum rounded to the tensor dtype).
+ * x: [M, K] with row stride ldx; w: [N, K] contiguous; residual, out_r, out_h: [M, N] contiguous; K % 64 == 0,
+ * N one of 64, 128, 192, 256, 384.  status_dev: optional int32 on the device, bit 0 = a bounded wait ran out.
+ */
+VIG_API int vig_linear_add_rmsnorm_supported(int64_t M, int K, int N, int dtype);
+VIG_API int vig_linear_add_rmsnorm_fwd(const void* x, int64_t ldx, const void* w, const void* residual, const void* norm_weight,
+                                       void* out_r, void* out_h, int64_t M, int K, int N, float eps, int dtype,
+                                       int32_t* status_dev, void* stream);
+
+/*
  * SwiGLU: out = gate * sigmoid(gate) * y (fla/modules/activations.py:109-113, the `swiglu` half of
  * `swiglu_linear`).  gate, y: [rows, I] with row stride ld_in elements (gate and y are the two halves of
  * one [rows, 2I] projection in the reference, vig.py:494-497); out: [rows, I] with row stride ld_out.

@@ -123,6 +123,48 @@ def test_swiglu(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N,with_res", [(392, 192, 192, True), (1000, 512, 192, True), (128, 64, 64, False), (70, 384, 384, True),
+                                            (5000, 1024, 384, True), (300, 192, 128, True), (260, 128, 256, True)])
+def test_linear_add_rmsnorm_fused_gemm(dtype, M, K, N, with_res):
+    """Projection + residual add + RMSNorm in one tcgen05 kernel against F.linear followed by vig_add_rmsnorm_fwd
+    (same roundings) and against fp32 arithmetic."""
+    import torch.nn.functional as F
+    import vig_b200
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype).cuda()
+    res = torch.randn(M, N, generator=g).to(dtype).cuda() if with_res else None
+    nw = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype).cuda()
+    assert vig_b200.ops.linear_add_rmsnorm_supported(x, w)
+    h, r = vig_b200.ops.linear_add_rmsnorm(x, w, res, nw, 1e-6)
+    y = F.linear(x, w)
+    if with_res:
+        h_ref, r_ref = vig_b200.add_rmsnorm(y, nw, residual=res, eps=1e-6, prenorm=True)
+    else:
+        h_ref, r_ref = vig_b200.add_rmsnorm(y, nw, eps=1e-6), y
+    assert rel_err(r.float(), r_ref.float()) < 5e-3          # the two GEMMs sum in different orders before rounding
+    assert rel_err(h.float(), h_ref.float()) < 5e-3
+    r32 = x.float() @ w.float().t() + (res.float() if with_res else 0)
+    h32 = r32 * torch.rsqrt(r32.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+    assert rel_err(r.float(), r32) < 2e-2 and rel_err(h.float(), h32) < 2e-2
+
+
+def test_model_with_norms_fused_into_projection_epilogues_matches_default_path():
+    """``ViG.fuse_norm_epilogues``: same logits as the default path (same roundings, different GEMM kernels)."""
+    import vig_b200
+    shape = oracle.ViGShape(192, 3, 3, 1.0, 1.0, True, True, num_classes=16)
+    model = vig_b200.ViG.from_shape(shape)
+    model.load_state_dict(oracle.make_state_dict(shape, seed=4))
+    model = model.cuda().bfloat16().eval()
+    images = oracle.make_images(2, 224, seed=5).cuda().bfloat16()
+    with torch.no_grad():
+        ref = model(images)
+        model.fuse_norm_epilogues = True
+        got = model(images)
+    assert rel_err(got.float(), ref.float()) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,K,I", [(392, 192, 512), (1000, 384, 1024), (128, 64, 64), (70, 192, 128), (5000, 192, 512)])
 def test_linear_swiglu_fused_gemm(dtype, M, K, I):
     import vig_b200

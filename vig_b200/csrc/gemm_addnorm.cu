@@ -1,0 +1,238 @@
+// r = x W^T + residual,  h = RMSNorm(r) * norm_weight   in one kernel (bf16 / fp16): the output projection of the
+// attention branch (or the down projection of the MLP) with the residual add and the next RMSNorm as its epilogue
+// (classification/models/vig.py:463 `o_proj`, :497 `down_proj`, :596-606 `attn_norm` / `mlp_norm` with residual and
+// prenorm).  The projection output never goes to HBM: instead of (GEMM: write y) + (norm: read y, read residual,
+// write r, write h) the kernel reads the residual and writes r and h.
+//
+// tcgen05 GEMM with full output rows per tile.  A persistent CTA owns tiles of 128 rows; x and W stream through a ring
+// of stages [128 x 64 of x | N x 64 of W] (TMA, 128-byte swizzle); the accumulator [128 x N] fp32 lives in tensor
+// memory (N <= 384 columns; two buffers when 2N <= 512, so the epilogue of a tile overlaps the MMAs of the next).
+// Epilogue (one thread per row, its TMEM lane): pass 1 adds the residual with the roundings of the unfused path
+// (projection rounded to T, sum rounded to T), stores r and accumulates the sum of squares; pass 2 re-reads its own r
+// (L1/L2 hits), scales and stores h.  Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 epilogue.  Every wait
+// is bounded.
+#include "tc_common.cuh"
+
+namespace vig {
+namespace {
+
+using namespace tc;
+
+constexpr int AN_BK = 64;                      // k elements per stage (128 bytes per row)
+constexpr int AN_THREADS = 64 + 128;
+constexpr int AN_A_BYTES = 128 * AN_BK * 2;    // [128 rows x 64 k]
+
+struct AnMaps { CUtensorMap x, w; };
+
+template <typename T, int NT>            // NT = N, the row width, a compile-time constant so that a row lives in registers
+__global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const __grid_constant__ AnMaps maps, const T* __restrict__ residual,
+                                                                           const T* __restrict__ norm_w, T* __restrict__ out_r,
+                                                                           T* __restrict__ out_h, int M, int KB, int CH, int nstage,
+                                                                           float eps, int32_t* status) {
+    extern __shared__ uint8_t an_smem_raw[];
+    uint8_t* smem = an_smem_raw + ((1024u - (smem_u32(an_smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    constexpr int N = NT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t stage_bytes = AN_A_BYTES + (uint32_t)N * AN_BK * 2;
+    const uint32_t off_bar = (uint32_t)nstage * stage_bytes;
+    const uint32_t bar_full = sbase + off_bar, bar_empty = bar_full + 8 * 8;          // up to 8 stages
+    const uint32_t bar_acc_full = bar_empty + 8 * 8, bar_acc_empty = bar_acc_full + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * 20);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const Waiter waiter{abort_flag, status};
+    const int nbuf = 2 * N <= 512 ? 2 : 1;
+    const int nch = N / CH;                                   // MMAs of N = CH columns per k step
+
+    if (tid == 0) {
+        for (int s = 0; s < nstage; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int ntiles = (M + 127) / 128;
+
+    if (warp == 0) {
+        if (lane == 0) {                          // ---- TMA producer -------------------------------------------
+            uint32_t st = 0, phase = 0;
+            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+                for (int kb = 0; kb < KB; ++kb) {
+                    waiter.wait(bar_empty + 8 * st, phase ^ 1u);
+                    if (*abort_flag) break;
+                    mbar_expect_tx(bar_full + 8 * st, stage_bytes);
+                    const uint32_t dst = sbase + st * stage_bytes;
+                    tma_load_2d(dst, &maps.x, kb * AN_BK, tile * 128, bar_full + 8 * st);
+                    for (int c = 0; c < nch; ++c)
+                        tma_load_2d(dst + AN_A_BYTES + (uint32_t)c * CH * AN_BK * 2, &maps.w, kb * AN_BK, c * CH, bar_full + 8 * st);
+                    if (++st == (uint32_t)nstage) { st = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                          // ---- MMA issuer ---------------------------------------------
+            const uint32_t idesc = (1u << 4) | (Pack2<T>::FMT << 7) | (Pack2<T>::FMT << 10) | (((uint32_t)CH >> 3) << 17) | ((128u >> 4) << 24);
+            uint32_t st = 0, phase = 0, acc_it = 0;
+            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++acc_it) {
+                const uint32_t buf = nbuf == 2 ? (acc_it & 1u) : 0u;
+                const uint32_t use = nbuf == 2 ? (acc_it >> 1) : acc_it;       // how often this buffer has been used before
+                waiter.wait(bar_acc_empty + 8 * buf, (use & 1u) ^ 1u);         // the epilogue has drained this buffer
+                if (*abort_flag) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb) {
+                    waiter.wait(bar_full + 8 * st, phase);
+                    tc_fence_after();
+                    const uint32_t a_addr = sbase + st * stage_bytes, b_addr = a_addr + AN_A_BYTES;
+                    for (int c = 0; c < nch; ++c) {
+                        const uint32_t d = tmem + buf * (uint32_t)N + (uint32_t)c * CH;
+#pragma unroll
+                        for (int k4 = 0; k4 < AN_BK / 16; ++k4)
+                            tc_mma(d, make_desc(a_addr + k4 * 32), make_desc(b_addr + (uint32_t)c * CH * AN_BK * 2 + k4 * 32), idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * st);                              // the stage is free when these MMAs are done
+                    if (++st == (uint32_t)nstage) { st = 0; phase ^= 1u; }
+                }
+                tc_commit(bar_acc_full + 8 * buf);
+            }
+        }
+    } else {                                      // ---- epilogue: one thread per row --------------------------------
+        // The thread's residual row is requested before the tile's accumulator is waited for (its latency hides behind
+        // the MMAs), the sums r replace it in the same registers, and pass 2 works from registers: no dependent global
+        // round trips inside the loops.  (192 threads per CTA: registers are plentiful.)
+        constexpr int NV = NT / 8;                // 16-byte vectors per row
+        const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
+        const int r_in_tile = 32 * (warp & 3) + lane;
+        uint32_t acc_it = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++acc_it) {
+            const uint32_t buf = nbuf == 2 ? (acc_it & 1u) : 0u;
+            const uint32_t use = nbuf == 2 ? (acc_it >> 1) : acc_it;
+            const int64_t row = (int64_t)tile * 128 + r_in_tile;
+            const bool live = row < M;
+            uint4 rr[NV];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) rr[v] = (live && residual) ? __ldg(reinterpret_cast<const uint4*>(residual + row * NT) + v) : make_uint4(0u, 0u, 0u, 0u);
+            if (lane == 0) waiter.wait(bar_acc_full + 8 * buf, use & 1u);
+            __syncwarp();
+            if (*abort_flag) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + lane_base + buf * (uint32_t)NT;
+            float ss = 0.f;
+#pragma unroll
+            for (int c = 0; c < NT; c += 32) {    // pass 1: r = T(T(acc) + residual), sum of squares
+                float a[32];
+                tc_ld32(acc + c, a);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint4& rv = rr[c / 8 + j];
+                    uint32_t* rw = reinterpret_cast<uint32_t*>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // the unfused path rounds the projection to T before the add, and the sum to T before the norm
+                        const float2 y = Pack2<T>::unpack(Pack2<T>::pack(a[8 * j + 2 * e], a[8 * j + 2 * e + 1]));
+                        const float2 rf = Pack2<T>::unpack(rw[e]);
+                        rw[e] = Pack2<T>::pack(y.x + rf.x, y.y + rf.y);       // residual words are zero when there is none
+                        const float2 s2 = Pack2<T>::unpack(rw[e]);
+                        ss = fmaf(s2.x, s2.x, ss); ss = fmaf(s2.y, s2.y, ss);
+                    }
+                    if (live) reinterpret_cast<uint4*>(out_r + row * NT + c)[j] = rv;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_plain(bar_acc_empty + 8 * buf);       // the accumulator is read: pass 2 works from registers
+            if (live) {
+                const float rstd = rsqrtf(ss / (float)NT + eps);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {    // pass 2: h = r * rstd * norm_weight
+                    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + v);
+                    const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rr[v]);
+                    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 rf = Pack2<T>::unpack(rw[e]), wf = Pack2<T>::unpack(ww[e]);
+                        o[e] = Pack2<T>::pack(rf.x * rstd * wf.x, rf.y * rstd * wf.y);
+                    }
+                    reinterpret_cast<uint4*>(out_h + row * NT)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+int an_chunk(int N) { return N % 192 == 0 ? 192 : (N % 128 == 0 ? 128 : 64); }
+
+}  // namespace
+}  // namespace vig
+
+using namespace vig;
+
+extern "C" int vig_linear_add_rmsnorm_supported(int64_t M, int K, int N, int dtype) {
+    if (dtype != VIG_DTYPE_BF16 && dtype != VIG_DTYPE_F16) return 0;
+    if (M <= 0 || K <= 0 || K % AN_BK || !(N == 64 || N == 128 || N == 192 || N == 256 || N == 384)) return 0;
+    return tc::encode_fn() != nullptr;
+}
+
+extern "C" int vig_linear_add_rmsnorm_fwd(const void* x, int64_t ldx, const void* w, const void* residual, const void* norm_weight,
+                                          void* out_r, void* out_h, int64_t M, int K, int N, float eps, int dtype,
+                                          int32_t* status_dev, void* stream) {
+    if (!x || !w || !norm_weight || !out_r || !out_h) return VIG_ERR_NULL;
+    if (M == 0) return VIG_OK;
+    if (!vig_linear_add_rmsnorm_supported(M, K, N, dtype)) return VIG_ERR_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(residual) |
+         reinterpret_cast<uintptr_t>(norm_weight) | reinterpret_cast<uintptr_t>(out_r) | reinterpret_cast<uintptr_t>(out_h)) & 15)
+        return VIG_ERR_ALIGN;
+    if (ldx < K || (ldx * 2) % 16 || M >= (1ll << 31) - 128) return VIG_ERR_ARG;
+    const int CH = an_chunk(N);
+    AnMaps maps;
+    if (!tc::make_map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !tc::make_map_2d(&maps.w, w, N, K, K, CH, dtype)) return VIG_ERR_DEVICE;
+    const int stage_bytes = AN_A_BYTES + N * AN_BK * 2;
+    int nstage = (200 * 1024) / stage_bytes;
+    if (nstage > 6) nstage = 6;
+    if (nstage < 2) return VIG_ERR_SHAPE;
+    const size_t smem = (size_t)nstage * stage_bytes + 8 * 20 + 16 + 1024;
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaError_t e;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return VIG_ERR_DEVICE;
+    if (!sm_count[dev]) {
+        int sms = 0;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        sm_count[dev] = sms;
+    }
+    const int64_t ntiles = (M + 127) / 128;
+    const int grid = (int)(ntiles < sm_count[dev] ? ntiles : sm_count[dev]);
+#define VIG_AN_LAUNCH(TT, NN)                                                                                                  \
+    {                                                                                                                          \
+        auto kfn = linear_add_rmsnorm_kernel<TT, NN>;                                                                          \
+        if ((e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
+        kfn<<<grid, AN_THREADS, smem, (cudaStream_t)stream>>>(maps, (const TT*)residual, (const TT*)norm_weight, (TT*)out_r,   \
+                                                               (TT*)out_h, (int)M, K / AN_BK, CH, nstage, eps, status_dev);   \
+    }
+#define VIG_AN_WIDTHS(TT)                                                                                                      \
+    switch (N) {                                                                                                               \
+        case 64: VIG_AN_LAUNCH(TT, 64) break;                                                                                  \
+        case 128: VIG_AN_LAUNCH(TT, 128) break;                                                                                \
+        case 192: VIG_AN_LAUNCH(TT, 192) break;                                                                                \
+        case 256: VIG_AN_LAUNCH(TT, 256) break;                                                                                \
+        default: VIG_AN_LAUNCH(TT, 384) break;                                                                                 \
+    }
+    if (dtype == VIG_DTYPE_BF16) VIG_AN_WIDTHS(__nv_bfloat16) else VIG_AN_WIDTHS(__half)
+#undef VIG_AN_WIDTHS
+#undef VIG_AN_LAUNCH
+    return (int)cudaGetLastError();
+}

@@ -100,6 +100,8 @@ class GatedLinearAttention(nn.Module):
         else:
             scan_fn(q, k, v, g_fwd, g_bwd, **scan_kw)
         y = ops.gate_inject(o, xs, gate_logits, self.g_norm.weight, self.l_norm.weight, self.g_norm.eps, self.use_out_act)
+        if kwargs.get("skip_o_proj"):                         # the caller fuses the output projection with the next norm
+            return y
         return self.o_proj(y)
 
 
@@ -146,6 +148,27 @@ class GLABlock(nn.Module):
         """Reference signature: returns a 1-tuple with ``residual + mlp(norm(residual))``."""
         h, residual = self.forward_deferred(hidden_states, None, **kwargs)
         return (residual + h,)
+
+    def fused_epilogues_supported(self, x):
+        """True when both projections of the block can run with the residual add and the following RMSNorm as their
+        epilogue (``ops.linear_add_rmsnorm``: 16-bit CUDA tensors, hidden size <= 384, no projection bias)."""
+        return (self.attn.o_proj.bias is None and self.mlp.down_proj.bias is None and x.shape[-1] <= 192 and
+                ops.linear_add_rmsnorm_supported(x, self.attn.o_proj.weight) and
+                x.shape[-1] == self.mlp.down_proj.weight.shape[0] and self.mlp.down_proj.weight.shape[1] % 64 == 0)
+
+    def forward_prenormed(self, h, residual, next_norm, **kwargs):
+        """The block with its norms moved into the projections' epilogues: takes ``h = attn_norm(residual stream)`` and
+        the residual stream, returns ``(next_norm(new residual stream), new residual stream)`` -- ``next_norm`` is the
+        next block's ``attn_norm`` or the model's final norm.  Same arithmetic as ``forward_deferred`` chained."""
+        y = self.attn(h, skip_o_proj=True, **kwargs)
+        h2, residual = ops.linear_add_rmsnorm(y, self.attn.o_proj.weight, residual, self.mlp_norm.weight, self.mlp_norm.eps)
+        m = self.mlp
+        if ops.linear_swiglu_supported(h2, m.gate_proj.weight, preferred=True):
+            z = ops.linear_swiglu(h2, m.gate_proj.weight)
+        else:
+            gate, yy = m.gate_proj(h2).chunk(2, -1)
+            z = ops.swiglu(gate, yy)
+        return ops.linear_add_rmsnorm(z, m.down_proj.weight, residual, next_norm.weight, next_norm.eps)
 
     def forward_deferred(self, hidden_states, residual, **kwargs):
         """Same block, but the trailing residual add is left to the caller's next norm: takes the pair

@@ -286,6 +286,35 @@ def layernorm_act(x, weight, bias, eps=1e-5, act_swish=False, pre_bias=None):
     return y
 
 
+def linear_add_rmsnorm_supported(x, w):
+    """True when ``linear_add_rmsnorm`` can run on these operands (16-bit CUDA tensors, K % 64 == 0, N in {64, 128, 192, 256, 384})."""
+    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and w.dtype == x.dtype and x.stride(-1) == 1):
+        return False
+    N, K = w.shape
+    M = x.numel() // K
+    return bool(_lib.lib().vig_linear_add_rmsnorm_supported(M, K, N, _lib.dtype_code(x)))
+
+
+def linear_add_rmsnorm(x, w, residual, norm_weight, eps=1e-6):
+    """``r = x @ w.T + residual`` (``residual`` may be None), ``h = RMSNorm(r) * norm_weight`` in one tensor-core kernel
+    (see ``vig_linear_add_rmsnorm_fwd``).  Returns ``(h, r)``; x: [..., K], w: [N, K], residual: [..., N]."""
+    _lib.require_cuda(x, w)
+    N, K = w.shape
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M = x2.shape[0]
+    res = residual.reshape(M, N).contiguous() if residual is not None else None
+    out_r = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    out_h = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    st = _lib.lib().vig_linear_add_rmsnorm_fwd(_lib.ptr(x2), x2.stride(0), _lib.ptr(w.contiguous()), _lib.ptr(res), _lib.ptr(norm_weight),
+                                               _lib.ptr(out_r), _lib.ptr(out_h), M, K, N, float(eps), _lib.dtype_code(x), None,
+                                               _lib.stream_ptr())
+    _lib.check(st, "vig_linear_add_rmsnorm_fwd")
+    return out_h.view(*lead, N), out_r.view(*lead, N)
+
+
 def stem_unfold(x, s):
     """Space-to-depth with the first stem convolution's padding: ``[B,Cin,H,W] -> [B, H/s+1, W/s+1, s*s*Cin]``
     (see ``vig_stem_unfold_fwd``)."""

@@ -99,6 +99,7 @@ class ViG(nn.Module):
                  use_out_act=False, use_act_in_conv=True, expand_k=0.5, expand_v=1, use_bias_in_patch=True,
                  use_bias_in_dwconv=False, clamp_min=None, rms_norm_eps=1e-6, **unused):
         super().__init__()
+        self.fuse_norm_epilogues = False
         self.embed_dim, self.num_classes = embed_dim, num_classes
         self.config = SimpleNamespace(hidden_size=embed_dim, num_hidden_layers=depth, num_attention_heads=num_heads,
                                       expand_k=expand_k, expand_v=expand_v, rms_norm_eps=rms_norm_eps, use_out_act=use_out_act,
@@ -136,6 +137,15 @@ class ViG(nn.Module):
     def forward_features(self, x):
         x, hw = self.patch_embed(x)
         x = x + self._pos(hw)
+        # Optional path (``fuse_norm_epilogues``): every residual add + RMSNorm runs as the epilogue of the projection in
+        # front of it.  Off by default: measured on B200 at 140 us per call against 112 us for cuBLAS + the norm kernel
+        # (its row-per-thread stores are scattered; a TMA-store epilogue is the known fix).
+        if self.fuse_norm_epilogues and len(self.blocks) and all(blk.fused_epilogues_supported(x) for blk in self.blocks):
+            h, residual = self.blocks[0].attn_norm(x), x
+            for i, blk in enumerate(self.blocks):
+                nxt = self.blocks[i + 1].attn_norm if i + 1 < len(self.blocks) else self.norm
+                h, residual = blk.forward_prenormed(h, residual, nxt, patch_resolution=hw)
+            return h.mean(dim=1)
         h, residual = x, None
         for blk in self.blocks:
             h, residual = blk.forward_deferred(h, residual, patch_resolution=hw)
