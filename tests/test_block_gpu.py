@@ -158,6 +158,7 @@ def test_model_with_norms_fused_into_projection_epilogues_matches_default_path()
     model = model.cuda().bfloat16().eval()
     images = oracle.make_images(2, 224, seed=5).cuda().bfloat16()
     with torch.no_grad():
+        model.fuse_norm_epilogues = False
         ref = model(images)
         model.fuse_norm_epilogues = True
         got = model(images)

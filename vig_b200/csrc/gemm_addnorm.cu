@@ -19,10 +19,15 @@ namespace {
 using namespace tc;
 
 constexpr int AN_BK = 64;                      // k elements per stage (128 bytes per row)
-constexpr int AN_THREADS = 64 + 128;
+constexpr int AN_THREADS = 64 + 256;            // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quadrant)
 constexpr int AN_A_BYTES = 128 * AN_BK * 2;    // [128 rows x 64 k]
 
-struct AnMaps { CUtensorMap x, w; };
+struct AnMaps { CUtensorMap x, w, res, r, h; };
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T, int NT>            // NT = N, the row width, a compile-time constant so that a row lives in registers
 __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const __grid_constant__ AnMaps maps, const T* __restrict__ residual,
@@ -35,10 +40,17 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
     constexpr int N = NT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t stage_bytes = AN_A_BYTES + (uint32_t)N * AN_BK * 2;
-    const uint32_t off_bar = (uint32_t)nstage * stage_bytes;
+    // rows of up to 192 values leave through shared memory and TMA stores (coalesced by the hardware); wider rows use
+    // per-thread row stores
+    constexpr bool TMA_EPI = NT <= 192;
+    constexpr uint32_t E_BYTES = (uint32_t)(NT / 64) * 128 * 128;      // one [128 x N] tile as N/64 swizzled boxes
+    const uint32_t off_e = (uint32_t)nstage * stage_bytes;
+    const uint32_t off_bar = off_e + (TMA_EPI ? 2 * E_BYTES : 0);
     const uint32_t bar_full = sbase + off_bar, bar_empty = bar_full + 8 * 8;          // up to 8 stages
     const uint32_t bar_acc_full = bar_empty + 8 * 8, bar_acc_empty = bar_acc_full + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * 20);
+    const uint32_t bar_res_full = bar_acc_empty + 16, bar_e_free = bar_res_full + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * 24);
+    float* ss_part = reinterpret_cast<float*>(smem + off_bar + 8 * 24 + 16);       // [2 column halves][128 rows]
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const Waiter waiter{abort_flag, status};
     const int nbuf = 2 * N <= 512 ? 2 : 1;
@@ -46,7 +58,10 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
 
     if (tid == 0) {
         for (int s = 0; s < nstage; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 128); }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, TMA_EPI ? 256 : 128);
+            mbar_init(bar_res_full + 8 * b, 1); mbar_init(bar_e_free + 8 * b, 1);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -62,8 +77,20 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
 
     if (warp == 0) {
         if (lane == 0) {                          // ---- TMA producer -------------------------------------------
-            uint32_t st = 0, phase = 0;
-            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            uint32_t st = 0, phase = 0, t_it = 0;
+            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t_it) {
+                if (TMA_EPI) {                        // the tile's residual rows, into the epilogue buffer of this tile
+                    const uint32_t eb = t_it & 1u;
+                    waiter.wait(bar_e_free + 8 * eb, ((t_it >> 1) & 1u) ^ 1u);
+                    if (*abort_flag) break;
+                    if (residual) {
+                        mbar_expect_tx(bar_res_full + 8 * eb, E_BYTES);
+                        for (int bx = 0; bx < NT / 64; ++bx)
+                            tma_load_2d(sbase + off_e + eb * E_BYTES + bx * 16384, &maps.res, bx * 64, tile * 128, bar_res_full + 8 * eb);
+                    } else {
+                        mbar_arrive_plain(bar_res_full + 8 * eb);
+                    }
+                }
                 for (int kb = 0; kb < KB; ++kb) {
                     waiter.wait(bar_empty + 8 * st, phase ^ 1u);
                     if (*abort_flag) break;
@@ -102,7 +129,90 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
                 tc_commit(bar_acc_full + 8 * buf);
             }
         }
-    } else {                                      // ---- epilogue: one thread per row --------------------------------
+    } else if (TMA_EPI) {                         // ---- epilogue through shared memory and TMA stores ----------------
+        // One thread per row (its TMEM lane).  The residual tile arrives by TMA in 128-byte-swizzled boxes; pass 1 turns
+        // it into r in place (and keeps r in registers), a TMA store sends it out; pass 2 writes h over the same boxes
+        // once that store has read them, and a second TMA store sends h out.
+        constexpr int NH = NT / 2, NV = NH / 8;   // my half of the row: NH columns = NV 16-byte vectors
+        const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
+        const int rr_ = 32 * (warp & 3) + lane;   // my row of the tile
+        const int chalf = (warp - 2) >> 2;        // warps 2..5 take the first half of the columns, 6..9 the second
+        const bool leader = warp == 2 && lane == 0;
+        uint32_t acc_it = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++acc_it) {
+            const uint32_t buf = nbuf == 2 ? (acc_it & 1u) : 0u;
+            const uint32_t use = nbuf == 2 ? (acc_it >> 1) : acc_it;
+            const uint32_t eb = acc_it & 1u;
+            uint8_t* ebuf = smem + off_e + eb * E_BYTES;
+            if (lane == 0) { waiter.wait(bar_res_full + 8 * eb, (acc_it >> 1) & 1u); waiter.wait(bar_acc_full + 8 * buf, use & 1u); }
+            __syncwarp();                         // (no early exit on an abort: the four warps meet at named barriers below,
+            tc_fence_after();                     //  and after an abort every wait returns at once)
+            const uint32_t acc = tmem + lane_base + buf * (uint32_t)NT;
+            uint4 rr[NV];
+            float ss = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < NH; cc += 32) { // pass 1: r = T(T(acc) + residual), sum of squares
+                const int c = chalf * NH + cc;
+                float a[32];
+                tc_ld32(acc + c, a);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int v = c / 8 + j;      // 16-byte vector of the row: box v / 8, chunk v % 8
+                    uint4* cell = reinterpret_cast<uint4*>(ebuf + (v / 8) * 16384 + rr_ * 128 + (((v % 8) ^ (rr_ & 7)) << 4));
+                    uint4 rv = residual ? *cell : make_uint4(0u, 0u, 0u, 0u);
+                    uint32_t* rw = reinterpret_cast<uint32_t*>(&rv);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        // the unfused path rounds the projection to T before the add, and the sum to T before the norm
+                        const float2 y = Pack2<T>::unpack(Pack2<T>::pack(a[8 * j + 2 * e], a[8 * j + 2 * e + 1]));
+                        const float2 rf = Pack2<T>::unpack(rw[e]);
+                        rw[e] = Pack2<T>::pack(y.x + rf.x, y.y + rf.y);
+                        const float2 s2 = Pack2<T>::unpack(rw[e]);
+                        ss = fmaf(s2.x, s2.x, ss); ss = fmaf(s2.y, s2.y, ss);
+                    }
+                    *cell = rv;
+                    rr[cc / 8 + j] = rv;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_plain(bar_acc_empty + 8 * buf);       // the accumulator is read
+            ss_part[chalf * 128 + rr_] = ss;                  // the other half of my row belongs to another warp
+            fence_proxy_async();
+            epi_bar_sync();
+            ss += ss_part[(chalf ^ 1) * 128 + rr_];
+            if (leader) {
+                for (int bx = 0; bx < NT / 64; ++bx) tma_store_2d(&maps.r, bx * 64, tile * 128, sbase + off_e + eb * E_BYTES + bx * 16384);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the boxes may be overwritten
+            }
+            epi_bar_sync();
+            const float rstd = rsqrtf(ss / (float)NT + eps);
+#pragma unroll
+            for (int vv = 0; vv < NV; ++vv) {     // pass 2: h = r * rstd * norm_weight, into the same boxes
+                const int v = chalf * NV + vv;
+                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(norm_w) + v);
+                const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rr[vv]);
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 rf = Pack2<T>::unpack(rw[e]), wf = Pack2<T>::unpack(ww[e]);
+                    o[e] = Pack2<T>::pack(rf.x * rstd * wf.x, rf.y * rstd * wf.y);
+                }
+                *reinterpret_cast<uint4*>(ebuf + (v / 8) * 16384 + rr_ * 128 + (((v % 8) ^ (rr_ & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            fence_proxy_async();
+            epi_bar_sync();
+            if (leader) {
+                for (int bx = 0; bx < NT / 64; ++bx) tma_store_2d(&maps.h, bx * 64, tile * 128, sbase + off_e + eb * E_BYTES + bx * 16384);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                mbar_arrive_plain(bar_e_free + 8 * eb);       // the buffer may take the residual of the tile after next
+            }
+        }
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores have landed before the CTA exits
+    } else if (warp < 6) {                        // ---- epilogue for wide rows: one thread per row, per-thread stores ----
         // The thread's residual row is requested before the tile's accumulator is waited for (its latency hides behind
         // the MMAs), the sums r replace it in the same registers, and pass 2 works from registers: no dependent global
         // round trips inside the loops.  (192 threads per CTA: registers are plentiful.)
@@ -203,7 +313,17 @@ extern "C" int vig_linear_add_rmsnorm_fwd(const void* x, int64_t ldx, const void
     int nstage = (200 * 1024) / stage_bytes;
     if (nstage > 6) nstage = 6;
     if (nstage < 2) return VIG_ERR_SHAPE;
-    const size_t smem = (size_t)nstage * stage_bytes + 8 * 20 + 16 + 1024;
+    const bool tma_epi = N <= 192;
+    const size_t e_bytes = tma_epi ? 2 * (size_t)(N / 64) * 16384 : 0;
+    if (tma_epi) {                                  // the ring gets what the two epilogue tiles leave of the 227 KB
+        nstage = (int)((227 * 1024 - 4096 - e_bytes) / stage_bytes);
+        if (nstage > 6) nstage = 6;
+        if (nstage < 2) return VIG_ERR_SHAPE;
+    }
+    const size_t smem = (size_t)nstage * stage_bytes + e_bytes + 8 * 24 + 16 + 2 * 128 * 4 + 1024;
+    if (tma_epi && ((residual && !tc::make_map_2d(&maps.res, residual, M, N, N, 128, dtype)) || !tc::make_map_2d(&maps.r, out_r, M, N, N, 128, dtype) ||
+                    !tc::make_map_2d(&maps.h, out_h, M, N, N, 128, dtype)))
+        return VIG_ERR_DEVICE;
     static int sm_count[64] = {};
     int dev = 0;
     cudaError_t e;
