@@ -196,6 +196,11 @@ VIG_API int vig_add_rmsnorm_fwd(const void* x, const void* residual, const void*
  */
 VIG_API int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, void* y,
                           int64_t rows, int N, float eps, int act_swish, int dtype, void* stream);
+/* The same, followed by `+ post_add[row % post_period]` (post_add: [post_period, N], added to the rounded result like a
+ * separate add): the last LayerNorm2d of the stem with the position-embedding add of `ViG.forward_features`
+ * (classification/models/vig.py:860-866) folded in. */
+VIG_API int vig_layernorm_act_add_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, const void* post_add,
+                                      int64_t post_period, void* y, int64_t rows, int N, float eps, int act_swish, int dtype, void* stream);
 
 /*
  * Space-to-depth of the input image for the stem's first convolution (`V2PatchEmbed`, classification/models/vig.py:

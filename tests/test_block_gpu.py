@@ -78,6 +78,19 @@ def test_layernorm_act(dtype, N, act):
     assert rel_err(y.float(), ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_layernorm_with_trailing_add(dtype):
+    """LayerNorm followed by `+ post_add[row % P]` in one kernel == the kernel plus a separate add."""
+    import vig_b200
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(3, 35, 192, generator=g).to(dtype).cuda()
+    w, b = (1 + 0.1 * torch.randn(192, generator=g)).to(dtype).cuda(), (0.1 * torch.randn(192, generator=g)).to(dtype).cuda()
+    pos = torch.randn(1, 35, 192, generator=g).to(dtype).cuda()
+    got = vig_b200.ops.layernorm_act(x, w, b, 1e-6, False, post_add=pos)
+    ref = vig_b200.ops.layernorm_act(x, w, b, 1e-6, False) + pos
+    assert torch.equal(got, ref)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,H,W", [(2, 32, 48), (1, 8, 8), (3, 224, 224)])

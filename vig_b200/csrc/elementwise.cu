@@ -325,6 +325,7 @@ __global__ void __launch_bounds__(EW_THREADS) layernorm_act_short_kernel(const T
 template <typename T, int MAXV>
 __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __restrict__ x, const T* __restrict__ pre_bias,
                                                                    const T* __restrict__ w, const T* __restrict__ bias,
+                                                                   const T* __restrict__ post_add, int64_t post_period,
                                                                    T* __restrict__ y, int64_t rows, int N, float eps, int act) {
     constexpr int V = DType<T>::VEC;
     const int lane = threadIdx.x & 31;
@@ -376,7 +377,15 @@ __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __re
                     if (act) t *= sigmoid_t<T>(t);
                     val[m][i] = t;
                 }
-                Vec16<T> ov; ov.from_float(val[m]); ov.store(y + r * N + vi * V);
+                Vec16<T> ov; ov.from_float(val[m]);
+                if (post_add) {                          // e.g. the position embedding: added to the rounded result, like a separate add
+                    Vec16<T> pv; pv.load_nc(post_add + (r % post_period) * N + vi * V);
+                    float pf[V]; pv.to_float(pf); ov.to_float(val[m]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[m][i] += pf[i];
+                    ov.from_float(val[m]);
+                }
+                ov.store(y + r * N + vi * V);
             }
         }
     }
@@ -509,11 +518,12 @@ int add_rmsnorm_t(const void* x, const void* res, const void* w, void* y, void* 
 }
 
 template <typename T>
-int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b, void* y, int64_t rows, int N, float eps, int act, cudaStream_t s) {
+int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b, const void* pa, int64_t pa_period, void* y, int64_t rows, int N,
+                    float eps, int act, cudaStream_t s) {
     constexpr int V = DType<T>::VEC;
     if (N % V) return VIG_ERR_SHAPE;
     const int nv = N / V;
-    if (nv <= 16) {
+    if (nv <= 16 && !pa) {
         const int lpr = nv <= 8 ? 8 : 16;
         const int g = grid_for(rows * lpr, EW_THREADS);
         if (lpr == 8) layernorm_act_short_kernel<T, 8><<<g, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act);
@@ -521,7 +531,7 @@ int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b,
         return (int)cudaGetLastError();
     }
     const int grid = grid_for(rows * 32, EW_THREADS);
-#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act)
+#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (const T*)pa, pa_period, (T*)y, rows, N, eps, act)
     if (nv <= 32) VIG_LN(1); else if (nv <= 64) VIG_LN(2); else if (nv <= 128) VIG_LN(4);
     else if (nv <= 256) VIG_LN(8); else return VIG_ERR_SHAPE;
 #undef VIG_LN
@@ -591,7 +601,17 @@ extern "C" int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const 
     if (rows < 0 || N <= 0) return VIG_ERR_SHAPE;
     if (rows == 0) return VIG_OK;
     if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y)) return VIG_ERR_ALIGN;
-    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, y, rows, N, eps, act_swish, (cudaStream_t)stream))
+    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, nullptr, 1, y, rows, N, eps, act_swish, (cudaStream_t)stream))
+}
+
+extern "C" int vig_layernorm_act_add_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, const void* post_add,
+                                        int64_t post_period, void* y, int64_t rows, int N, float eps, int act_swish, int dtype, void* stream) {
+    if (!x || !w || !bias || !y || !post_add) return VIG_ERR_NULL;
+    if (pre_bias && !aligned16(pre_bias)) return VIG_ERR_ALIGN;
+    if (rows < 0 || N <= 0 || post_period <= 0) return VIG_ERR_SHAPE;
+    if (rows == 0) return VIG_OK;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y) || !aligned16(post_add)) return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, post_add, post_period, y, rows, N, eps, act_swish, (cudaStream_t)stream))
 }
 
 extern "C" int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream) {

@@ -271,15 +271,23 @@ def add_rmsnorm(x, weight, residual=None, eps=1e-6, prenorm=False):
     return y
 
 
-def layernorm_act(x, weight, bias, eps=1e-5, act_swish=False, pre_bias=None):
+def layernorm_act(x, weight, bias, eps=1e-5, act_swish=False, pre_bias=None, post_add=None):
     """LayerNorm over the last (contiguous) dimension with affine parameters and optional swish
     (``LayerNorm2d`` of ``classification/models/vig.py:619-624`` on channels-last data).  ``pre_bias`` is an
-    optional per-channel vector added to ``x`` first (the bias of the convolution that produced ``x``)."""
+    optional per-channel vector added to ``x`` first (the bias of the convolution that produced ``x``);
+    ``post_add`` an optional ``[P, N]`` tensor added to row ``r`` as ``post_add[r % P]`` (the position embedding)."""
     _lib.require_cuda(x, weight, bias)
     if not x.is_contiguous():
         raise ValueError("x must be contiguous")
     N = x.shape[-1]
     y = torch.empty_like(x)
+    if post_add is not None:
+        pa = post_add.reshape(-1, N).to(x.dtype).contiguous()
+        st = _lib.lib().vig_layernorm_act_add_fwd(_lib.ptr(x), _lib.ptr(pre_bias), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(pa), pa.shape[0],
+                                                  _lib.ptr(y), x.numel() // N, N, float(eps), int(bool(act_swish)), _lib.dtype_code(x),
+                                                  _lib.stream_ptr())
+        _lib.check(st, "vig_layernorm_act_add_fwd")
+        return y
     st = _lib.lib().vig_layernorm_act_fwd(_lib.ptr(x), _lib.ptr(pre_bias), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(y), x.numel() // N, N,
                                           float(eps), int(bool(act_swish)), _lib.dtype_code(x), _lib.stream_ptr())
     _lib.check(st, "vig_layernorm_act_fwd")

@@ -70,7 +70,8 @@ class V2PatchEmbed(nn.Module):
             cells = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
         return F.conv2d(cells.permute(0, 3, 1, 2), self._block_weight(), None)
 
-    def forward(self, x):
+    def forward(self, x, pos_fn=None):
+        """``pos_fn(hw) -> [1, h*w, C]`` (optional): the position embedding, added inside the last LayerNorm kernel."""
         from . import ops
         ln1, ln2, conv2 = self.proj[1], self.proj[4], self.proj[3]
         # the convolutions run without their bias; it is added inside the LayerNorm kernel that follows
@@ -78,8 +79,9 @@ class V2PatchEmbed(nn.Module):
         y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=True,
                               pre_bias=self.proj[0].bias)
         y = F.conv2d(y.permute(0, 3, 1, 2), conv2.weight, None, conv2.stride, conv2.padding)
-        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln2.weight, ln2.bias, ln2.eps, act_swish=False,
-                              pre_bias=conv2.bias)
+        y = y.permute(0, 2, 3, 1).contiguous()
+        pos = pos_fn((y.shape[1], y.shape[2])) if pos_fn is not None else None
+        y = ops.layernorm_act(y, ln2.weight, ln2.bias, ln2.eps, act_swish=False, pre_bias=conv2.bias, post_add=pos)
         B, h, w, C = y.shape
         return y.view(B, h * w, C), (h, w)
 
@@ -135,8 +137,7 @@ class ViG(nn.Module):
         return self._pos_cache[key]
 
     def forward_features(self, x):
-        x, hw = self.patch_embed(x)
-        x = x + self._pos(hw)
+        x, hw = self.patch_embed(x, pos_fn=self._pos)  # position embedding added by the stem's last kernel
         # ``fuse_norm_epilogues``: every residual add + RMSNorm runs as the epilogue of the projection in front of it
         # (hidden size <= 192, 16-bit tensors; measured 74 + 104 us against 112 + 141 us for cuBLAS + the norm kernel).
         if self.fuse_norm_epilogues and len(self.blocks) and all(blk.fused_epilogues_supported(x) for blk in self.blocks):
