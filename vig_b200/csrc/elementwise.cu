@@ -448,14 +448,25 @@ __global__ void __launch_bounds__(EW_THREADS) stem_unfold_kernel(const T* __rest
     }
     __syncthreads();
     T* dst = cells + (((size_t)b * ch + cy) * cw + cx0) * CELL;
+    const T* flat = &tile[0][0][0];
     for (int vi = threadIdx.x; vi < ncell * CELL / V; vi += EW_THREADS) {
         alignas(16) T vals[V];
+        // element e = vi*V + i of the cell row is (cell, dy, dx, ic); the indices are split once and then stepped
+        const int e0 = vi * V;
+        int cell = e0 / CELL, r = e0 % CELL;
+        int dy = r / (S * C), dx = (r % (S * C)) / C, ic = r % C;
+        int off = (dy * C + ic) * UNFOLD_TW + S * cell + dx + S - 1;
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            const int e = vi * V + i;
-            const int cell = e / CELL, r = e % CELL;
-            const int dy = r / (S * C), dx = (r % (S * C)) / C, ic = r % C;
-            vals[i] = tile[dy][ic][S * cell + dx + S - 1];
+            vals[i] = flat[off];
+            ++ic; off += UNFOLD_TW;
+            if (ic == C) {
+                ic = 0; off -= C * UNFOLD_TW - 1; ++dx;
+                if (dx == S) {
+                    dx = 0; off += C * UNFOLD_TW - S; ++dy;
+                    if (dy == S) { dy = 0; off -= S * C * UNFOLD_TW - S; }
+                }
+            }
         }
         reinterpret_cast<uint4*>(dst)[vi] = *reinterpret_cast<const uint4*>(vals);
     }
