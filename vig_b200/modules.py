@@ -55,6 +55,8 @@ class GatedLinearAttention(nn.Module):
         self.l_norm = RMSNorm(self.head_v_dim, eps=layernorm_eps)
         self.g_proj = nn.Linear(d_model, self.value_dim, bias=True)
         self._packed = None
+        # inference-time weight folding of the gate bottleneck (16-bit runs only; fp32 keeps the reference's two steps)
+        self.fold_gate_bottleneck = True
 
     def _pack(self):
         """Derived weight layouts, built once per dtype/device: the conv taps as [9, C] and one stacked
@@ -67,7 +69,10 @@ class GatedLinearAttention(nn.Module):
             stacked = torch.cat([self.qkv_proj.weight, self.g_proj.weight, self.gk_proj[0].weight], dim=0).detach().contiguous()
             bias = torch.cat([torch.zeros(self.qkv_proj.out_features, dtype=w.dtype, device=w.device), self.g_proj.bias.detach(),
                               torch.zeros(self.gk_proj[0].out_features, dtype=w.dtype, device=w.device)])
-            self._packed = (key, taps, stacked, bias)
+            # the rank-16 gate bottleneck folded into one [2*key_dim, d_model] matrix (product in fp32, rounded once):
+            # a K = d_model GEMM of a friendly width replaces the 16 odd columns of the stacked projection plus a K = 16 GEMM
+            folded = (self.gk_proj[1].weight.detach().float() @ self.gk_proj[0].weight.detach().float()).to(w.dtype).contiguous()
+            self._packed = (key, taps, stacked, bias, folded)
         return self._packed[1:]
 
     def forward(self, x, lower_bound=0, **kwargs):
@@ -76,7 +81,7 @@ class GatedLinearAttention(nn.Module):
         B, L, C = x.shape
         hw = kwargs["patch_resolution"]
         H, dk, dv, kd, vd = self.num_heads, self.head_qk_dim, self.head_v_dim, self.key_dim, self.value_dim
-        taps, w_in, b_in = self._pack()
+        taps, w_in, b_in, w_gk = self._pack()
         # ``local_fn`` / ``scan_fn`` let a caller substitute the two steps that look beyond the tokens at hand (the
         # 3x3 neighbourhood and the scan) -- the sequence-parallel driver supplies halo and boundary-state versions
         local_fn, scan_fn = kwargs.get("local_fn"), kwargs.get("scan_fn")
@@ -84,13 +89,18 @@ class GatedLinearAttention(nn.Module):
             xs = ops.dwconv3x3(x, taps, self.in_proj[0].bias, hw, self.use_act_in_conv)
         else:
             xs = local_fn(x, taps, self.in_proj[0].bias, hw, self.use_act_in_conv)
-        # one GEMM for [q | k | v | output-gate logits | low-rank gate features]
-        z = F.linear(xs, w_in, b_in)
+        fold = self.fold_gate_bottleneck and x.dtype != torch.float32
+        n_main = 2 * kd + 2 * vd
+        # one GEMM for [q | k | v | output-gate logits | low-rank gate features] (without the last part when it is folded)
+        z = F.linear(xs, w_in[:n_main], b_in[:n_main]) if fold else F.linear(xs, w_in, b_in)
         heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)           # [B,H,L,d] views, no copy
         q, k, v = heads(z[..., :kd], dk), heads(z[..., kd:2 * kd], dk), heads(z[..., 2 * kd:2 * kd + vd], dv)
         gate_logits = z[..., 2 * kd + vd:2 * kd + 2 * vd]
         # raw gate logits [B,L,2*kd]: bias and the strided low-rank slice go straight into one GEMM call
-        gk = torch.addmm(self.gk_proj[1].bias, z.view(B * L, -1)[:, 2 * kd + 2 * vd:], self.gk_proj[1].weight.t()).view(B, L, 2 * kd)
+        if fold:
+            gk = F.linear(xs, w_gk, self.gk_proj[1].bias)
+        else:
+            gk = torch.addmm(self.gk_proj[1].bias, z.view(B * L, -1)[:, 2 * kd + 2 * vd:], self.gk_proj[1].weight.t()).view(B, L, 2 * kd)
         g_fwd, g_bwd = heads(gk[..., :kd], dk), heads(gk[..., kd:], dk)
         o = torch.empty(B, L, H, dv, dtype=x.dtype, device=x.device).permute(0, 2, 1, 3)
         # reference: (o_f + o_b) / 2 in the operator wrapper, / 2 again in the eval branch (vig.py:443)
