@@ -263,3 +263,27 @@ def test_clamp_min_and_raw_logits(dtype):
     ref = oracle.naive_bi_gla(ins[0].float(), ins[1].float(), ins[2].float(), lf(ins[3]), lf(ins[4]))
     o = vig_b200.bi_gla(*[t.cuda() for t in ins], gate_logit_normalizer=16.0, clamp_min=-0.3)
     assert rel_err(o.float(), ref) < TOL[dtype]
+
+
+def test_wavefront_form_raw_logits_clamp_and_range_flag():
+    """The wavefront kernel's gate path: raw logits with `logsigmoid(x) / 16` and a lower clamp inside the kernel
+    (vig.py:439-441), strong gates inside the factorisation range, and gates beyond it (flagged, finite)."""
+    import vig_b200
+    from vig_b200 import _lib
+    q, k, v, _, _ = oracle.make_bigla_inputs(2, 2, 600, 64, 64, seed=6)
+    gen = torch.Generator().manual_seed(10)
+    xf, xb = 8 * torch.randn(2, 2, 600, 64, generator=gen), 8 * torch.randn(2, 2, 600, 64, generator=gen)
+    ins = [t.bfloat16() for t in (q, k, v, xf, xb)]
+    lf = lambda t: torch.clamp_min(torch.nn.functional.logsigmoid(t.float()) / 16, -0.3)
+    ref = oracle.naive_bi_gla(ins[0].float(), ins[1].float(), ins[2].float(), lf(ins[3]), lf(ins[4]))
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o = vig_b200.bi_gla(*[t.cuda() for t in ins], gate_logit_normalizer=16.0, clamp_min=-0.3, impl=_lib.IMPL_TC_WAVE, status=status)
+    assert rel_err(o.float(), ref) < 2e-2 and int(status.item()) == 0
+    # about -0.8 per token: exponents reach ~50 around the reference token, nothing is clamped
+    strong = [t.bfloat16() for t in _strong_gate_inputs(0.8, L=600)]
+    o = vig_b200.bi_gla(*[t.cuda() for t in strong], impl=_lib.IMPL_TC_WAVE, status=status)
+    assert rel_err(o.float(), oracle.naive_bi_gla(*[t.float() for t in strong])) < 2e-2 and int(status.item()) == 0
+    # about -4 per token: beyond the range; reported in the status word, output finite
+    wild = [t.bfloat16() for t in _strong_gate_inputs(4.0, L=600)]
+    o = vig_b200.bi_gla(*[t.cuda() for t in wild], impl=_lib.IMPL_TC_WAVE, status=status)
+    assert int(status.item()) & 2 and torch.isfinite(o.float()).all()

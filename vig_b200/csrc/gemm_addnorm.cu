@@ -7,10 +7,14 @@
 // tcgen05 GEMM with full output rows per tile.  A persistent CTA owns tiles of 128 rows; x and W stream through a ring
 // of stages [128 x 64 of x | N x 64 of W] (TMA, 128-byte swizzle); the accumulator [128 x N] fp32 lives in tensor
 // memory (N <= 384 columns; two buffers when 2N <= 512, so the epilogue of a tile overlaps the MMAs of the next).
-// Epilogue (one thread per row, its TMEM lane): pass 1 adds the residual with the roundings of the unfused path
-// (projection rounded to T, sum rounded to T), stores r and accumulates the sum of squares; pass 2 re-reads its own r
-// (L1/L2 hits), scales and stores h.  Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 epilogue.  Every wait
-// is bounded.
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 epilogue.  Every wait is bounded.
+// Epilogue for rows of up to 192 values: the tile's residual rows arrive by TMA in 128-byte-swizzled boxes (two tile
+// buffers); a thread owns half a row (its TMEM lane, two warps per lane quadrant): pass 1 adds the residual with the
+// roundings of the unfused path (projection rounded to T, sum rounded to T), writes r in place and keeps it in
+// registers, the halves' sums of squares meet in shared memory; a TMA store sends r out; pass 2 writes h over the same
+// boxes once that store has read them and a second TMA store sends h out.  (Per-thread row stores, the first version,
+// cost 32 sectors per request and made the kernel slower than the pair it replaces.)  Wider rows still use per-thread
+// loads and stores.
 #include "tc_common.cuh"
 
 namespace vig {
