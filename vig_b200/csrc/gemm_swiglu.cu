@@ -6,7 +6,9 @@
 // in shared memory (TMA, 128-byte swizzle), the weights stream through a ring of 16 KB stages holding 64 gate
 // rows and the 64 matching y rows, so one M128 N128 MMA per subtile fills an accumulator [128 x (64 gate | 64 y)]
 // in tensor memory.  Accumulators are double buffered: while the MMA warp works on feature block n+1, the
-// epilogue warps read block n with tcgen05.ld, apply silu(g)*y and store bf16 / fp16.
+// epilogue warps read block n with tcgen05.ld and apply silu(g)*y.  Each warp packs its [32 rows x 64 features] piece
+// into a swizzled 4 KB box of shared memory and lane 0 sends it out with one TMA store: a thread owns a row, so direct
+// 16-byte stores would touch 32 lines per request and fill only half of each 32-byte sector.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2.. epilogue.  Every wait is bounded.
 #include <cuda.h>
 #include <mutex>
@@ -17,11 +19,14 @@ namespace {
 
 constexpr int BK = 64;                         // k elements per stage row (128 bytes)
 constexpr int BNF = 64;                        // features per block: 64 gate rows + 64 y rows -> MMA N = 128
-constexpr int NSTAGE = 4;
+constexpr int NSTAGE = 6;                      // weight stages in flight (16 KB each)
+constexpr int MAX_KB = 6;                      // k boxes of an x tile (K <= 384)
 constexpr int A_BOX_BYTES = 128 * BK * 2;      // one [128 rows x 64 k] box
 constexpr int B_STAGE_BYTES = 2 * BNF * BK * 2;
 constexpr int MAX_A_BYTES = 96 * 1024;
 constexpr int GS_THREADS = 64 + 256;
+constexpr int OUT_BOX_BYTES = 32 * BNF * 2;    // one epilogue warp's [32 rows x 64 features] box
+constexpr int OUT_STAGE_BYTES = 8 * OUT_BOX_BYTES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
@@ -35,6 +40,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -85,28 +93,28 @@ template <> struct Pk<__nv_bfloat16> { static constexpr uint32_t FMT = 1;
 template <> struct Pk<__half> { static constexpr uint32_t FMT = 0;
     __device__ static uint32_t pack(float a, float b) { __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); } };
 
-struct GsMaps { CUtensorMap x, w; };
+struct GsMaps { CUtensorMap x, w, o; };
 
 // S = subtiles of 128 rows per CTA tile (1 or 2); KB = K / 64.
 template <typename T>
-__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __grid_constant__ GsMaps maps, T* __restrict__ out, int64_t ldo,
-                                                                      int M, int I, int KB, int S, int nsplit, int32_t* status) {
+__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __grid_constant__ GsMaps maps, int M, int I, int KB, int S, int nsplit, int32_t* status) {
     extern __shared__ uint8_t gs_smem_raw[];
     uint8_t* smem = gs_smem_raw + ((1024u - (smem_u32(gs_smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t a_bytes = (uint32_t)S * KB * A_BOX_BYTES;
     const uint32_t off_b = a_bytes;
-    const uint32_t off_bar = off_b + NSTAGE * B_STAGE_BYTES;
-    const uint32_t bar_a_full = sbase + off_bar, bar_a_empty = bar_a_full + 8;
-    const uint32_t bar_b_full = bar_a_full + 16, bar_b_empty = bar_b_full + 8 * NSTAGE;
+    const uint32_t off_out = off_b + NSTAGE * B_STAGE_BYTES;
+    const uint32_t off_bar = off_out + OUT_STAGE_BYTES;
+    const uint32_t bar_a_full = sbase + off_bar, bar_a_empty = bar_a_full + 8 * MAX_KB;   // one pair per k box of the x tile
+    const uint32_t bar_b_full = bar_a_empty + 8 * MAX_KB, bar_b_empty = bar_b_full + 8 * NSTAGE;
     const uint32_t bar_acc_full = bar_b_empty + 8 * NSTAGE, bar_acc_empty = bar_acc_full + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (2 + 2 * NSTAGE + 4));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (2 * MAX_KB + 2 * NSTAGE + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const GsWaiter waiter{abort_flag, status};
 
     if (tid == 0) {
-        mbar_init(bar_a_full, 1); mbar_init(bar_a_empty, 1);
+        for (int kb = 0; kb < MAX_KB; ++kb) { mbar_init(bar_a_full + 8 * kb, 1); mbar_init(bar_a_empty + 8 * kb, 1); }
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_b_full + 8 * s, 1); mbar_init(bar_b_empty + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 128 * S); }
         *abort_flag = 0;
@@ -130,15 +138,19 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
 
     if (warp == 0) {
         if (lane == 0) {                          // ---- TMA producer -------------------------------------------
+            // The x tile is handed over per k box: box kb of the next tile is requested as soon as the last feature
+            // block of this tile has used box kb, just ahead of the weight stage that needs it.
             uint32_t a_phase = 0, st = 0, b_phase = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-                waiter.wait(bar_a_empty, a_phase ^ 1u);                 // the previous tile's MMAs have read A
-                mbar_expect_tx(bar_a_full, a_bytes);
-                for (int s = 0; s < S; ++s)
-                    for (int kb = 0; kb < KB; ++kb)
-                        tma_load_2d(sbase + (s * KB + kb) * A_BOX_BYTES, &maps.x, kb * BK, (tile / nsplit) * BM + s * 128, bar_a_full);
-                for (int nb = nb_begin(tile); nb < nb_end(tile); ++nb)
+                const int nb0 = nb_begin(tile), nb1 = nb_end(tile);
+                for (int nb = nb0; nb < nb1; ++nb)
                     for (int kb = 0; kb < KB; ++kb) {
+                        if (nb == nb0) {
+                            waiter.wait(bar_a_empty + 8 * kb, a_phase ^ 1u);    // the previous tile's MMAs have read this box
+                            mbar_expect_tx(bar_a_full + 8 * kb, (uint32_t)S * A_BOX_BYTES);
+                            for (int s = 0; s < S; ++s)
+                                tma_load_2d(sbase + (s * KB + kb) * A_BOX_BYTES, &maps.x, kb * BK, (tile / nsplit) * BM + s * 128, bar_a_full + 8 * kb);
+                        }
                         waiter.wait(bar_b_empty + 8 * st, b_phase ^ 1u);
                         mbar_expect_tx(bar_b_full + 8 * st, B_STAGE_BYTES);
                         const uint32_t dst = sbase + off_b + st * B_STAGE_BYTES;
@@ -149,74 +161,91 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
                 a_phase ^= 1u;
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0) {                          // ---- MMA issuer ---------------------------------------------
-            uint32_t a_phase = 0, st = 0, b_phase = 0, acc_it = 0;
-            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-                waiter.wait(bar_a_full, a_phase);
-                for (int nb = nb_begin(tile); nb < nb_end(tile); ++nb, ++acc_it) {
-                    const uint32_t buf = acc_it & 1u;
-                    waiter.wait(bar_acc_empty + 8 * buf, ((acc_it >> 1) & 1u) ^ 1u);    // the epilogue has drained this buffer
+    } else if (warp == 1) {                       // ---- MMA issuer ---------------------------------------------
+        // The whole warp walks the loop (uniform control flow keeps the descriptor arithmetic off the issuing lane's
+        // critical path); lane 0 issues.  Descriptors advance by adding to their 14-bit address field (16-byte units).
+        uint32_t a_phase = 0, st = 0, b_phase = 0, acc_it = 0;
+        const uint32_t a_lo0 = desc_lo(sbase), b_lo0 = desc_lo(sbase + off_b);
+        const uint32_t a_sub = (uint32_t)KB * (A_BOX_BYTES >> 4);
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            const int nb0 = nb_begin(tile), nb1 = nb_end(tile);
+            for (int nb = nb0; nb < nb1; ++nb, ++acc_it) {
+                const uint32_t buf = acc_it & 1u;
+                waiter.wait(bar_acc_empty + 8 * buf, ((acc_it >> 1) & 1u) ^ 1u);    // the epilogue has drained this buffer
+                tc_fence_after();
+                const uint32_t d0 = tmem + buf * (uint32_t)(S * 128);
+                uint32_t a_lo = a_lo0;
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (nb == nb0) waiter.wait(bar_a_full + 8 * kb, a_phase);
+                    waiter.wait(bar_b_full + 8 * st, b_phase);
                     tc_fence_after();
-                    for (int kb = 0; kb < KB; ++kb) {
-                        waiter.wait(bar_b_full + 8 * st, b_phase);
-                        tc_fence_after();
-                        const uint32_t b_addr = sbase + off_b + st * B_STAGE_BYTES;
+                    const uint32_t b_lo = b_lo0 + st * (B_STAGE_BYTES >> 4);
+                    if (lane == 0) {
                         for (int s = 0; s < S; ++s) {
-                            const uint32_t a_addr = sbase + (s * KB + kb) * A_BOX_BYTES;
-                            const uint32_t d = tmem + buf * (uint32_t)(S * 128) + (uint32_t)s * 128u;
-#pragma unroll
-                            for (int k4 = 0; k4 < BK / 16; ++k4)
-                                tc_mma(d, desc_lo(a_addr + k4 * 32), desc_lo(b_addr + k4 * 32), IDESC, (kb > 0 || k4 > 0) ? 1u : 0u);
+                            const uint32_t a_s = a_lo + s * a_sub, d = d0 + (uint32_t)s * 128u;
+                            tc_mma(d, a_s, b_lo, IDESC, kb > 0 ? 1u : 0u);
+                            tc_mma(d, a_s + 2, b_lo + 2, IDESC, 1u);
+                            tc_mma(d, a_s + 4, b_lo + 4, IDESC, 1u);
+                            tc_mma(d, a_s + 6, b_lo + 6, IDESC, 1u);
                         }
                         tc_commit(bar_b_empty + 8 * st);                // the stage is free when these MMAs are done
-                        if (++st == NSTAGE) { st = 0; b_phase ^= 1u; }
+                        if (nb == nb1 - 1) tc_commit(bar_a_empty + 8 * kb);   // and, in the tile's last block, so is the x box
                     }
-                    tc_commit(bar_acc_full + 8 * buf);
+                    __syncwarp();
+                    a_lo += A_BOX_BYTES >> 4;
+                    if (++st == NSTAGE) { st = 0; b_phase ^= 1u; }
                 }
-                tc_commit(bar_a_empty);
-                a_phase ^= 1u;
+                if (lane == 0) tc_commit(bar_acc_full + 8 * buf);
+                __syncwarp();
             }
+            a_phase ^= 1u;
         }
     } else {                                      // ---- epilogue: silu(gate) * y -> out ----------------------------
         const int ew = warp - 2;                  // 0..7
         const int sub = ew >> 2;                  // subtile
         if (sub < S) {
             const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
-            const int r_in_sub = 32 * (warp & 3) + lane;
+            const int r_in_tile = sub * 128 + 32 * (warp & 3);          // first of this warp's 32 rows within the tile
+            uint8_t* box = smem + off_out + ew * OUT_BOX_BYTES;
+            const uint32_t box_u32 = sbase + off_out + ew * OUT_BOX_BYTES;
+            uint8_t* my_row = box + lane * 128;
+            const uint32_t sw = (uint32_t)(lane & 7);
             uint32_t acc_it = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-                const int64_t row = (int64_t)(tile / nsplit) * BM + sub * 128 + r_in_sub;
+                const int row0 = (tile / nsplit) * BM + r_in_tile;
                 for (int nb = nb_begin(tile); nb < nb_end(tile); ++nb, ++acc_it) {
                     const uint32_t buf = acc_it & 1u;
                     if (lane == 0) waiter.wait(bar_acc_full + 8 * buf, (acc_it >> 1) & 1u);
                     __syncwarp();
                     tc_fence_after();
                     const uint32_t acc = tmem + lane_base + buf * (uint32_t)(S * 128) + (uint32_t)sub * 128u;
+                    uint32_t pk[BNF / 2];
 #pragma unroll
                     for (int c = 0; c < BNF; c += 32) {
                         float g[32], y[32];
                         tc_ld32(acc + c, g);
                         tc_ld32(acc + BNF + c, y);
                         tc_wait_ld();
-                        if (row < M) {
-                            uint4* dst = reinterpret_cast<uint4*>(out + row * ldo + nb * BNF + c);
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                float o[8];
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) o[e] = g[j + e] * y[j + e] * sigmoid_tanh(g[j + e]);
-                                uint4 w;
-                                w.x = Pk<T>::pack(o[0], o[1]); w.y = Pk<T>::pack(o[2], o[3]);
-                                w.z = Pk<T>::pack(o[4], o[5]); w.w = Pk<T>::pack(o[6], o[7]);
-                                dst[j / 8] = w;
-                            }
-                        }
+                        for (int e = 0; e < 32; e += 2)
+                            pk[(c + e) / 2] = Pk<T>::pack(g[e] * y[e] * sigmoid_tanh(g[e]), g[e + 1] * y[e + 1] * sigmoid_tanh(g[e + 1]));
                     }
                     tc_fence_before();
-                    mbar_arrive(bar_acc_empty + 8 * buf);
+                    mbar_arrive(bar_acc_empty + 8 * buf);               // the accumulator is in registers: the MMA warp may refill it
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the box
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < BNF / 8; ++j)
+                        *reinterpret_cast<uint4*>(my_row + (((uint32_t)j ^ sw) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && row0 < M) {
+                        tma_store_2d(&maps.o, nb * BNF, row0, box_u32);  // rows past M are clipped by the tensor map
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
                 }
             }
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA exits
         }
     }
     tc_fence_before();
@@ -280,10 +309,11 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) return VIG_ERR_ALIGN;
     if (ldx < K || ldo < I || (ldx * 2) % 16 || (ldo * 2) % 16 || M >= (1ll << 31)) return VIG_ERR_ARG;
     GsMaps maps;
-    if (!map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !map_2d(&maps.w, w, 2 * (int64_t)I, K, K, BNF, dtype)) return VIG_ERR_DEVICE;
+    if (!map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !map_2d(&maps.w, w, 2 * (int64_t)I, K, K, BNF, dtype) ||
+        !map_2d(&maps.o, out, M, I, ldo, 32, dtype)) return VIG_ERR_DEVICE;
     const int KB = K / BK;
     const int S = ((int64_t)256 * K * 2 <= MAX_A_BYTES && M > 128) ? 2 : 1;
-    const int smem = S * KB * A_BOX_BYTES + NSTAGE * B_STAGE_BYTES + 8 * (2 + 2 * NSTAGE + 4) + 16 + 1024;
+    const int smem = S * KB * A_BOX_BYTES + NSTAGE * B_STAGE_BYTES + OUT_STAGE_BYTES + 8 * (2 * MAX_KB + 2 * NSTAGE + 4) + 16 + 1024;
     int dev = 0, sms = 0;
     cudaError_t e;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
@@ -298,11 +328,11 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     if (dtype == VIG_DTYPE_BF16) {
         auto kfn = linear_swiglu_kernel<__nv_bfloat16>;
         if ((e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
-        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (__nv_bfloat16*)out, ldo, (int)M, I, KB, S, nsplit, status_dev);
+        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, nsplit, status_dev);
     } else {
         auto kfn = linear_swiglu_kernel<__half>;
         if ((e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
-        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (__half*)out, ldo, (int)M, I, KB, S, nsplit, status_dev);
+        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, nsplit, status_dev);
     }
     return (int)cudaGetLastError();
 }
