@@ -108,8 +108,11 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {                          // ---- MMA issuer ---------------------------------------------
+        {                                         // ---- MMA issuer ---------------------------------------------
+            // The whole warp walks the loop (uniform control flow keeps the descriptor arithmetic cheap), lane 0 issues;
+            // a descriptor's low word advances by adding to its address field (16-byte units).
             const uint32_t idesc = (1u << 4) | (Pack2<T>::FMT << 7) | (Pack2<T>::FMT << 10) | (((uint32_t)CH >> 3) << 17) | ((128u >> 4) << 24);
+            const uint32_t ch_lo = ((uint32_t)CH * AN_BK * 2) >> 4;
             uint32_t st = 0, phase = 0, acc_it = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++acc_it) {
                 const uint32_t buf = nbuf == 2 ? (acc_it & 1u) : 0u;
@@ -117,20 +120,26 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
                 waiter.wait(bar_acc_empty + 8 * buf, (use & 1u) ^ 1u);         // the epilogue has drained this buffer
                 if (*abort_flag) break;
                 tc_fence_after();
+                const uint32_t d0 = tmem + buf * (uint32_t)N;
                 for (int kb = 0; kb < KB; ++kb) {
                     waiter.wait(bar_full + 8 * st, phase);
                     tc_fence_after();
-                    const uint32_t a_addr = sbase + st * stage_bytes, b_addr = a_addr + AN_A_BYTES;
-                    for (int c = 0; c < nch; ++c) {
-                        const uint32_t d = tmem + buf * (uint32_t)N + (uint32_t)c * CH;
-#pragma unroll
-                        for (int k4 = 0; k4 < AN_BK / 16; ++k4)
-                            tc_mma(d, make_desc(a_addr + k4 * 32), make_desc(b_addr + (uint32_t)c * CH * AN_BK * 2 + k4 * 32), idesc, (kb > 0 || k4 > 0) ? 1u : 0u);
+                    const uint32_t a_lo = make_desc(sbase + st * stage_bytes), b_lo = make_desc(sbase + st * stage_bytes + AN_A_BYTES);
+                    if (lane == 0) {
+                        for (int c = 0; c < nch; ++c) {
+                            const uint32_t d = d0 + (uint32_t)c * CH, b_c = b_lo + (uint32_t)c * ch_lo;
+                            tc_mma(d, a_lo, b_c, idesc, kb > 0 ? 1u : 0u);
+                            tc_mma(d, a_lo + 2, b_c + 2, idesc, 1u);
+                            tc_mma(d, a_lo + 4, b_c + 4, idesc, 1u);
+                            tc_mma(d, a_lo + 6, b_c + 6, idesc, 1u);
+                        }
+                        tc_commit(bar_empty + 8 * st);                          // the stage is free when these MMAs are done
                     }
-                    tc_commit(bar_empty + 8 * st);                              // the stage is free when these MMAs are done
+                    __syncwarp();
                     if (++st == (uint32_t)nstage) { st = 0; phase ^= 1u; }
                 }
-                tc_commit(bar_acc_full + 8 * buf);
+                if (lane == 0) tc_commit(bar_acc_full + 8 * buf);
+                __syncwarp();
             }
         }
     } else if (TMA_EPI) {                         // ---- epilogue through shared memory and TMA stores ----------------
