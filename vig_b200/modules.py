@@ -72,7 +72,12 @@ class GatedLinearAttention(nn.Module):
             # the rank-16 gate bottleneck folded into one [2*key_dim, d_model] matrix (product in fp32, rounded once):
             # a K = d_model GEMM of a friendly width replaces the 16 odd columns of the stacked projection plus a K = 16 GEMM
             folded = (self.gk_proj[1].weight.detach().float() @ self.gk_proj[0].weight.detach().float()).to(w.dtype).contiguous()
-            self._packed = (key, taps, stacked, bias, folded)
+            # with the bottleneck folded, its rows join the stacked projection: one GEMM reads the conv output once
+            n_main = self.qkv_proj.out_features + self.g_proj.out_features
+            gk_bias = self.gk_proj[1].bias
+            gk_bias = torch.zeros(folded.shape[0], dtype=w.dtype, device=w.device) if gk_bias is None else gk_bias.detach()
+            merged = (torch.cat([stacked[:n_main], folded], dim=0).contiguous(), torch.cat([bias[:n_main], gk_bias]))
+            self._packed = (key, taps, stacked, bias, merged)
         return self._packed[1:]
 
     def forward(self, x, lower_bound=0, **kwargs):
@@ -81,7 +86,7 @@ class GatedLinearAttention(nn.Module):
         B, L, C = x.shape
         hw = kwargs["patch_resolution"]
         H, dk, dv, kd, vd = self.num_heads, self.head_qk_dim, self.head_v_dim, self.key_dim, self.value_dim
-        taps, w_in, b_in, w_gk = self._pack()
+        taps, w_in, b_in, merged = self._pack()
         # ``local_fn`` / ``scan_fn`` let a caller substitute the two steps that look beyond the tokens at hand (the
         # 3x3 neighbourhood and the scan) -- the sequence-parallel driver supplies halo and boundary-state versions
         local_fn, scan_fn = kwargs.get("local_fn"), kwargs.get("scan_fn")
@@ -91,14 +96,14 @@ class GatedLinearAttention(nn.Module):
             xs = local_fn(x, taps, self.in_proj[0].bias, hw, self.use_act_in_conv)
         fold = self.fold_gate_bottleneck and x.dtype != torch.float32
         n_main = 2 * kd + 2 * vd
-        # one GEMM for [q | k | v | output-gate logits | low-rank gate features] (without the last part when it is folded)
-        z = F.linear(xs, w_in[:n_main], b_in[:n_main]) if fold else F.linear(xs, w_in, b_in)
+        # one GEMM for [q | k | v | output-gate logits | low-rank gate features] (folded: | raw gate logits)
+        z = F.linear(xs, merged[0], merged[1]) if fold else F.linear(xs, w_in, b_in)
         heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)           # [B,H,L,d] views, no copy
         q, k, v = heads(z[..., :kd], dk), heads(z[..., kd:2 * kd], dk), heads(z[..., 2 * kd:2 * kd + vd], dv)
         gate_logits = z[..., 2 * kd + vd:2 * kd + 2 * vd]
         # raw gate logits [B,L,2*kd]: bias and the strided low-rank slice go straight into one GEMM call
         if fold:
-            gk = F.linear(xs, w_gk, self.gk_proj[1].bias)
+            gk = z[..., n_main:]
         else:
             gk = torch.addmm(self.gk_proj[1].bias, z.view(B * L, -1)[:, 2 * kd + 2 * vd:], self.gk_proj[1].weight.t()).view(B, L, 2 * kd)
         g_fwd, g_bwd = heads(gk[..., :kd], dk), heads(gk[..., kd:], dk)
