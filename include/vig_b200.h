@@ -137,9 +137,11 @@ VIG_API int vig_bigla_bwd(const void* q, const void* k, const void* v, const voi
  * `workspace` lives here in a fixed device array of VIG_NOALLOC_SCRATCH_BYTES inside the library, which
  * every GPU that loads the library holds until the process exits.
  *
- * Limit: vig_bigla_workspace_bytes(B,H,L,dk,dv,dtype,impl) must not exceed VIG_NOALLOC_SCRATCH_BYTES,
- * else VIG_ERR_SCRATCH_LIMIT is returned and nothing is launched (sequences of at most one 256-token
- * segment on the tensor-core path, or 64 tokens on the SIMT path, need no scratch at all).
+ * Limit: what the call really uses must fit VIG_NOALLOC_SCRATCH_BYTES, else VIG_ERR_SCRATCH_LIMIT is returned
+ * and nothing is launched.  Used: B*H*ceil(L/256)*2*(dk*dv+dk)*4 bytes on the tensor-core path (16-bit types,
+ * dk in {32,64}, dv = 64) when L > 256 and nothing for a single segment; B*H*ceil(L/64)*2*(dk*dv+dk)*4 bytes
+ * on the SIMT path (fp32, other head sizes, impl = VIG_IMPL_SIMT) when L > 64 and nothing up to 64 tokens.
+ * At dk = dv = 64 that is B*H*ceil(L/256) <= 504 (tensor core) or B*H*ceil(L/64) <= 504 (SIMT).
  * The call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
  * The first call on each device looks up the array's device address (with that device current); make that
  * first call outside any stream capture.  All calls on a device share the one array: calls that may overlap

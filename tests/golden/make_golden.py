@@ -1,7 +1,9 @@
 """Generate the golden vectors in this folder from the REFERENCE's own Python code on CPU.
 
 Run once, in a container that has the reference checkout, as
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [ops] [blocks] [full]
+(no selection = all three files: ``bigla_ref.npz``, ``block_ref.npz``, ``model_ref.npz``; ``full`` alone takes
+about a quarter of an hour on 8 cores, most of it the 16384-token case).
 It cannot run where the reference is absent; the committed ``.npz`` files are what the
 tests read.  What is executed on the reference side:
   * ``fla/ops/gla/naive.py`` ``naive_recurrent_gla`` (the operator pin), and
@@ -84,9 +86,48 @@ def ref_bigla(naive, q, k, v, gf, gb):
     return o_f + o_b.flip(2)
 
 
-def main(ref_root):
+def build_reference_model(vig, shape, sd):
+    model = vig.ViG(img_size=224, patch_size=16, stride=16, depth=shape.depth, num_heads=shape.num_heads,
+                    embed_dim=shape.embed_dim, num_classes=shape.num_classes, if_cls_token=False,
+                    classification_mode="avgpool", use_out_act=shape.use_out_act, use_swiglu=True,
+                    use_act_in_conv=shape.use_act_in_conv, expand_k=shape.expand_k, expand_v=shape.expand_v,
+                    patch_embed_version="v2", drop_path_rate=0.0)
+    missing, unexpected = model.load_state_dict(sd, strict=False)
+    assert not unexpected and not missing, (missing, unexpected)
+    return model.eval()
+
+
+# Full-depth models at the benchmark's configurations: the same seeded weights and images the benchmark uses
+# (weights seed 0, 1000 classes, images seed 0), so the vectors pin the very model the throughput is quoted on.
+FULL_CASES = (("t1024", "vig_t_dk64", 1024, 1), ("s224x16", "vig_s_dk64", 224, 16), ("t224x4_dk32", "vig_t", 224, 4),
+              ("b2048", "vig_b_dk64", 2048, 1))
+
+
+def full_models(vig):
+    import time
+    out = {}
+    for tag, preset, size, batch in FULL_CASES:
+        shape = oracle.PRESETS[preset]
+        model = build_reference_model(vig, shape, oracle.make_state_dict(shape, seed=0))
+        t0 = time.time()
+        out[f"vig_{tag}_logits"] = model(oracle.make_images(batch, size, seed=0)).numpy().astype(np.float32)
+        print(tag, f"{time.time() - t0:.1f} s", flush=True)
+    np.savez_compressed(os.path.join(HERE, "model_ref.npz"), **out)
+
+
+def main(ref_root, only=()):
     vig, naive = load_reference(ref_root)
     torch.set_grad_enabled(False)
+    if not only or "ops" in only:
+        operator_pins(naive)
+    if not only or "blocks" in only:
+        block_pins(vig)
+    if not only or "full" in only:
+        full_models(vig)
+    print("written", sorted(os.listdir(HERE)))
+
+
+def operator_pins(naive):
     out = {}
     # ---- operator pins -------------------------------------------------------------------
     cases = {"cfg1": (2, 3, 196, 64, 64, 0), "dk32": (1, 3, 196, 32, 64, 1), "L1": (1, 2, 1, 64, 64, 2),
@@ -105,6 +146,8 @@ def main(ref_root):
     out["gla_state_o"], out["gla_state_hT"] = o.numpy(), hT.numpy()
     np.savez_compressed(os.path.join(HERE, "bigla_ref.npz"), **out)
 
+
+def block_pins(vig):
     # ---- block / model pins --------------------------------------------------------------
     out = {}
     for tag, preset, size, batch in (("t224", "vig_t", 224, 2), ("t320", "vig_t", 320, 1),
@@ -112,14 +155,7 @@ def main(ref_root):
         base = oracle.PRESETS[preset]
         shape = oracle.ViGShape(**{**base.__dict__, "depth": 2, "num_classes": 16})
         sd = oracle.make_state_dict(shape, seed=11)
-        model = vig.ViG(img_size=224, patch_size=16, stride=16, depth=shape.depth, num_heads=shape.num_heads,
-                        embed_dim=shape.embed_dim, num_classes=shape.num_classes, if_cls_token=False,
-                        classification_mode="avgpool", use_out_act=shape.use_out_act, use_swiglu=True,
-                        use_act_in_conv=shape.use_act_in_conv, expand_k=shape.expand_k, expand_v=shape.expand_v,
-                        patch_embed_version="v2", drop_path_rate=0.0)
-        missing, unexpected = model.load_state_dict(sd, strict=False)
-        assert not unexpected and not missing, (missing, unexpected)
-        model.eval()
+        model = build_reference_model(vig, shape, sd)
         images = oracle.make_images(batch, size, seed=3)
         out[f"vig_{tag}_logits"] = model(images).numpy()
         # one block in isolation on a random token tensor
@@ -132,8 +168,9 @@ def main(ref_root):
         out[f"attn_{tag}_y"] = h.numpy()
         blk.attn.__DEBUG__ = False
     np.savez_compressed(os.path.join(HERE, "block_ref.npz"), **{k: v.astype(np.float32) for k, v in out.items()})
-    print("written", os.listdir(HERE))
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference [ops] [blocks] [full]")
+    main(sys.argv[1], tuple(sys.argv[2:]))

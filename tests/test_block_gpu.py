@@ -218,6 +218,8 @@ def test_block_and_model_match_reference_vectors(golden_block, tag, preset, size
         y = blk(x.to("cuda", dtype), patch_resolution=(g, g))[0]
         logits = model(oracle.make_images(batch, size, seed=3).to("cuda", dtype))
     tol = TOL[dtype]
-    assert rel_err(a.float(), golden_block[f"attn_{tag}_y"]) < tol
-    assert rel_err(y.float(), golden_block[f"block_{tag}_y"]) < tol
-    assert rel_err(logits.float(), golden_block[f"vig_{tag}_logits"]) < (2e-4 if dtype == torch.float32 else 3e-2)
+    errs = (rel_err(a.float(), golden_block[f"attn_{tag}_y"]), rel_err(y.float(), golden_block[f"block_{tag}_y"]),
+            rel_err(logits.float(), golden_block[f"vig_{tag}_logits"]))
+    print(f"{tag} {dtype}: attn {errs[0]:.2e} block {errs[1]:.2e} logits {errs[2]:.2e} (bar {tol:.0e})")
+    vig_b200.check_status()
+    assert errs[0] < tol and errs[1] < tol and errs[2] < tol, errs

@@ -57,3 +57,16 @@ def test_block_and_model_oracle_match_reference(golden_block, tag, preset, size,
     assert rel_err(y, golden_block[f"block_{tag}_y"]) < 2e-5
     logits = oracle.vig_forward(sd, oracle.make_images(batch, size, seed=3), shape)
     assert rel_err(logits, golden_block[f"vig_{tag}_logits"]) < 5e-5
+
+
+@pytest.mark.parametrize("tag,preset,size,batch", [("t1024", "vig_t_dk64", 1024, 1), ("s224x16", "vig_s_dk64", 224, 16),
+                                                   ("t224x4_dk32", "vig_t", 224, 4)])
+def test_full_depth_model_oracle_matches_reference(tag, preset, size, batch):
+    """12-block models with the benchmark's weights and images (seed 0) against the reference's logits.  (The 16384-token
+    ViG-B vector in the same file takes the oracle a minute and is compared on the GPU only.)"""
+    import os
+    from conftest import GOLDEN
+    ref = np.load(os.path.join(GOLDEN, "model_ref.npz"))[f"vig_{tag}_logits"]
+    shape = oracle.PRESETS[preset]
+    logits = oracle.vig_forward(oracle.make_state_dict(shape, seed=0), oracle.make_images(batch, size, seed=0), shape)
+    assert rel_err(logits, ref) < 1e-4

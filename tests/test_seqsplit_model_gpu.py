@@ -51,5 +51,7 @@ def test_row_split_forward_matches_single_gpu(size):
     for r in range(world):
         split, whole = ret[r]
         scale = whole.abs().max()
-        assert (split - whole).abs().max() / scale < 1e-2          # same arithmetic up to bf16 rounding of boundary data
-        assert (split - ref).abs().max() / ref.abs().max() < 3e-2  # and within the bf16 bar of the fp32 oracle
+        e_split, e_ref = float((split - whole).abs().max() / scale), float((split - ref).abs().max() / ref.abs().max())
+        print(f"rank {r}: split vs single GPU {e_split:.2e}, split vs fp32 oracle {e_ref:.2e}")
+        assert e_split < 1e-2          # same arithmetic up to bf16 rounding of boundary data
+        assert e_ref < 2e-2            # and within the bf16 bar of the fp32 oracle

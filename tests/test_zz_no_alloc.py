@@ -21,14 +21,18 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row(dtype):
     import vig_b200
     from vig_b200 import ops
     # both shapes span several segments, so the scratch array is really used; the second call is larger
+    status = ops.status_word().tensor                            # the error word exists before the calls under test
     for call, (B, H, L, dk) in enumerate([(2, 3, 1300, 64), (3, 2, 2100, 32)]):
         q, k, v, gf, gb = _inputs(B, H, L, dk, dtype, seed=40 + call)
         expected = vig_b200.bi_gla(q, k, v, gf, gb, out_scale=0.5)
         out = torch.full_like(expected, float("nan"))
-        before = torch.cuda.memory_allocated()
-        ops.bi_gla_noalloc(q, k, v, gf, gb, out, out_scale=0.5)
-        assert torch.cuda.memory_allocated() == before           # nothing came from torch's allocator either
         torch.cuda.synchronize()
+        before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
+        ops.bi_gla_noalloc(q, k, v, gf, gb, out, out_scale=0.5, status=status)
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before           # nothing came from torch's allocator ...
+        assert torch.cuda.mem_get_info()[0] == free_before       # ... and nothing from cudaMalloc inside the library
+        ops.check_status()
         # same arithmetic; for 2048..8192 tokens the workspace entry point runs the tensor-core path as one launch and
         # this one as three, which differ by bf16 rounding of the cross-segment term
         tol = 1e-5 if dtype == torch.float32 else 1e-2
@@ -53,3 +57,31 @@ def test_noalloc_rejects_problems_beyond_the_fixed_scratch():
     assert b"scratch" in L_.vig_strerror(st)
     with pytest.raises(RuntimeError, match="scratch"):
         _lib.check(st, "vig_bigla_fwd_noalloc")
+
+
+def test_noalloc_limit_is_what_the_call_uses():
+    """The scratch limit counts what the kernel family that runs really uses: a single 256-token segment on the
+    tensor-core path uses none, however large the batch; fp32 (SIMT path, 64-token chunks) reaches the limit at a
+    quarter of the tokens the tensor-core path does."""
+    import vig_b200
+    from vig_b200 import _lib, ops
+    status = ops.status_word().tensor
+    # ViG-T at 224x224 with a large batch: one segment per sequence, no scratch, accepted
+    q, k, v, gf, gb = _inputs(256, 3, 196, 64, torch.bfloat16, seed=50)
+    out = torch.empty_like(v)
+    ops.bi_gla_noalloc(q, k, v, gf, gb, out, out_scale=0.5, status=status)
+    expected = vig_b200.bi_gla(q, k, v, gf, gb, out_scale=0.5)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert float((out.float() - expected.float()).abs().max()) == 0.0
+    # B*H*ceil(L/256) = 480 <= 504 < B*H*ceil(L/64) = 1920: bf16 runs, the same shape in fp32 is over the SIMT limit
+    q, k, v, gf, gb = _inputs(40, 3, 1024, 64, torch.bfloat16, seed=51)
+    out = torch.empty_like(v)
+    ops.bi_gla_noalloc(q, k, v, gf, gb, out, status=status)
+    expected = vig_b200.bi_gla(q, k, v, gf, gb, impl=_lib.IMPL_TC_SPLIT)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert float((out.float() - expected.float()).abs().max()) == 0.0
+    f32 = [t.float() for t in (q, k, v, gf, gb)]
+    with pytest.raises(RuntimeError, match="scratch"):
+        ops.bi_gla_noalloc(*f32, torch.empty_like(f32[2]), status=status)

@@ -127,7 +127,7 @@ int vig::bigla_fwd_internal(const void* q, const void* k, const void* v, const v
     if (use_tc) {
         // the single-launch form (on request, or by default where it is the faster one) needs the larger workspace;
         // with only the states' worth of workspace the call runs as three launches
-        const size_t need = bigla_tc_workspace(B, H, L, dk, dv, true);
+        const size_t need = bigla_tc_min_workspace(p);
         if (need && (!workspace || workspace_bytes < need)) return VIG_ERR_WORKSPACE;
         if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return VIG_ERR_ALIGN;
         return bigla_tc_launch(p, workspace, workspace_bytes, !no_single && (impl == VIG_IMPL_TC_SINGLE || (impl != VIG_IMPL_TC_SPLIT && bigla_tc_prefers_single(L))), (cudaStream_t)stream);

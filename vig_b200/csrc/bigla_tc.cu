@@ -59,15 +59,6 @@ __device__ __forceinline__ void half_bar_sync(int half) {
 }
 
 
-#ifdef VIG_TC_TIMING
-__device__ long long g_tc_timing[64 * 16];
-#define TC_STAMP(slot) do { if (FUSED) { if (tid == 0 && blockIdx.x == 1 && item_count < 4 && n < 4) g_tc_timing[(item_count * 4 + n) * 16 + (slot)] = clock64(); } \
-    else if (tid == 0 && blockIdx.x == 1 && blockIdx.y == 1 && n < 4) g_tc_timing[(STATES_ONLY ? 0 : 512) + n * 16 + (slot)] = clock64(); } while (0)
-#define TC_STAMPX(slot) do { if (FUSED && tid == 0 && blockIdx.x == 1 && item_count < 4) g_tc_timing[(item_count * 4 + 3) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TC_STAMP(slot) do { } while (0)
-#define TC_STAMPX(slot) do { } while (0)
-#endif
 
 // MODE 0: one segment per CTA, entering states from the workspace (or the caller's initial states).
 // MODE 1: states only -- local end states of every segment from a zero state, no q, no output.
@@ -219,10 +210,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
             if (tid < DK) gtot[tid] = 0.f;
         }
-        TC_STAMP(0);
         if (warp == 0) waiter.wait(bar_gk, par);              // one warp polls; the others sleep in the barrier
         __syncthreads();
-        TC_STAMP(1);
 
         // ---- phase 1: cumulative gates (log2 units) and the scaled operand tiles ------------------------
         // One code path for both directions and for clamped / padded chunks (runtime selects, not template variants),
@@ -298,7 +287,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
             out_of_range = worst > MAX_EXPONENT2;
         }
-        TC_STAMP(2);
         if (out_of_range && p.status) atomicOr(p.status, 2);
         if (grp == 0) {
             vec[2 * cp] = ex2(glast.x); vec[2 * cp + 1] = ex2(glast.y);
@@ -326,7 +314,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         tc_fence_before();
         __syncthreads();                          // raw q / k / gate tiles are dead from here on
         if (tid == 0 && n + 1 < n_iter) issue_gk(n + 1);
-        TC_STAMP(3);
 
         const uint32_t kt = sbase + OFF_KT, v_addr = sbase + OFF_V;
         bool o_has = dir != dir_first;            // the chunk's output accumulator already has content (issuer 0's view)
@@ -354,7 +341,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                 tc_commit(bar_p0);                        // with issuer 0's commit: both readers of the scaled q tile are done
             }
             __syncwarp();
-            TC_STAMP(4);
             // ---- scores -> masked bf16 P tiles (warps 0-3: keys 0..63 over the dead raw q tile,
             //      warps 4-7: keys 64..127 over the dead scaled q tile) ---------------------------------
             const int half = warp >> 2;
@@ -363,7 +349,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             uint8_t* ptile = smem + (half ? OFF_QT : OFF_RQ);         // both tiles are dead once the score MMA is done
             if ((warp & 3) == 0) waiter.wait(bar_p0, par);
             half_bar_sync(half);
-            TC_STAMP(5);
             tc_fence_after();
             // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test); on the
             // diagonal, bit j of `dbits` says whether key j of the block is kept for my query row.
@@ -396,11 +381,9 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
                     }
                 }
             }
-            TC_STAMP(6);
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
-            TC_STAMP(7);
         }
         // ---- MMA issue 2: P V into the output accumulator (issuer 0), K^T V into the second score buffer (issuer 1)
         if (issuer == 0) {
@@ -422,7 +405,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             tc_commit(bar_o);
         }
         __syncwarp();
-        TC_STAMP(8);
 
         // ---- state update in registers ---------------------------------------------------------------
         if (warp == 0) {
@@ -430,7 +412,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             if (tid == 0 && n + 1 < n_iter) issue_qv(n + 1);
         }
         __syncthreads();
-        TC_STAMP(9);
         tc_fence_after();
         {
             float u[32];
@@ -445,7 +426,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             }
         }
         s_zero = false;
-        TC_STAMP(10);
         tc_fence_before();                        // ordered before the next tensor-core write of this buffer by the
                                                   // CTA barriers of the next iteration
 
@@ -508,9 +488,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
             __threadfence();
             __syncthreads();
         };
-        TC_STAMPX(11);
         group_wait(p.group_cnt + bh);             // every segment's local end state is in the workspace
-        TC_STAMPX(12);
         // ---- scan over the segments, split by state element across the sequence's CTAs: each CTA turns, for its
         //      slice of the dk x dv elements, every segment's local end state into the state that ENTERS that
         //      segment (in place), and delivers the sequence's final state / total decay for that slice ----------
@@ -566,13 +544,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         __syncthreads();
         uint32_t* scanned = p.group_cnt + (size_t)p.B * p.H + bh;
         if (tid == 0) atomicAdd(scanned, 1u);
-        TC_STAMPX(13);
         group_wait(scanned);                      // every slice of the entering states is in place
         // Draw the next item and keep it in a register until the end of this one, so that the round trip of the
         // atomic costs no stall.  Not earlier: a CTA that holds a ticket of a sequence it is still waiting for
         // could never be released.
         if (tid == 0) next_item = (int)atomicAdd(p.ticket, 1u);
-        TC_STAMPX(14);
         // ---- state operand of every chunk: bf16(2^{cvec} * S_enter), MN-major [channel][value] -------------------
         const uint32_t st_off[4] = {(uint32_t)OFF_ST, (uint32_t)OFF_RG, (uint32_t)(OFF_RG + 64 * 128), (uint32_t)OFF_V};
         float4 enter[2][4];                       // both directions' entering states are requested before either is used
@@ -620,7 +596,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) bigla_tc_kernel(const __grid_cons
         __syncwarp();
         if (warp == 0) waiter.wait(bar_x, item_count & 1u);
         __syncthreads();
-        TC_STAMPX(15);
         ++item_count;
     }
 
@@ -687,9 +662,9 @@ int launch_tc(const BiglaParams& p_in, const TcMaps& maps, bool allow_fused, cud
         int dev = 0;
         if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
         if (dev >= 0 && dev < 64) {
-            if ((e = cudaFuncSetAttribute(kF, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
-            if ((e = cudaFuncSetAttribute(kF, cudaFuncAttributePreferredSharedMemoryCarveout, 100)) != cudaSuccess) return (int)e;
+            if ((e = ensure_smem_attr(reinterpret_cast<const void*>(kF), SMEM_BYTES)) != cudaSuccess) return (int)e;
             if (!resident[dev]) {
+                if ((e = cudaFuncSetAttribute(kF, cudaFuncAttributePreferredSharedMemoryCarveout, 100)) != cudaSuccess) return (int)e;
                 int per_sm = 0, sms = 0;
                 if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kF, NTHREADS, SMEM_BYTES)) != cudaSuccess) return (int)e;
                 if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
@@ -714,13 +689,13 @@ int launch_tc(const BiglaParams& p_in, const TcMaps& maps, bool allow_fused, cud
         }
     }
     if (use_ws || (need_states && !p.o)) {
-        if ((e = cudaFuncSetAttribute(kA, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
+        if ((e = ensure_smem_attr(reinterpret_cast<const void*>(kA), SMEM_BYTES)) != cudaSuccess) return (int)e;
         kA<<<grid, NTHREADS, SMEM_BYTES, stream>>>(maps, p, 1);
         p.nchunk = nseg;
         if (int st = bigla_scan_launch(p, stream)) return st;
     }
     if (p.o) {
-        if ((e = cudaFuncSetAttribute(kC, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)) != cudaSuccess) return (int)e;
+        if ((e = ensure_smem_attr(reinterpret_cast<const void*>(kC), SMEM_BYTES)) != cudaSuccess) return (int)e;
         kC<<<grid, NTHREADS, SMEM_BYTES, stream>>>(maps, p, use_ws);
     }
     return (int)cudaGetLastError();
@@ -728,11 +703,6 @@ int launch_tc(const BiglaParams& p_in, const TcMaps& maps, bool allow_fused, cud
 
 }  // namespace
 
-#ifdef VIG_TC_TIMING
-extern "C" __attribute__((visibility("default"))) int vig_dbg_tc_timing(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_tc_timing, sizeof(long long) * 64 * 16);
-}
-#endif
 
 // Measured on B200: the single-launch form wins for sequences of 8..32 segments (2048..8192 tokens) and halves
 // the DRAM traffic there; shorter sequences have too few segments to amortise the two group barriers, longer
@@ -760,11 +730,20 @@ size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv, bool split_only) 
     return ((st + 255) & ~(size_t)255) + counter_bytes(B, H) + (size_t)MAX_SLOTS * 4 * TILE_B;
 }
 
+// What this call really touches: nothing for a single segment with an output (its end states go straight to the caller).
+size_t bigla_tc_min_workspace(const BiglaParams& p) {
+    const bool need_states = p.final_f || p.final_b || p.logdecay_f || p.logdecay_b;
+    if (p.L <= SEG && (p.o || !need_states)) return 0;
+    return states_bytes(p.B, p.H, p.L, p.dk, p.dv);
+}
+
 int bigla_tc_launch(const BiglaParams& p_in, void* ws, size_t ws_bytes, bool allow_fused, cudaStream_t stream) {
     BiglaParams p = p_in;
     const size_t nseg = (p.L + SEG - 1) / SEG;
     const size_t st = states_bytes(p.B, p.H, p.L, p.dk, p.dv);
-    if (ws_bytes < st) return VIG_ERR_WORKSPACE;
+    const size_t min_ws = bigla_tc_min_workspace(p);
+    if (min_ws && (!ws || ws_bytes < min_ws)) return VIG_ERR_WORKSPACE;
+    if (!ws) ws_bytes = 0;
     if (ws_bytes < bigla_tc_workspace(p.B, p.H, p.L, p.dk, p.dv, false)) allow_fused = false;
     p.ws_state = reinterpret_cast<float*>(ws);
     p.ws_decay = p.ws_state + (size_t)p.B * p.H * nseg * 2 * p.dk * p.dv;

@@ -71,9 +71,6 @@ struct WaveParams {
 
 struct Item { int bh, seg, dir, nch, w, pad0, pad1, pad2; };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 template <typename T> struct RedAdd;
 template <> struct RedAdd<__nv_bfloat16> {
@@ -99,16 +96,6 @@ __device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, 
     if (status) atomicOr(status, 1);
 }
 
-#ifdef VIG_WAVE_TIMING
-__device__ long long g_wave_timing[160 * 32];
-#define WT_DECL long long wt_acc[6] = {0, 0, 0, 0, 0, 0}; const long long wt_start = clock64();
-#define WT(i, stmt) do { const long long wt_t = clock64(); stmt; wt_acc[i] += clock64() - wt_t; } while (0)
-#define WT_DUMP(role) do { if (blockIdx.x < 160) { for (int i_ = 0; i_ < 6; ++i_) g_wave_timing[blockIdx.x * 32 + (role) * 6 + i_] = wt_acc[i_]; g_wave_timing[blockIdx.x * 32 + 30] = clock64() - wt_start; } } while (0)
-#else
-#define WT_DECL
-#define WT(i, stmt) do { stmt; } while (0)
-#define WT_DUMP(role) do { } while (0)
-#endif
 
 template <typename T>
 __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_constant__ TcMaps maps, const WaveParams wp) {
@@ -166,7 +153,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             int tk_next = (int)atomicAdd(wp.ticket, 1u);       // consumed one item later: its round trip costs no stall
             Item lcur; lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = 0;
             int l_items = 0, l_ci = 0;
-            WT_DECL
             #pragma unroll 1
             for (uint32_t lm = 0;; ++lm, ++l_ci) {
                 if (l_ci == lcur.nch) {                        // next work item
@@ -189,9 +175,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     l_ci = 0;
                 }
                 const uint32_t s = lm % 3;
-                if (lm >= 3) WT(0, waiter.wait(bar(B_SFREE + s), ((lm / 3) - 1) & 1));
+                if (lm >= 3) waiter.wait(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
                 if (*abort_flag) break;
-                if (lcur.nch == 0) { mbar_arrive(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
+                if (lcur.nch == 0) { mbar_arrive_plain(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
                 const int t0 = lcur.seg * W_SEG + chunk_of(lcur, l_ci) * CHUNK;
                 const int b = lcur.bh / p.H, h = lcur.bh % p.H;
                 const uint32_t dst = sbase + s * W_STAGE_B, fb = bar(B_FULL + s);
@@ -201,19 +187,17 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 tma_load_4d(dst + WS_Q, &maps.q, 0, t0, h, b, fb);
                 tma_load_4d(dst + WS_V, &maps.v, 0, t0, h, b, fb);
             }
-            WT_DUMP(0);
         } else if (tid == 16 * 32) {
             // ---- MMA thread ----
             Item mcur; mcur.nch = 0; mcur.bh = mcur.seg = mcur.dir = mcur.w = 0;
             int m_items = 0, m_ci = 0;
-            WT_DECL
             #pragma unroll 1
             for (uint32_t m = 0;; ++m, ++m_ci) {
                 const uint32_t s = m % 3, st = sbase + s * W_STAGE_B;
-                WT(0, waiter.wait(bar(B_PREPPED + s), (m / 3) & 1));  // also orders the read of the work item after its write
+                waiter.wait(bar(B_PREPPED + s), (m / 3) & 1);  // also orders the read of the work item after its write
                 if (*abort_flag) break;
                 if (m_ci == mcur.nch) { read_item(m_items, mcur); ++m_items; m_ci = 0; }
-                if (mcur.nch == 0) { mbar_arrive(bar(B_PFULL)); break; }      // end marker: wakes the score warps
+                if (mcur.nch == 0) { mbar_arrive_plain(bar(B_PFULL)); break; }      // end marker: wakes the score warps
                 const uint32_t qt = st + WS_Q, kt = st + WS_K, vt = st + WS_V, p0 = st + WS_G, p1 = sbase + WO_X, stt = sbase + WO_ST;
                 const uint32_t o_acc = tmem + WT_O + 64u * (m & 1u);
                 const bool s_zero = state_zero(mcur, m_ci);
@@ -223,15 +207,15 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 for (int k4 = 0; k4 < WDK / 16; ++k4) tc_mma(tmem + WT_P, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
                 tc_commit(bar(B_PFULL));
                 // (b) product with the entering state
-                WT(1, waiter.wait(bar(B_STREADY), m & 1));
-                if (m >= 2) WT(2, waiter.wait(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1));
+                waiter.wait(bar(B_STREADY), m & 1);
+                if (m >= 2) waiter.wait(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
                 tc_fence_after();
                 if (!s_zero) {
 #pragma unroll 1
                     for (int k4 = 0; k4 < WDK / 16; ++k4) tc_mma(o_acc, make_desc(qt + k4 * 32), make_desc(stt + k4 * 2048), IDESC_OV, k4 > 0);
                 }
                 // (c) masked scores x v, state update
-                WT(3, waiter.wait(bar(B_PREADY), m & 1));
+                waiter.wait(bar(B_PREADY), m & 1);
                 tc_fence_after();
 #pragma unroll 1
                 for (int k8 = 0; k8 < CHUNK / 16; ++k8)
@@ -243,7 +227,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 tc_commit(bar(B_UFULL));
                 tc_commit(bar(B_SFREE + s));
             }
-            WT_DUMP(1);
         }
     } else if (warp < W_PREP_WARPS) {
         // =============================== prep warps: gates and operand scaling, in place ===============================
@@ -255,15 +238,14 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         const float clamp_lo = (p.clamp_min == p.clamp_min) ? p.clamp_min * LOG2E : -INFINITY;
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
         int items = 0, ci = 0;
-        WT_DECL
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) WT(0, waiter.wait(bar(B_FULL + s), (m / 3) & 1));
+            if (lane == 0) waiter.wait(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
-            if (cur.nch == 0) { if (lane == 0) mbar_arrive(bar(B_PREPPED + s)); break; }
+            if (cur.nch == 0) { if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s)); break; }
             uint8_t* stg = smem + s * W_STAGE_B;
             const uint32_t* sg = reinterpret_cast<const uint32_t*>(stg + WS_G);
             float* part = reinterpret_cast<float*>(smem + WO_PART) + (m & 1) * (NG * WDK);
@@ -285,9 +267,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // halves rotate through two register arrays (glA = first half, glB = second), so the loop bodies are half the
             // code of a full unroll while four tokens x four channels still overlap their latencies.
             float4 glA[4], glB[4];
-#ifdef VIG_WAVE_TIMING
-            const long long wt_p0 = clock64();
-#endif
             {
                 float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
@@ -319,14 +298,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             // the prep warps meet on an mbarrier, not a named barrier: its wait is bounded like every other wait here
             __syncwarp();
-#ifdef VIG_WAVE_TIMING
-            wt_acc[3] += clock64() - wt_p0;
-#endif
-            if (lane == 0) { mbar_arrive(bar(B_PART)); WT(1, waiter.wait(bar(B_PART), m & 1)); }
+            if (lane == 0) { mbar_arrive_plain(bar(B_PART)); waiter.wait(bar(B_PART), m & 1); }
             __syncwarp();
-#ifdef VIG_WAVE_TIMING
-            const long long wt_p1 = clock64();
-#endif
             float4 off = half_off, gref = make_float4(0.f, 0.f, 0.f, 0.f), glast = gref;
 #pragma unroll 2
             for (int g2 = 0; g2 < NG; ++g2) {
@@ -338,10 +311,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 glast.x += s4.x; glast.y += s4.y; glast.z += s4.z; glast.w += s4.w;
             }
             off.x -= gref.x; off.y -= gref.y; off.z -= gref.z; off.w -= gref.w;
-#ifdef VIG_WAVE_TIMING
-            wt_acc[4] += clock64() - wt_p1;
-            const long long wt_p2 = clock64();
-#endif
             // Log-gates are <= 0, so a lane's exponents are monotone along its 8 tokens: the largest magnitude (for the
             // status flag; every exponent is clamped regardless) is at one of the two ends.
             float worst = fmaxf(fmaxf(fabsf(off.x + glA[0].x), fabsf(off.y + glA[0].y)), fmaxf(fabsf(off.z + glA[0].z), fabsf(off.w + glA[0].w)));
@@ -373,10 +342,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
 #pragma unroll
                 for (int i = 0; i < 4; ++i) glA[i] = glB[i];
             }
-#ifdef VIG_WAVE_TIMING
-            __syncwarp();
-            wt_acc[5] += clock64() - wt_p2;
-#endif
             if (grp == 0 && half == 0) {                      // per-channel factors of this iteration for the state warps
                 float* ve = vec + (m & 3) * 256 + 4 * c4l;
                 *reinterpret_cast<float4*>(ve) = make_float4(ex2(glast.x), ex2(glast.y), ex2(glast.z), ex2(glast.w));
@@ -388,9 +353,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             if (out_of_range && p.status) atomicOr(p.status, 2);
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_PREPPED + s));
+            if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s));
         }
-        if (warp == 0 && lane == 0) WT_DUMP(2);
     } else if (warp < W_PREP_WARPS + 4) {
         // =============================== score warps: masking, output ===============================
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(W_REGS_SCORE));
@@ -401,10 +365,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
         Item prev = cur;
         int items = 0, ci = 0, prev_ci = 0;
-        WT_DECL
         // output of iteration j: accumulator slot j & 1 -> global
         auto epilogue = [&](uint32_t j, const Item& it, int jci) {
-            if (lane == 0) WT(2, waiter.wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1));
+            if (lane == 0) waiter.wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
             __syncwarp();
             tc_fence_after();
             const int c = chunk_of(it, jci);
@@ -413,7 +376,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             const bool first = ndir == 1 || it.w < w_other || (it.w == w_other && it.dir == 0);
             uint32_t* flag = wp.chunk_flag + (size_t)it.bh * nseg * W_SEG_CHUNKS + it.seg * W_SEG_CHUNKS + c;
             if (!first) {                                     // the other direction's half must be in place
-                if (lane == 0) WT(3, global_wait(flag, 4u, abort_flag, p.status));
+                if (lane == 0) global_wait(flag, 4u, abort_flag, p.status);
                 __syncwarp();
             }
             T* obase = reinterpret_cast<T*>(p.o) + (it.bh / p.H) * p.so[0] + (it.bh % p.H) * p.so[1] + (int64_t)tok * p.so[2];
@@ -425,7 +388,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (half == 1) {                              // the slot is read: hand it back before the global traffic
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_OFREE + (j & 1)));
+                    if (lane == 0) mbar_arrive_plain(bar(B_OFREE + (j & 1)));
                 }
                 if (tok < p.L) {
 #pragma unroll
@@ -440,12 +403,12 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             if (first && ndir == 2) {                         // publish my half of the chunk
                 __syncwarp();
-                if (lane == 0) WT(4, { __threadfence(); atomicAdd(flag, 1u); });
+                if (lane == 0) { __threadfence(); atomicAdd(flag, 1u); }
             }
         };
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
-            if (lane == 0) WT(0, waiter.wait(bar(B_PFULL), m & 1));
+            if (lane == 0) waiter.wait(bar(B_PFULL), m & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -461,7 +424,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
 #pragma unroll 1
             for (int cb = 0; cb < 4; ++cb) {                  // key block: keys 32*cb .. 32*cb+31
                 if (cb == 2 && m > 0) {                       // the second tile is free once the previous iteration's MMAs are done
-                    if (lane == 0) WT(1, waiter.wait(bar(B_UFULL), (m - 1) & 1));
+                    if (lane == 0) waiter.wait(bar(B_UFULL), (m - 1) & 1);
                     __syncwarp();
                 }
                 const bool all_zero = dir ? cb < quad : cb > quad;
@@ -490,13 +453,12 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             tc_fence_before();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_PREADY));
+            if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
             }
-            if (m > 0) WT(5, epilogue(m - 1, prev, prev_ci));       // one iteration behind: the MMAs of m - 1 finish meanwhile
+            if (m > 0) epilogue(m - 1, prev, prev_ci);       // one iteration behind: the MMAs of m - 1 finish meanwhile
             if (at_end) break;
             prev = cur; prev_ci = ci;
         }
-        if (warp == 8 && lane == 0) WT_DUMP(3);
     } else if (warp < W_PREP_WARPS + 8) {
         // =============================== state warps ===============================
         const int quad = warp & 3;
@@ -510,11 +472,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
         int items = 0, ci = 0;
         bool s_zero = true;
-        WT_DECL
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) WT(0, waiter.wait(bar(B_PREPPED + s), (m / 3) & 1));
+            if (lane == 0) waiter.wait(bar(B_PREPPED + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -527,7 +488,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     gacc = 0.f;
                 } else {
                     uint32_t* cnt = wp.chain_cnt + cur.bh * 2 + cur.dir;
-                    if (lane == 0) WT(1, global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag, p.status));
+                    if (lane == 0) global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag, p.status);
                     __syncwarp();
                     const float* box = wp.mailbox + (((size_t)cur.bh * 2 + cur.dir) * 2 + ((cur.w - 1) & 1)) * SLOT;
                     src = box;
@@ -553,8 +514,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 fence_proxy_async();
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(B_STREADY));
-            if (lane == 0) WT(2, waiter.wait(bar(B_UFULL), m & 1));
+            if (lane == 0) mbar_arrive_plain(bar(B_STREADY));
+            if (lane == 0) waiter.wait(bar(B_UFULL), m & 1);
             __syncwarp();
             tc_fence_after();
             {
@@ -596,11 +557,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (gdst && hi == 0) gdst[st_row] = last ? gacc * LN2 : gacc;   // the caller gets natural-log units
                 if (!last) {
                     __syncwarp();
-                    if (lane == 0) WT(3, { __threadfence(); atomicAdd(wp.chain_cnt + cur.bh * 2 + cur.dir, 1u); });
+                    if (lane == 0) { __threadfence(); atomicAdd(wp.chain_cnt + cur.bh * 2 + cur.dir, 1u); }
                 }
             }
         }
-        if (warp == 12 && lane == 0) WT_DUMP(4);
     }
     // ---- teardown: every role has left its loop; all MMAs were waited for by their consumers ----
     tc_fence_before();
@@ -639,7 +599,7 @@ int launch_wave(const BiglaParams& p, const TcMaps& maps, void* ws, cudaStream_t
         if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
         sm_count[dev] = sms;
     }
-    if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES)) != cudaSuccess) return (int)e;
+    if ((e = ensure_smem_attr(reinterpret_cast<const void*>(kern), W_SMEM_BYTES)) != cudaSuccess) return (int)e;
     const int ndir = p.dir_mask == 3 ? 2 : 1;
     const long long items = (long long)BH * ndir * nseg;
     const int grid = (int)(items < sm_count[dev] ? items : sm_count[dev]);
@@ -701,8 +661,3 @@ int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStrea
 
 }  // namespace vig
 
-#ifdef VIG_WAVE_TIMING
-extern "C" __attribute__((visibility("default"))) int vig_dbg_wave_timing(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, vig::g_wave_timing, sizeof(long long) * 160 * 32);
-}
-#endif

@@ -92,6 +92,7 @@ size_t bigla_simt_workspace(int B, int H, int L, int dk, int dv);
 int bigla_scan_launch(const BiglaParams& p, cudaStream_t stream);
 int bigla_tc_launch(const BiglaParams& p, void* ws, size_t ws_bytes, bool allow_fused, cudaStream_t stream);
 size_t bigla_tc_workspace(int B, int H, int L, int dk, int dv, bool split_only);
+size_t bigla_tc_min_workspace(const BiglaParams& p);   // what this very call uses (0 for one segment with an output)
 bool bigla_tc_supported(const BiglaParams& p);
 bool bigla_tc_prefers_single(int L);
 // warp-specialised wavefront form (large batches): one persistent CTA per SM, state hand-off between segments

@@ -133,7 +133,6 @@ __global__ void __launch_bounds__(EW_THREADS, 2) dwconv3x3_rows_kernel(const T* 
     for (int i = 0; i < RUN; ++i) {
         const int xx = x0 + i;
         if (xx >= w) break;
-        constexpr int dummy = 0; (void)dummy;
         const int sl = i % 3, sc = (i + 1) % 3, sr = (i + 2) % 3;     // slots of columns xx-1, xx, xx+1 (static: the loop is unrolled)
 #pragma unroll
         for (int ky = 0; ky < 3; ++ky) unpack4(raw[i % PF][ky], win[sr][ky]);

@@ -28,9 +28,6 @@ constexpr int AN_A_BYTES = 128 * AN_BK * 2;    // [128 rows x 64 k]
 
 struct AnMaps { CUtensorMap x, w, res, r, h; };
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
-}
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <typename T, int NT>            // NT = N, the row width, a compile-time constant so that a row lives in registers
@@ -352,7 +349,7 @@ extern "C" int vig_linear_add_rmsnorm_fwd(const void* x, int64_t ldx, const void
 #define VIG_AN_LAUNCH(TT, NN)                                                                                                  \
     {                                                                                                                          \
         auto kfn = linear_add_rmsnorm_kernel<TT, NN>;                                                                          \
-        if ((e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e; \
+        if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), (int)smem)) != cudaSuccess) return (int)e; \
         kfn<<<grid, AN_THREADS, smem, (cudaStream_t)stream>>>(maps, (const TT*)residual, (const TT*)norm_weight, (TT*)out_r,   \
                                                                (TT*)out_h, (int)M, K / AN_BK, CH, nstage, eps, status_dev);   \
     }

@@ -10,12 +10,12 @@
 // into a swizzled 4 KB box of shared memory and lane 0 sends it out with one TMA store: a thread owns a row, so direct
 // 16-byte stores would touch 32 lines per request and fill only half of each 32-byte sector.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2.. epilogue.  Every wait is bounded.
-#include <cuda.h>
-#include <mutex>
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace vig {
 namespace {
+
+using namespace tc;
 
 constexpr int BK = 64;                         // k elements per stage row (128 bytes)
 constexpr int BNF = 64;                        // features per block: 64 gate rows + 64 y rows -> MMA N = 128
@@ -27,44 +27,6 @@ constexpr int MAX_A_BYTES = 96 * 1024;
 constexpr int GS_THREADS = 64 + 256;
 constexpr int OUT_BOX_BYTES = 32 * BNF * 2;    // one epilogue warp's [32 rows x 64 features] box
 constexpr int OUT_STAGE_BYTES = 8 * OUT_BOX_BYTES;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)); }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
-constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\tmov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
-                 ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(DESC_HI) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-}
 
 // sigmoid(x) = 0.5 tanh(x / 2) + 0.5 with the single-instruction tanh: one MUFU per element instead of two
 // (exp + reciprocal), which is what bounds the epilogue; its error (~2^-11) is below the bf16 / fp16 output step.
@@ -165,7 +127,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
         // The whole warp walks the loop (uniform control flow keeps the descriptor arithmetic off the issuing lane's
         // critical path); lane 0 issues.  Descriptors advance by adding to their 14-bit address field (16-byte units).
         uint32_t a_phase = 0, st = 0, b_phase = 0, acc_it = 0;
-        const uint32_t a_lo0 = desc_lo(sbase), b_lo0 = desc_lo(sbase + off_b);
+        const uint32_t a_lo0 = make_desc(sbase), b_lo0 = make_desc(sbase + off_b);
         const uint32_t a_sub = (uint32_t)KB * (A_BOX_BYTES >> 4);
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             const int nb0 = nb_begin(tile), nb1 = nb_end(tile);
@@ -231,7 +193,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
                             pk[(c + e) / 2] = Pk<T>::pack(g[e] * y[e] * sigmoid_tanh(g[e]), g[e + 1] * y[e + 1] * sigmoid_tanh(g[e + 1]));
                     }
                     tc_fence_before();
-                    mbar_arrive(bar_acc_empty + 8 * buf);               // the accumulator is in registers: the MMA warp may refill it
+                    mbar_arrive_plain(bar_acc_empty + 8 * buf);               // the accumulator is in registers: the MMA warp may refill it
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the box
                     __syncwarp();
 #pragma unroll
@@ -256,33 +218,6 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn gs_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
-bool map_2d(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int dtype) {
-    EncodeTiledFn fn = gs_encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(m, dtype == VIG_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
-              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace
 }  // namespace vig
 
@@ -292,7 +227,7 @@ extern "C" int vig_linear_swiglu_supported(int64_t M, int K, int I, int dtype) {
     if (dtype != VIG_DTYPE_BF16 && dtype != VIG_DTYPE_F16) return 0;
     if (M <= 0 || K <= 0 || I <= 0 || K % BK || I % BNF) return 0;
     if ((int64_t)128 * K * 2 > MAX_A_BYTES) return 0;            // one 128-row subtile of x must fit its shared-memory budget
-    return gs_encode_fn() != nullptr;
+    return tc::encode_fn() != nullptr;
 }
 
 // Measured on B200 against cuBLAS + the SwiGLU kernel: 1.5-1.7x faster while two 128-row subtiles of x fit in shared
@@ -309,8 +244,8 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) return VIG_ERR_ALIGN;
     if (ldx < K || ldo < I || (ldx * 2) % 16 || (ldo * 2) % 16 || M >= (1ll << 31)) return VIG_ERR_ARG;
     GsMaps maps;
-    if (!map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !map_2d(&maps.w, w, 2 * (int64_t)I, K, K, BNF, dtype) ||
-        !map_2d(&maps.o, out, M, I, ldo, 32, dtype)) return VIG_ERR_DEVICE;
+    if (!tc::make_map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !tc::make_map_2d(&maps.w, w, 2 * (int64_t)I, K, K, BNF, dtype) ||
+        !tc::make_map_2d(&maps.o, out, M, I, ldo, 32, dtype)) return VIG_ERR_DEVICE;
     const int KB = K / BK;
     const int S = ((int64_t)256 * K * 2 <= MAX_A_BYTES && M > 128) ? 2 : 1;
     const int smem = S * KB * A_BOX_BYTES + NSTAGE * B_STAGE_BYTES + OUT_STAGE_BYTES + 8 * (2 * MAX_KB + 2 * NSTAGE + 4) + 16 + 1024;
@@ -327,11 +262,11 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     const int grid = ntiles < sms ? ntiles : sms;
     if (dtype == VIG_DTYPE_BF16) {
         auto kfn = linear_swiglu_kernel<__nv_bfloat16>;
-        if ((e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
+        if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
         kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, nsplit, status_dev);
     } else {
         auto kfn = linear_swiglu_kernel<__half>;
-        if ((e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)) != cudaSuccess) return (int)e;
+        if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
         kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, nsplit, status_dev);
     }
     return (int)cudaGetLastError();

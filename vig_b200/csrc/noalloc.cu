@@ -12,7 +12,6 @@
 using namespace vig;
 
 namespace vig {
-size_t bigla_workspace_internal(int B, int H, int L, int dk, int dv, int dtype, int impl, bool no_single);
 int bigla_fwd_internal(const void* q, const void* k, const void* v, const void* g_fwd, const void* g_bwd, void* o,
                        int B, int H, int L, int dk, int dv, int dtype,
                        const int64_t* strides_q, const int64_t* strides_k, const int64_t* strides_v,
@@ -60,15 +59,16 @@ extern "C" int vig_bigla_fwd_noalloc(const void* q, const void* k, const void* v
                                      float scale, float out_scale, float gate_logit_normalizer, float clamp_min,
                                      int impl, int32_t* status_dev, void* stream) {
     if (!o) return VIG_ERR_NULL;
-    // the single-launch form of the tensor-core path needs more scratch than this array holds: it is ruled out here
-    const size_t need = bigla_workspace_internal(B, H, L, dk, dv, dtype, impl, true);
-    if (need > VIG_NOALLOC_SCRATCH_BYTES) return VIG_ERR_SCRATCH_LIMIT;
     void* scratch = nullptr;
     if (int st = scratch_for_current_device(&scratch)) return st;
+    // The launcher sizes the scratch for the kernel family that will really run with these pointers and this shape
+    // (nothing for a single 256-token segment on the tensor-core path) and refuses before any launch when the array
+    // is too small.  The single-launch and wavefront forms need more scratch than the array holds: ruled out here.
     // Every workspace slot a call reads is written earlier in the same call, so nothing needs clearing
     // between calls; what the previous call left behind is simply overwritten.
-    return bigla_fwd_internal(q, k, v, g_fwd, g_bwd, o, B, H, L, dk, dv, dtype, strides_q, strides_k, strides_v, strides_gf,
-                              strides_gb, strides_o, scale, out_scale, gate_logit_normalizer, clamp_min,
-                              nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 3, impl, true,
-                              scratch, VIG_NOALLOC_SCRATCH_BYTES, status_dev, stream);
+    const int st = bigla_fwd_internal(q, k, v, g_fwd, g_bwd, o, B, H, L, dk, dv, dtype, strides_q, strides_k, strides_v, strides_gf,
+                                      strides_gb, strides_o, scale, out_scale, gate_logit_normalizer, clamp_min,
+                                      nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 3, impl, true,
+                                      scratch, VIG_NOALLOC_SCRATCH_BYTES, status_dev, stream);
+    return st == VIG_ERR_WORKSPACE ? VIG_ERR_SCRATCH_LIMIT : st;
 }

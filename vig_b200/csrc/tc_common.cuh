@@ -53,6 +53,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_plain(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -177,31 +180,94 @@ inline EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [B,H,L,d] view with element strides s = (b, h, l): box of 128 tokens x d channels of one (b, h).
-inline bool make_map(CUtensorMap* m, const void* base, const int64_t* s, int B, int H, int L, int d, int dtype, bool swizzle128) {
+// Tensor maps are cached: a model calls the same kernels with the same buffers and shapes layer after layer and step
+// after step, and encoding five maps per scan launch is host time that shows at small problem sizes.  Key = every
+// argument of the encoding (base pointer, dims, strides, box, type, swizzle); direct-mapped table behind a mutex.
+struct MapKey {
+    const void* base;
+    uint64_t dims[4], strides[3];
+    uint32_t box[4];
+    int rank, dtype, swizzle;
+    bool operator==(const MapKey& o) const {
+        if (base != o.base || rank != o.rank || dtype != o.dtype || swizzle != o.swizzle) return false;
+        for (int i = 0; i < 4; ++i) if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+        for (int i = 0; i < 3; ++i) if (strides[i] != o.strides[i]) return false;
+        return true;
+    }
+    uint64_t hash() const {
+        uint64_t h = 1469598103934665603ull;
+        auto mix = [&](uint64_t v) { h = (h ^ v) * 1099511628211ull; h ^= h >> 29; };
+        mix(reinterpret_cast<uint64_t>(base));
+        for (int i = 0; i < 4; ++i) { mix(dims[i]); mix(box[i]); }
+        for (int i = 0; i < 3; ++i) mix(strides[i]);
+        mix((uint64_t)rank * 64 + (uint64_t)dtype * 8 + (uint64_t)swizzle);
+        return h;
+    }
+};
+
+inline bool encode_cached(CUtensorMap* m, const MapKey& key) {
+    constexpr int SLOTS = 1024;
+    struct Slot { bool used; MapKey key; CUtensorMap map; };
+    static Slot* table = new Slot[SLOTS]();
+    static std::mutex mu;
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
-    cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)B};
-    cuuint64_t strides[3] = {(cuuint64_t)s[2] * 2, (cuuint64_t)s[1] * 2, (cuuint64_t)s[0] * 2};
-    cuuint32_t box[4] = {(cuuint32_t)d, CHUNK, 1, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = fn(m, dtype == VIG_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    const int slot = (int)(key.hash() % SLOTS);
+    std::lock_guard<std::mutex> lock(mu);
+    Slot& s = table[slot];
+    if (s.used && s.key == key) { *m = s.map; return true; }
+    cuuint64_t dims[4], strides[3];
+    cuuint32_t box[4], estr[4] = {1, 1, 1, 1};
+    for (int i = 0; i < 4; ++i) { dims[i] = key.dims[i]; box[i] = key.box[i]; }
+    for (int i = 0; i < 3; ++i) strides[i] = key.strides[i];
+    CUresult r = fn(m, key.dtype == VIG_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)key.rank,
+                    const_cast<void*>(key.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    key.swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS;
+    if (r != CUDA_SUCCESS) return false;
+    s.used = true; s.key = key; s.map = *m;
+    return true;
 }
 
+// [B,H,L,d] view with element strides s = (b, h, l): box of 128 tokens x d channels of one (b, h).
+inline bool make_map(CUtensorMap* m, const void* base, const int64_t* s, int B, int H, int L, int d, int dtype, bool swizzle128) {
+    MapKey key{};
+    key.base = base; key.rank = 4; key.dtype = dtype; key.swizzle = swizzle128 ? 1 : 0;
+    key.dims[0] = (uint64_t)d; key.dims[1] = (uint64_t)L; key.dims[2] = (uint64_t)H; key.dims[3] = (uint64_t)B;
+    key.strides[0] = (uint64_t)s[2] * 2; key.strides[1] = (uint64_t)s[1] * 2; key.strides[2] = (uint64_t)s[0] * 2;
+    key.box[0] = (uint32_t)d; key.box[1] = CHUNK; key.box[2] = 1; key.box[3] = 1;
+    return encode_cached(m, key);
+}
+
+// Row-major [rows, cols] matrix with leading dimension ld (elements): boxes of box_rows x 64 columns, 128-byte swizzle.
 inline bool make_map_2d(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, int dtype) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return fn(m, dtype == VIG_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base),
-              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    MapKey key{};
+    key.base = base; key.rank = 2; key.dtype = dtype; key.swizzle = 1;
+    key.dims[0] = (uint64_t)cols; key.dims[1] = (uint64_t)rows;
+    key.strides[0] = (uint64_t)ld * 2;
+    key.box[0] = 64; key.box[1] = (uint32_t)box_rows;
+    return encode_cached(m, key);
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of on every launch.
+inline cudaError_t ensure_smem_attr(const void* kern, int bytes) {
+    struct Entry { const void* kern; int dev; int bytes; };
+    static std::mutex mu;
+    static Entry entries[256];
+    static int count = 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    Entry* hit = nullptr;
+    for (int i = 0; i < count; ++i)
+        if (entries[i].kern == kern && entries[i].dev == dev) { hit = &entries[i]; break; }
+    if (hit && hit->bytes >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    if (hit) hit->bytes = bytes;
+    else if (count < 256) entries[count++] = Entry{kern, dev, bytes};
+    return cudaSuccess;
 }
 
 inline bool tma_ok(const void* base, const int64_t* s, int B, int H) {

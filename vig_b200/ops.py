@@ -14,7 +14,103 @@ import torch
 from . import _lib
 
 _NAN = float("nan")
+# (dk, dv) pairs the backward kernels are compiled for (vig_bigla_bwd)
+BWD_HEAD_DIMS = {(16, 32), (32, 32), (32, 64), (64, 64), (64, 128)}
 _ws_cache = {}
+_status_words = {}
+
+
+class StatusWord:
+    """The device-side error word of one GPU.  Every scan and fused-GEMM launch of this module ORs its error bits into
+    it (bit 0: a bounded wait inside a kernel ran out, bit 1: a chunk's cumulative log-gate left the range the
+    tensor-core factorisation covers, so that chunk's numbers are wrong).  ``check()`` reads it with a synchronising
+    copy; ``snapshot()`` / ``poll()`` read it without stalling the stream (an asynchronous copy to pinned memory that
+    the next ``poll()`` looks at once it has landed)."""
+    BITS = {1: "a bounded wait inside a kernel ran out", 2: "a cumulative log-gate left the tensor-core range (use impl=IMPL_SIMT)"}
+
+    def __init__(self, device):
+        self.tensor = torch.zeros(1, dtype=torch.int32, device=device)
+        self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._event = None
+
+    def _raise(self, value):
+        self.tensor.zero_()
+        what = "; ".join(msg for bit, msg in self.BITS.items() if value & bit) or "unknown bits"
+        raise RuntimeError(f"vig_b200 kernels reported status {value}: {what}")
+
+    def check(self):
+        """Blocking read; raises (and clears the word) when a kernel has reported an error."""
+        self._event = None
+        value = int(self.tensor.item())
+        if value:
+            self._raise(value)
+
+    def snapshot(self):
+        """Queue an asynchronous read on the current stream (skipped while the stream is being captured)."""
+        if torch.cuda.is_current_stream_capturing():
+            return
+        self.poll()
+        if self._event is None:
+            self._host.copy_(self.tensor, non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+    def poll(self):
+        """Look at the last snapshot if its copy has finished; raises like ``check``."""
+        if self._event is not None and self._event.query():
+            self._event = None
+            value = int(self._host[0])
+            if value:
+                self._raise(value)
+
+
+def status_word(device=None):
+    """The ``StatusWord`` of ``device`` (default: the current CUDA device), created on first use."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    sw = _status_words.get(device)
+    if sw is None:
+        sw = _status_words[device] = StatusWord(device)
+    return sw
+
+
+def check_status(device=None):
+    """Raise if any kernel launched through this module on ``device`` has reported an error since the last check."""
+    status_word(device).check()
+
+
+def _status_ptr(status, device):
+    return _lib.ptr(status_word(device).tensor if status is None else status)
+
+
+def _same_device(*tensors):
+    """All given tensors (``None`` entries skipped) must be CUDA tensors on one device; returns it."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("vig_b200 kernels need CUDA tensors; there is no CPU path")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"tensors live on different devices ({dev} and {t.device})")
+    return dev
+
+
+def _check_scan_shapes(q, k, v, g_fwd, g_bwd, out=None):
+    """Shapes and dtypes the scan kernels index with: q and the gates like k, out like v."""
+    if k.dim() != 4 or v.dim() != 4 or v.shape[:3] != k.shape[:3]:
+        raise ValueError(f"k and v must be [B,H,L,dk] / [B,H,L,dv]; got {tuple(k.shape)} and {tuple(v.shape)}")
+    for name, t in (("q", q), ("g_fwd", g_fwd), ("g_bwd", g_bwd)):
+        if t is not None and t.shape != k.shape:
+            raise ValueError(f"{name} must have k's shape {tuple(k.shape)}; got {tuple(t.shape)}")
+    for name, t in (("q", q), ("v", v), ("g_fwd", g_fwd), ("g_bwd", g_bwd), ("out", out)):
+        if t is not None and t.dtype != k.dtype:
+            raise TypeError(f"{name} has dtype {t.dtype}, k has {k.dtype}: q, k, v, the gates and out must share one dtype")
+    if out is not None and out.shape != v.shape:
+        raise ValueError(f"out must have v's shape {tuple(v.shape)}; got {tuple(out.shape)}")
 
 
 def _workspace(nbytes, device):
@@ -35,25 +131,27 @@ def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_log
            dir_mask=3, impl=_lib.IMPL_AUTO, want_output=True, status=None):
     """o_t = out_scale * scale * q_t (S^f_t + S^b_t) with separate forward / backward log-gates.
 
-    ``status``: optional int32 CUDA tensor of one element; kernels OR error bits into it (bit 0: a bounded wait
-    ran out, bit 1: a chunk's cumulative gate left the range of the tensor-core factorisation).
+    ``status``: int32 CUDA tensor of one element that the kernels OR error bits into (bit 0: a bounded wait ran
+    out, bit 1: a chunk's cumulative gate left the range of the tensor-core factorisation); default: the device's
+    ``status_word()``, which ``check_status()`` reads.
     Returns ``o`` or ``(o, extras)`` where ``extras`` holds ``final_fwd/final_bwd`` ([B,H,dk,dv] fp32) and
     ``logdecay_fwd/logdecay_bwd`` ([B,H,dk] fp32) when requested.
     """
-    _lib.require_cuda(q, k, v, g_fwd, g_bwd)
+    dev = _same_device(q, k, v, g_fwd, g_bwd, out, init_state_fwd, init_state_bwd, status)
+    _check_scan_shapes(q if want_output else None, k, v, g_fwd, g_bwd, out)
+    if want_output and q is None:
+        raise ValueError("q is required unless want_output=False")
+    B, H, L, dk = k.shape
+    dv = v.shape[-1]
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g_fwd, g_bwd)):
         if (init_state_fwd is not None or init_state_bwd is not None or output_final_state or output_logdecay
                 or out is not None or not want_output):
             raise NotImplementedError("the differentiable form takes no states and allocates its own output")
+        if (dk, dv) not in BWD_HEAD_DIMS:
+            raise NotImplementedError(f"the backward kernels cover (dk, dv) in {sorted(BWD_HEAD_DIMS)}; got ({dk}, {dv})")
         return _BiGLAFunction.apply(q, k, v, g_fwd, g_bwd, float(scale if scale is not None else -1), float(out_scale),
                                     float(gate_logit_normalizer), clamp_min, dir_mask, impl)
-    B, H, L, dk = k.shape
-    dv = v.shape[-1]
     code = _lib.dtype_code(k)
-    for t in (q, v, g_fwd, g_bwd):
-        if t is not None and t.dtype != k.dtype:
-            raise TypeError("q, k, v and the gates must share one dtype")
-    dev = k.device
     if want_output:
         if out is None:
             out = torch.empty(B, H, L, dv, dtype=v.dtype, device=dev)
@@ -75,20 +173,21 @@ def bi_gla(q, k, v, g_fwd, g_bwd, scale=-1, out_scale=1.0, *, out=None, gate_log
         if s is not None and (s.dtype != torch.float32 or not s.is_contiguous() or s.shape != (B, H, dk, dv)):
             raise ValueError("initial states must be contiguous fp32 [B,H,dk,dv]")
     L_ = _lib.lib()
-    nbytes = L_.vig_bigla_workspace_bytes(B, H, L, dk, dv, code, impl)
-    ws = _workspace(nbytes, dev)
-    st = L_.vig_bigla_fwd(
-        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(out),
-        B, H, L, dk, dv, code,
-        _lib.strides3(q) if q is not None else None, _lib.strides3(k), _lib.strides3(v),
-        _lib.strides3(g_fwd) if g_fwd is not None else None, _lib.strides3(g_bwd) if g_bwd is not None else None,
-        _lib.strides3(out) if out is not None else None,
-        float(scale if scale is not None else -1), float(out_scale), float(gate_logit_normalizer),
-        _NAN if clamp_min is None else float(clamp_min),
-        _lib.ptr(init_state_fwd), _lib.ptr(init_state_bwd),
-        _lib.ptr(extras.get("final_fwd")), _lib.ptr(extras.get("final_bwd")),
-        _lib.ptr(extras.get("logdecay_fwd")), _lib.ptr(extras.get("logdecay_bwd")),
-        dir_mask, impl, _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.ptr(status), _lib.stream_ptr())
+    with torch.cuda.device(dev):
+        nbytes = L_.vig_bigla_workspace_bytes(B, H, L, dk, dv, code, impl)
+        ws = _workspace(nbytes, dev)
+        st = L_.vig_bigla_fwd(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(out),
+            B, H, L, dk, dv, code,
+            _lib.strides3(q) if q is not None else None, _lib.strides3(k), _lib.strides3(v),
+            _lib.strides3(g_fwd) if g_fwd is not None else None, _lib.strides3(g_bwd) if g_bwd is not None else None,
+            _lib.strides3(out) if out is not None else None,
+            float(scale if scale is not None else -1), float(out_scale), float(gate_logit_normalizer),
+            _NAN if clamp_min is None else float(clamp_min),
+            _lib.ptr(init_state_fwd), _lib.ptr(init_state_bwd),
+            _lib.ptr(extras.get("final_fwd")), _lib.ptr(extras.get("final_bwd")),
+            _lib.ptr(extras.get("logdecay_fwd")), _lib.ptr(extras.get("logdecay_bwd")),
+            dir_mask, impl, _lib.ptr(ws), ws.numel() if ws is not None else 0, _status_ptr(status, dev), _lib.stream_ptr())
     _lib.check(st, "vig_bigla_fwd")
     if extras:
         return out, extras
@@ -99,22 +198,25 @@ def bi_gla_backward(q, k, v, g_fwd, g_bwd, d_out, scale=-1, out_scale=1.0, dir_m
     """Gradients of ``bi_gla`` with log-space gates: ``(dq, dk, dv, dg_fwd, dg_bwd)`` (``None`` for a direction that
     is masked out).  The kernels deliver ``e = dq*q - dk*k`` per direction; the gate gradients are its cumulative
     sums over the tokens (``fla/ops/gla/chunk_fuse.py:506-516`` does the same in PyTorch)."""
-    _lib.require_cuda(q, k, v, d_out)
+    dev = _same_device(q, k, v, g_fwd, g_bwd, d_out)
+    _check_scan_shapes(q, k, v, g_fwd, g_bwd, d_out)
     B, H, L, dk = k.shape
     dv = v.shape[-1]
-    dev = k.device
+    if (dk, dv) not in BWD_HEAD_DIMS:
+        raise NotImplementedError(f"the backward kernels cover (dk, dv) in {sorted(BWD_HEAD_DIMS)}; got ({dk}, {dv})")
     dq, dk_, dv_ = (torch.empty(B, H, L, d, dtype=k.dtype, device=dev) for d in (dk, dk, dv))
     e_f = torch.empty(B, H, L, dk, dtype=torch.float32, device=dev) if dir_mask & 1 else None
     e_b = torch.empty(B, H, L, dk, dtype=torch.float32, device=dev) if dir_mask & 2 else None
     L_ = _lib.lib()
-    nbytes = L_.vig_bigla_bwd_workspace_bytes(B, H, L, dk, dv)
-    ws = _workspace(nbytes, dev)
     s3 = lambda t: None if t is None else _lib.strides3(t)
-    st = L_.vig_bigla_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(d_out),
-                          _lib.ptr(dq), _lib.ptr(dk_), _lib.ptr(dv_), _lib.ptr(e_f), _lib.ptr(e_b),
-                          B, H, L, dk, dv, _lib.dtype_code(k), s3(q), s3(k), s3(v), s3(g_fwd), s3(g_bwd), s3(d_out),
-                          float(scale if scale is not None else -1), float(out_scale), dir_mask,
-                          _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream_ptr())
+    with torch.cuda.device(dev):
+        nbytes = L_.vig_bigla_bwd_workspace_bytes(B, H, L, dk, dv)
+        ws = _workspace(nbytes, dev)
+        st = L_.vig_bigla_bwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(d_out),
+                              _lib.ptr(dq), _lib.ptr(dk_), _lib.ptr(dv_), _lib.ptr(e_f), _lib.ptr(e_b),
+                              B, H, L, dk, dv, _lib.dtype_code(k), s3(q), s3(k), s3(v), s3(g_fwd), s3(g_bwd), s3(d_out),
+                              float(scale if scale is not None else -1), float(out_scale), dir_mask,
+                              _lib.ptr(ws), ws.numel() if ws is not None else 0, _lib.stream_ptr())
     _lib.check(st, "vig_bigla_bwd")
     dg_f = e_f.flip(2).cumsum(2).flip(2) if e_f is not None else None
     dg_b = e_b.cumsum(2) if e_b is not None else None
@@ -131,47 +233,55 @@ class _BiGLAFunction(torch.autograd.Function):
             if x is None:
                 return None, None
             g = torch.nn.functional.logsigmoid(x.float()) / gate_norm if gate_norm > 0 else x.float()
+            # gradient passes where the unclamped fp32 gate is at or above the bound (torch.clamp_min's rule)
+            keep = None
             if clamp_min is not None:
+                keep = g >= clamp_min
                 g = torch.clamp_min(g, clamp_min)
-            return g.to(x.dtype), g
-        gf, gf32 = to_log(g_fwd)
-        gb, gb32 = to_log(g_bwd)
+            return g.to(x.dtype), keep
+        gf, keep_f = to_log(g_fwd)
+        gb, keep_b = to_log(g_bwd)
         with torch.no_grad():
             o = bi_gla(q, k, v, gf, gb, scale=scale, out_scale=out_scale, dir_mask=dir_mask, impl=impl)
-        ctx.save_for_backward(q, k, v, g_fwd, g_bwd, gf, gb)
+        ctx.save_for_backward(q, k, v, g_fwd, g_bwd, gf, gb, keep_f, keep_b)
         ctx.cfg = (scale, out_scale, gate_norm, clamp_min, dir_mask)
         return o
 
     @staticmethod
     def backward(ctx, d_out):
-        q, k, v, x_f, x_b, gf, gb = ctx.saved_tensors
+        q, k, v, x_f, x_b, gf, gb, keep_f, keep_b = ctx.saved_tensors
         scale, out_scale, gate_norm, clamp_min, dir_mask = ctx.cfg
         dq, dk, dv, dg_f, dg_b = bi_gla_backward(q, k, v, gf, gb, d_out.contiguous(), scale, out_scale, dir_mask)
 
-        def through_gate(dg, x, g):
+        def through_gate(dg, x, keep):
             if dg is None or x is None:
                 return None
-            if clamp_min is not None:
-                dg = dg * (g.float() > clamp_min)
+            if keep is not None:
+                dg = dg * keep
             if gate_norm > 0:                                       # d logsigmoid(x) / dx = sigmoid(-x)
                 dg = dg * torch.sigmoid(-x.float()) / gate_norm
             return dg.to(x.dtype)
-        return dq, dk, dv, through_gate(dg_f, x_f, gf), through_gate(dg_b, x_b, gb), None, None, None, None, None, None
+        return dq, dk, dv, through_gate(dg_f, x_f, keep_f), through_gate(dg_b, x_b, keep_b), None, None, None, None, None, None
 
 
 def bi_gla_noalloc(q, k, v, g_fwd, g_bwd, out, scale=-1, out_scale=1.0, gate_logit_normalizer=0.0, clamp_min=None,
-                   impl=_lib.IMPL_AUTO):
+                   impl=_lib.IMPL_AUTO, status=None):
     """``bi_gla`` through the entry point that allocates nothing: the caller supplies ``out`` and the scan's
     scratch is a fixed array inside the library (see ``vig_bigla_fwd_noalloc`` in the header for who needs
-    this and for its size limit).  Calls on one device must not overlap on the GPU."""
-    _lib.require_cuda(q, k, v, g_fwd, g_bwd, out)
+    this and for its size limit).  Calls on one device must not overlap on the GPU.  ``status``: as in ``bi_gla``;
+    pass a tensor of your own if even the status word's one-time allocation is unwelcome."""
+    dev = _same_device(q, k, v, g_fwd, g_bwd, out, status)
+    if q is None or g_fwd is None or g_bwd is None or out is None:
+        raise ValueError("q, both gate tensors and out are required")
+    _check_scan_shapes(q, k, v, g_fwd, g_bwd, out)
     B, H, L, dk = k.shape
     dv = v.shape[-1]
-    st = _lib.lib().vig_bigla_fwd_noalloc(
-        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(out), B, H, L, dk, dv,
-        _lib.dtype_code(k), _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(g_fwd), _lib.strides3(g_bwd),
-        _lib.strides3(out), float(scale if scale is not None else -1), float(out_scale), float(gate_logit_normalizer),
-        _NAN if clamp_min is None else float(clamp_min), impl, None, _lib.stream_ptr())
+    with torch.cuda.device(dev):
+        st = _lib.lib().vig_bigla_fwd_noalloc(
+            _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(g_fwd), _lib.ptr(g_bwd), _lib.ptr(out), B, H, L, dk, dv,
+            _lib.dtype_code(k), _lib.strides3(q), _lib.strides3(k), _lib.strides3(v), _lib.strides3(g_fwd), _lib.strides3(g_bwd),
+            _lib.strides3(out), float(scale if scale is not None else -1), float(out_scale), float(gate_logit_normalizer),
+            _NAN if clamp_min is None else float(clamp_min), impl, _status_ptr(status, dev), _lib.stream_ptr())
     _lib.check(st, "vig_bigla_fwd_noalloc")
     return out
 
@@ -317,8 +427,8 @@ def linear_add_rmsnorm(x, w, residual, norm_weight, eps=1e-6):
     out_r = torch.empty(M, N, dtype=x.dtype, device=x.device)
     out_h = torch.empty(M, N, dtype=x.dtype, device=x.device)
     st = _lib.lib().vig_linear_add_rmsnorm_fwd(_lib.ptr(x2), x2.stride(0), _lib.ptr(w.contiguous()), _lib.ptr(res), _lib.ptr(norm_weight),
-                                               _lib.ptr(out_r), _lib.ptr(out_h), M, K, N, float(eps), _lib.dtype_code(x), None,
-                                               _lib.stream_ptr())
+                                               _lib.ptr(out_r), _lib.ptr(out_h), M, K, N, float(eps), _lib.dtype_code(x),
+                                               _status_ptr(None, x.device), _lib.stream_ptr())
     _lib.check(st, "vig_linear_add_rmsnorm_fwd")
     return out_h.view(*lead, N), out_r.view(*lead, N)
 
@@ -370,7 +480,7 @@ def linear_swiglu(x, weight):
         x2 = x2.contiguous()
     out = torch.empty(*x.shape[:-1], I, dtype=x.dtype, device=x.device)
     st = _lib.lib().vig_linear_swiglu_fwd(_lib.ptr(x2), x2.stride(0), _lib.ptr(weight), _lib.ptr(out), I, x2.shape[0], K, I,
-                                          _lib.dtype_code(x), None, _lib.stream_ptr())
+                                          _lib.dtype_code(x), _status_ptr(None, x.device), _lib.stream_ptr())
     _lib.check(st, "vig_linear_swiglu_fwd")
     return out
 

@@ -153,7 +153,15 @@ class ViG(nn.Module):
         return x.mean(dim=1)
 
     def forward(self, x, **kwargs):
-        return self.head(self.forward_features(x))
+        """Logits.  The kernels' error word is looked at without stalling the stream: this call raises if a kernel of an
+        EARLIER forward reported an error (its status copy has landed by now), and queues the copy for its own;
+        ``vig_b200.check_status()`` is the blocking form."""
+        from . import ops
+        status = ops.status_word(x.device)
+        status.poll()
+        logits = self.head(self.forward_features(x))
+        status.snapshot()
+        return logits
 
 
 _PRESETS = {
