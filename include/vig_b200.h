@@ -143,8 +143,10 @@ VIG_API int vig_bigla_bwd(const void* q, const void* k, const void* v, const voi
  * on the SIMT path (fp32, other head sizes, impl = VIG_IMPL_SIMT) when L > 64 and nothing up to 64 tokens.
  * At dk = dv = 64 that is B*H*ceil(L/256) <= 504 (tensor core) or B*H*ceil(L/64) <= 504 (SIMT).
  * The call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
- * The first call on each device looks up the array's device address (with that device current); make that
- * first call outside any stream capture.  All calls on a device share the one array: calls that may overlap
+ * The first call on each device looks up the array's device address (with that device current); with CUDA's
+ * lazy module loading that is also the moment the runtime places this library's device image -- the array
+ * included -- in device memory, so cudaMemGetInfo drops by the array's size across that one call.  Make that
+ * first call at start-up (any tiny problem will do), outside any stream capture; later calls change nothing.  All calls on a device share the one array: calls that may overlap
  * on the GPU (different streams without ordering between them) race on it -- keep them on one stream or
  * order them with events.  Nothing in the array has to start at zero; each call overwrites what it uses.
  */

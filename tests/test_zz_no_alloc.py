@@ -16,12 +16,23 @@ def _inputs(B, H, L, dk, dtype, seed):
     return [t.to("cuda", dtype) for t in oracle.make_bigla_inputs(B, H, L, dk, 64, seed=seed)]
 
 
+def _setup_call(status):
+    """The entry point's first call on a device looks up the scratch array's address; with CUDA's lazy module loading
+    that is also when the runtime places the library's device image, the 16 MiB array included, in device memory.
+    Callers make this call at start-up, before their memory is frozen; the tests make it before they measure."""
+    from vig_b200 import ops
+    q, k, v, gf, gb = _inputs(1, 1, 8, 64, torch.bfloat16, seed=0)
+    ops.bi_gla_noalloc(q, k, v, gf, gb, torch.empty_like(v), status=status)
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_noalloc_matches_workspace_entry_point_twice_in_a_row(dtype):
     import vig_b200
     from vig_b200 import ops
     # both shapes span several segments, so the scratch array is really used; the second call is larger
     status = ops.status_word().tensor                            # the error word exists before the calls under test
+    _setup_call(status)
     for call, (B, H, L, dk) in enumerate([(2, 3, 1300, 64), (3, 2, 2100, 32)]):
         q, k, v, gf, gb = _inputs(B, H, L, dk, dtype, seed=40 + call)
         expected = vig_b200.bi_gla(q, k, v, gf, gb, out_scale=0.5)
