@@ -193,9 +193,10 @@ def test_wavefront_form_matches_oracle(shape, dir_mask, init, dtype):
     o1, ex1 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_WAVE, status=status, **kw)
     o0, ex0 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_SPLIT, **kw)
     assert int(status.item()) == 0
-    assert rel_err(o1.float(), o0.float()) < 1e-2
-    for name in ex0:                                   # same operand rounding, different summation order of the gates
-        assert rel_err(ex1[name], ex0[name]) < 1e-3, name
+    assert rel_err(o1.float(), o0.float()) < 1.5e-2    # two bf16 results: a couple of output ulps apart at most
+    for name in ex0:                                   # operands rounded differently (packed scaling), gates summed in another order
+        tol = 1e-5 if name.startswith("logdecay") else 1e-2
+        assert rel_err(ex1[name], ex0[name]) < tol, name
     if B * L <= 4096:                                  # the naive oracle is a token loop
         f32 = [t.float().cpu() for t in dev]
         if dir_mask == 3:
