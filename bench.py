@@ -48,6 +48,7 @@ def parse():
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's)")
     ap.add_argument("--graph", type=int, default=0, help="1: replay the forward as a CUDA graph in the timed region")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-seq-split", action="store_true", help="skip the sequence-split measurement that multi-GPU runs append")
     return ap.parse_args()
 
 
@@ -192,7 +193,9 @@ def main():
     counts = {"launches": 0}
     scan_events = []
     timing = {"on": False}
-    orig = {n: getattr(vops, n) for n in ("bi_gla", "dwconv3x3", "gate_inject", "add_rmsnorm", "swiglu")}
+    orig = {n: getattr(vops, n) for n in ("bi_gla", "dwconv3x3", "gate_inject", "add_rmsnorm", "swiglu", "linear_swiglu",
+                                          "linear_add_rmsnorm", "layernorm_act", "stem_unfold", "linear_bias")
+            if hasattr(vops, n)}
     L = (size // 16) ** 2
     nseg = (L + 255) // 256                       # 256-token segments of the tensor-core scan
     scan_launches = 1 if nseg == 1 or 8 <= nseg <= 32 else 3   # one persistent launch, or states + scan + outputs
@@ -237,6 +240,7 @@ def main():
 
     for _ in range(max(args.warmup, 3)):
         step()
+    vops.check_status()          # no kernel reported a run-out wait or an out-of-range gate during warm-up
     graph = None
     if args.graph:
         graph = torch.cuda.CUDAGraph()
@@ -258,6 +262,7 @@ def main():
     e1.record()
     sync_all()
     timing["on"] = False
+    vops.check_status()          # ... nor inside the timed region (read after it, outside the timing)
     ms = e0.elapsed_time(e1)
     launches = counts["launches"] if graph is None else None
     clocks = sampler.stop()
@@ -298,6 +303,7 @@ def main():
         host_logits.copy_(out, non_blocking=True)
     f1.record()
     sync_all()
+    vops.check_status()
     ms_e2e = f0.elapsed_time(f1)
 
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
@@ -331,6 +337,11 @@ def main():
                 "tensor_tflops_accounting": alg_flops / (scan_ms * 1e-3) / 1e12,
                 "share_of_step": scan_ms * shape.depth / (ms / args.steps)}
 
+    seq_split_line = None
+    if world > 1 and args.workload == "vig_t_1024" and not args.no_seq_split:
+        del model, images, dbuf
+        torch.cuda.empty_cache()
+        seq_split_line = run_seq_split(vig_b200, vops, oracle, dev, rank, world)
     if rank == 0:
         total_images = batch * (1 if args.workload in SEQ_SPLIT else world) * args.steps
         line = {"metric": "images_per_sec", "value": total_images / (ms * 1e-3), "unit": "images/s", "n_gpus": world,
@@ -340,6 +351,8 @@ def main():
                 "e2e": {"value": total_images / (ms_e2e * 1e-3), "unit": "images/s",
                         "h2d_bytes_per_step": host_images.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
                 "roofline": roofline, "graph": bool(args.graph)}
+        if seq_split_line is not None:
+            line["seq_split"] = seq_split_line
         if world == 1 and not args.no_cpu_baseline:
             ips, dt = cpu_model_throughput(preset, size)
             line["cpu_baseline"] = {"value": ips, "unit": "images/s", "cores": os.cpu_count() or 1, "kind": "port",
@@ -348,6 +361,52 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_seq_split(vig_b200, vops, oracle, dev, rank, world, steps=5, warmup=3):
+    """The second multi-GPU mode, measured in the same run: ViG-B at 2048x2048 (L = 16384), batch 8, the token sequence
+    of every image split across the ranks by rows of the patch grid (per block: conv halo rows from the two neighbours,
+    one all-gather of the per-head boundary states; one all-reduce for the pool).  Every rank holds the same images;
+    times are CUDA-event times, max over ranks; the unsplit forward of the same batch on one GPU is timed beside it and
+    the two results are compared."""
+    import torch.distributed as dist
+    from vig_b200 import seqsplit
+    preset, size, batch = WORKLOADS["vig_b_2048_seq"]
+    shape = oracle.PRESETS[preset]
+    model = vig_b200.ViG.from_shape(shape)
+    model.load_state_dict(oracle.make_state_dict(shape, seed=0))
+    model = model.to(dev, torch.bfloat16).eval()
+    images = oracle.make_images(batch, size, seed=0).to(dev, torch.bfloat16)
+
+    def timed(fn):
+        for _ in range(warmup):
+            out = fn()
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            out = fn()
+        e1.record()
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0]) / steps, out
+
+    with torch.no_grad():
+        ms_split, split = timed(lambda: seqsplit.vig_forward_sequence_parallel(model, images))
+        vops.check_status()
+        ms_one, whole = timed(lambda: model(images))
+        vops.check_status()
+        phases = seqsplit.phase_times(model, images) if hasattr(seqsplit, "phase_times") else None
+    err = float((split.float() - whole.float()).abs().max() / whole.float().abs().max())
+    line = {"workload": f"vig_b_2048_seq: ViG {preset} forward, {size}x{size} images (L={(size // 16) ** 2}), batch {batch}, "
+                        "token sequence split across the GPUs", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "images_per_s": batch / (ms_split * 1e-3), "ms_per_step": ms_split,
+            "single_gpu_images_per_s": batch / (ms_one * 1e-3), "single_gpu_ms_per_step": ms_one,
+            "strong_scaling_efficiency": ms_one / (ms_split * world), "split_vs_unsplit_rel_err": err}
+    if phases is not None:
+        line["phases_ms_per_step"] = phases
+    return line
 
 
 def time_scan_alone(vig_b200, batch, H, L, dk, dv, dev, reps=10):

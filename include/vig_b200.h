@@ -170,6 +170,16 @@ VIG_API int vig_dwconv3x3_fwd(const void* x, const void* weight_tap_major, const
                       int B, int h, int w, int C, int act_silu, int dtype, void* stream);
 
 /*
+ * The same convolution on a horizontal band of a taller image (rows [r0, r0 + h) of the token grid): `top` and `bottom`
+ * are the image rows just above and below the band, [B, w, C] each, or NULL where the band touches the image border
+ * (zero padding there, as in vig_dwconv3x3_fwd).  It is what a sequence split across GPUs by rows of the patch grid
+ * needs from `in_proj` (classification/models/vig.py:291-294, 428-430): the two halo rows arrive from the neighbouring
+ * ranks and are read in place, no padded copy of the band is made.  bf16 / fp16, C % 4 == 0.
+ */
+VIG_API int vig_dwconv3x3_halo_fwd(const void* x, const void* top, const void* bottom, const void* weight_tap_major,
+                           const void* bias, void* y, int B, int h, int w, int C, int act_silu, int dtype, void* stream);
+
+/*
  * 2-D gating locality injection: y = RMSNorm_g(o) * sigmoid(gate_logits) + RMSNorm_l(local) * (1 - sigmoid),
  * head-wise norms over dv, optional swish on y.  Replaces l_norm, g_norm, sigmoid, the blend, out_act and
  * the `b h l d -> b l h d` transposes of classification/models/vig.py:444-457 (norm:

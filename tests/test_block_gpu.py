@@ -223,3 +223,20 @@ def test_block_and_model_match_reference_vectors(golden_block, tag, preset, size
     print(f"{tag} {dtype}: attn {errs[0]:.2e} block {errs[1]:.2e} logits {errs[2]:.2e} (bar {tol:.0e})")
     vig_b200.check_status()
     assert errs[0] < tol and errs[1] < tol and errs[2] < tol, errs
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dwconv3x3_band_with_halo_rows(dtype):
+    """A band of image rows with the rows above and below handed over separately (what a rank of the sequence split
+    holds) gives exactly the rows the whole-image call gives."""
+    import vig_b200
+    B, h, w, C = 2, 12, 10, 192
+    x = torch.randn(B, h * w, C, generator=torch.Generator().manual_seed(31)).to("cuda", dtype)
+    taps = (0.3 * torch.randn(9, C, generator=torch.Generator().manual_seed(32))).to("cuda", dtype)
+    whole = vig_b200.dwconv3x3(x, taps, None, (h, w), True)
+    for r0, r1 in ((0, 5), (5, 9), (9, 12)):
+        band = x[:, r0 * w:r1 * w].contiguous()
+        top = x[:, (r0 - 1) * w:r0 * w].contiguous() if r0 > 0 else None
+        bottom = x[:, r1 * w:(r1 + 1) * w].contiguous() if r1 < h else None
+        y = vig_b200.dwconv3x3(band, taps, None, (r1 - r0, w), True, top=top, bottom=bottom)
+        assert torch.equal(y, whole[:, r0 * w:r1 * w])

@@ -88,3 +88,28 @@ def test_sequence_split_on_gpu_matches_unsplit(dtype, P, L):
     if L <= 4096:
         ref = oracle.naive_bi_gla(*[t.float().cpu() for t in ins], out_scale=0.5)
         assert rel_err(got.float(), ref) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def _halo_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        w, C = 5, 8
+        x = torch.arange(2 * 3 * w * C, dtype=torch.float32).reshape(2, 3 * w, C) + 1000 * rank     # my 3 rows of the grid
+        top, bottom = seqsplit.exchange_halo_rows(x, w, None, rank, world)
+        ret[rank] = (top, bottom, x[:, :w].clone(), x[:, -w:].clone())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_halo_rows_come_from_the_two_neighbours_only():
+    world = 3
+    ret = mp.Manager().dict()
+    mp.spawn(_halo_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        top, bottom, first, last = ret[r]
+        assert (top is None) == (r == 0) and (bottom is None) == (r == world - 1)      # image border: zero padding
+        if r > 0:
+            assert torch.equal(top, ret[r - 1][3])            # the last row of the rank above
+        if r < world - 1:
+            assert torch.equal(bottom, ret[r + 1][2])         # the first row of the rank below

@@ -13,8 +13,8 @@
 //   MMA thread        all tcgen05.mma issue
 //   16 prep warps     gate transform and cumulative log-gates (in registers), then q * 2^(G_i - G_ref) and
 //                     k * 2^(G_ref - G_j) IN PLACE over the raw tiles
-//   prefix warp       turns the 16 prep warps' group sums into each group's offset (exclusive prefix minus G_ref)
-//                     while the prep warps fetch their raw operand rows
+//                     (group sums exchanged through shared memory; every warp forms its own offset from them: code that
+//                     all sixteen run stays in the instruction cache, a seventeenth warp's would not)
 //   4 score warps     scores TMEM -> masked bf16 tiles; output accumulators TMEM -> 16-bit tile in shared memory
 //   store thread      output tile -> global by TMA (store, or reduction onto the other direction's half); chunk flags
 //   4 state warps     S <- 2^G_last S + 2^(G_last - G_ref) K~^T V in registers; bf16 state operand; mailbox
@@ -38,9 +38,9 @@ using namespace tc;
 
 constexpr int WDK = 64, WDV = 64;
 constexpr int W_SEG_CHUNKS = 2, W_SEG = CHUNK * W_SEG_CHUNKS;
-// seven warpgroups: prep x4, score, state, control (MMA warp, load thread, prefix warp, store thread)
+// seven warpgroups: prep x4, score, state, control (MMA warp, load thread, store thread)
 constexpr int W_PREP_WARPS = 16, W_STATE_WARP0 = 20, W_CTRL_WARP0 = 24, W_THREADS = 28 * 32;
-constexpr int W_MMA_WARP = W_CTRL_WARP0, W_LOAD_WARP = W_CTRL_WARP0 + 1, W_PREFIX_WARP = W_CTRL_WARP0 + 2, W_STORE_WARP = W_CTRL_WARP0 + 3;
+constexpr int W_MMA_WARP = W_CTRL_WARP0, W_LOAD_WARP = W_CTRL_WARP0 + 1, W_STORE_WARP = W_CTRL_WARP0 + 2;
 constexpr int W_STAGES = 3;
 // Registers per thread.  The kernel is compiled and launched with W_REGS_BASE for all seven warpgroups (seven warps
 // per scheduler allow no more); the control warpgroup gives most of its share back and the score and state
@@ -66,7 +66,7 @@ constexpr uint32_t WT_P = 0, WT_U = 128, WT_O = 256, WT_COLS = 512;   // U and O
 
 // mbarrier indices
 enum { B_FULL = 0, B_SFREE = 3, B_PREPPED = 6, B_PFULL = 9, B_PREADY = 10, B_STREADY = 11, B_UFULL = 12, B_OFULL = 14, B_OFREE = 16,
-       B_PART = 18, B_PREFIX = 20, B_STFREE = 22, B_OSTAGED = 23, B_COUNT = 25 };
+       B_PART = 18, B_XFREE = 20, B_STFREE = 22, B_OSTAGED = 23, B_COUNT = 25 };
 static_assert(B_COUNT <= 32, "barrier slots");
 
 struct WaveMaps { CUtensorMap q, k, v, gf, gb, o; };
@@ -78,13 +78,22 @@ struct WaveParams {
     uint32_t* chunk_flag;  // [B*H][nseg*2]: score warps of the first direction that have stored the chunk (4 = done)
     float* mailbox;        // [B*H][2 dirs][2 slots][dk*dv + dk]
     int nseg;
+    float inv_per_step, inv_H;   // reciprocals for the ticket decode (a division costs twenty-odd instructions)
 };
 
-struct Item { int bh, seg, dir, nch, w, pad0, pad1, pad2; };
+// n / d and n % d for 0 <= n < 2^24 from a float reciprocal and two corrections.
+__device__ __forceinline__ void divmod(int n, int d, float inv_d, int& q, int& r) {
+    q = __float2int_rz(__int2float_rz(n) * inv_d);
+    r = n - q * d;
+    if (r >= d) { ++q; r -= d; }
+    if (r < 0) { --q; r += d; }
+}
+
+struct Item { int bh, seg, dir, nch, w, b, h, pad; };
 
 
 // Bounded wait on a global counter (one lane polls).
-__device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, volatile int* abort_flag, int32_t* status) {
+__device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, volatile int* abort_flag) {
 #pragma unroll 1
     for (uint32_t i = 0; i < (1u << 21); ++i) {
         if (ld_acquire_u32(ctr) >= need) return;
@@ -92,7 +101,6 @@ __device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, 
         __nanosleep(64);
     }
     *abort_flag = 1;
-    if (status) atomicOr(status, 1);
 }
 
 
@@ -137,8 +145,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     const Waiter waiter{abort_flag, p.status};
 
     if (tid == 0) {
-        for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_SFREE + i), 2); mbar_init(bar(B_PREPPED + i), W_PREP_WARPS); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_PART + i), W_PREP_WARPS); mbar_init(bar(B_PREFIX + i), 1); }
+        for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_SFREE + i), 1); mbar_init(bar(B_PREPPED + i), W_PREP_WARPS); }
+        for (int i = 0; i < 2; ++i) mbar_init(bar(B_PART + i), W_PREP_WARPS);
+        mbar_init(bar(B_XFREE), 1);
         mbar_init(bar(B_PFULL), 1); mbar_init(bar(B_PREADY), 4); mbar_init(bar(B_STREADY), 4); mbar_init(bar(B_STFREE), 1);
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_OFULL + i), 1); mbar_init(bar(B_OFREE + i), 4); mbar_init(bar(B_UFULL + i), 1); mbar_init(bar(B_OSTAGED + i), 4); }
         *abort_flag = 0;
@@ -171,54 +180,52 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         if (tid == W_LOAD_WARP * 32) {
             // ---- load thread: work tickets and TMA loads, up to W_STAGES iterations ahead of the tensor core ----
             auto decode = [&](int t, Item& it) {               // ticket -> work item (nch = 0: no more work)
+                it.nch = 0;
                 if (t < total) {
-                    it.w = t / per_step;
-                    const int r = t % per_step;
-                    it.bh = r / ndir;
-                    it.dir = dir_first + r % ndir;
+                    int r;
+                    divmod(t, per_step, wp.inv_per_step, it.w, r);
+                    it.bh = ndir == 2 ? r >> 1 : r;
+                    it.dir = dir_first + (ndir == 2 ? r & 1 : 0);
+                    divmod(it.bh, p.H, wp.inv_H, it.b, it.h);
                     it.seg = it.dir ? nseg - 1 - it.w : it.w;
                     it.nch = min(W_SEG_CHUNKS, (p.L - it.seg * W_SEG + CHUNK - 1) / CHUNK);
-                } else {
-                    it.nch = 0;
                 }
             };
             // A ticket is drawn two items before its loads are issued.  One item before, when its value has long arrived,
-            // its tiles are asked into L2, so the loads that fill the 3-stage ring later find them there (the ring alone
-            // does not cover DRAM latency).
-            auto prefetch = [&](int t) {
-                Item it; it.bh = it.seg = it.dir = it.w = 0;
-                decode(t, it);
-                for (int c = 0; c < it.nch; ++c) {
-                    const int t0 = it.seg * W_SEG + c * CHUNK, b = it.bh / p.H, h = it.bh % p.H;
-                    tma_prefetch_4d(&maps.k, 0, t0, h, b);
-                    tma_prefetch_4d(it.dir ? &maps.gb : &maps.gf, 0, t0, h, b);
-                    tma_prefetch_4d(&maps.q, 0, t0, h, b);
-                    tma_prefetch_4d(&maps.v, 0, t0, h, b);
-                }
-            };
+            // it is decoded and its tiles are asked into L2, so the loads that fill the 3-stage ring later find them there
+            // (the ring alone does not cover DRAM latency).
+            Item lcur, lnext;
+            lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = lcur.b = lcur.h = 0; lnext = lcur;
             int tk = (int)atomicAdd(wp.ticket, 1u);
-            int tk_next = (int)atomicAdd(wp.ticket, 1u);       // consumed one item later: its round trip costs no stall
-            Item lcur; lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = 0;
-            int l_items = 0, l_ci = 0;
+            int l_items = -1, l_ci = 0;                        // the first pass through the item block only fills lnext
             #pragma unroll 1
             for (uint32_t lm = 0;; ++lm, ++l_ci) {
-                if (l_ci == lcur.nch) {                        // next work item
-                    const int t = tk;
-                    tk = tk_next;
-                    tk_next = (int)atomicAdd(wp.ticket, 1u);
-                    decode(t, lcur);
-                    volatile Item* r = ring + (l_items & 7);
-                    r->bh = lcur.bh; r->seg = lcur.seg; r->dir = lcur.dir; r->nch = lcur.nch; r->w = lcur.w;
+                while (l_ci == lcur.nch) {                     // next work item (twice at the start)
+                    lcur = lnext;
+                    if (l_items >= 0) {
+                        volatile Item* r = ring + (l_items & 7);
+                        r->bh = lcur.bh; r->seg = lcur.seg; r->dir = lcur.dir; r->nch = lcur.nch; r->w = lcur.w; r->b = lcur.b; r->h = lcur.h;
+                    }
                     ++l_items;
                     l_ci = 0;
-                    prefetch(tk);                              // the item after this one
+                    decode(tk, lnext);                         // the item after this one
+                    tk = (int)atomicAdd(wp.ticket, 1u);        // and the ticket of the one after that: consumed an item later
+#pragma unroll 1
+                    for (int c = 0; c < lnext.nch; ++c) {
+                        const int t0 = lnext.seg * W_SEG + c * CHUNK;
+                        tma_prefetch_4d(&maps.k, 0, t0, lnext.h, lnext.b);
+                        tma_prefetch_4d(lnext.dir ? &maps.gb : &maps.gf, 0, t0, lnext.h, lnext.b);
+                        tma_prefetch_4d(&maps.q, 0, t0, lnext.h, lnext.b);
+                        tma_prefetch_4d(&maps.v, 0, t0, lnext.h, lnext.b);
+                    }
+                    if (l_items > 0) break;                    // a real item is in lcur (an empty one ends the stream below)
                 }
                 const uint32_t s = lm % 3;
-                if (lm >= 3) waiter.wait(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
+                if (lm >= 3) waiter.wait_lite(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
                 if (*abort_flag) break;
                 if (lcur.nch == 0) { mbar_arrive_plain(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
                 const int t0 = lcur.seg * W_SEG + chunk_of(lcur, l_ci) * CHUNK;
-                const int b = lcur.bh / p.H, h = lcur.bh % p.H;
+                const int b = lcur.b, h = lcur.h;
                 const uint32_t dst = sbase + s * W_STAGE_B, fb = bar(B_FULL + s);
                 mbar_expect_tx(fb, W_STAGE_B);
                 tma_load_4d(dst + WS_K, &maps.k, 0, t0, h, b, fb);
@@ -235,7 +242,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             #pragma unroll 1
             for (uint32_t m = 0;; ++m, ++m_ci) {
                 const uint32_t s = m % 3, st = sbase + s * W_STAGE_B;
-                waiter.wait(bar(B_PREPPED + s), (m / 3) & 1);  // also orders the read of the work item after its write
+                waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);  // also orders the read of the work item after its write
                 if (*abort_flag) break;
                 if (m_ci == mcur.nch) { read_item(m_items, mcur); ++m_items; m_ci = 0; }
                 if (mcur.nch == 0) { if (lane == 0) mbar_arrive_plain(bar(B_PFULL)); break; }      // end marker: wakes the score warps
@@ -255,8 +262,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     tc_commit(bar(B_UFULL + (m & 1u)));
                 }
                 // (b) product with the entering state
-                waiter.wait(bar(B_STREADY), m & 1);
-                if (m >= 2) waiter.wait(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
+                waiter.wait_lite(bar(B_STREADY), m & 1);
+                if (m >= 2) waiter.wait_lite(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
                 tc_fence_after();
                 if (lane == 0) {
                     if (!s_zero) {
@@ -266,7 +273,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     tc_commit(bar(B_STFREE));                  // the state operand may be overwritten
                 }
                 // (c) masked scores x v
-                waiter.wait(bar(B_PREADY), m & 1);
+                waiter.wait_lite(bar(B_PREADY), m & 1);
                 tc_fence_after();
                 if (lane == 0) {
 #pragma unroll 1
@@ -277,76 +284,33 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 }
                 __syncwarp();
             }
-        } else if (warp == W_PREFIX_WARP) {
-            // ---- prefix warp: group sums of iteration m -> group offsets, in place ----
-            // part[g][c] holds the summed log2-gates of token group g (8 tokens, one prep warp) for channel c.  In scan
-            // order the offset of a group is the sum of the groups before it minus G_ref, the cumulative gate at the
-            // chunk's middle token (the first 8 groups).  A lane owns 4 channels of 8 consecutive groups (scan order):
-            // 16-byte accesses, independent loads, one exchange with the lane that owns the other 8 groups.
-            Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
-            int items = 0, ci = 0;
-            const int gq = lane >> 4, c4l = lane & 15;
-            #pragma unroll 1
-            for (uint32_t m = 0;; ++m, ++ci) {
-                if (lane == 0) waiter.wait(bar(B_PART + (m & 1)), (m >> 1) & 1);
-                __syncwarp();
-                if (*abort_flag) break;
-                if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
-                if (cur.nch == 0) break;
-                float4* part = reinterpret_cast<float4*>(smem + WO_PART) + (m & 1) * (W_PREP_WARPS * 16) + c4l;
-                const int flip = cur.dir ? W_PREP_WARPS - 1 : 0;          // scan position go -> group go ^ flip
-                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);            // two passes over the 8 values: the control warpgroup has few registers
-#pragma unroll 4
-                for (int i = 0; i < 8; ++i) { const float4 t = part[((gq * 8 + i) ^ flip) * 16]; sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w; }
-                float4 other;
-                other.x = __shfl_xor_sync(0xffffffffu, sum.x, 16); other.y = __shfl_xor_sync(0xffffffffu, sum.y, 16);
-                other.z = __shfl_xor_sync(0xffffffffu, sum.z, 16); other.w = __shfl_xor_sync(0xffffffffu, sum.w, 16);
-                const float4 gref = gq ? other : sum;                     // the first 8 groups in scan order
-                // offsets: exclusive prefix minus G_ref; the second half starts at 0 (its prefix is exactly G_ref)
-                float4 run = gq ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(-gref.x, -gref.y, -gref.z, -gref.w);
-#pragma unroll 2
-                for (int i = 0; i < 8; ++i) {
-                    float4* slot = part + ((gq * 8 + i) ^ flip) * 16;
-                    const float4 t = *slot;
-                    *slot = run;
-                    run.x += t.x; run.y += t.y; run.z += t.z; run.w += t.w;
-                }
-                if (gq == 0) {                                            // [G_ref | G_last] for the state warps
-                    float4* ve = reinterpret_cast<float4*>(vec + (m & 3) * 128) + c4l;
-                    ve[0] = gref;
-                    ve[16] = make_float4(sum.x + other.x, sum.y + other.y, sum.z + other.z, sum.w + other.w);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive_plain(bar(B_PREFIX + (m & 1)));
-            }
         } else if (tid == W_STORE_WARP * 32) {
-            // ---- store thread: the output tile of iteration j, staged by the score warps over the dead q tile of its
-            // stage, goes out as one TMA store (first direction to reach the chunk) or one TMA reduction (second).
+            // ---- store thread: the output tile of iteration j, staged by the score warps, goes out as one TMA store (first direction to reach the chunk) or one TMA reduction (second).
             // The global-memory latencies of the hand-over between the directions (write complete -> flag; flag -> add)
             // are spent here, by a thread that has nothing else to do.
             Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
             int items = 0, ci = 0;
             #pragma unroll 1
             for (uint32_t j = 0;; ++j, ++ci) {
-                waiter.wait(bar(B_OSTAGED + (j & 1)), (j >> 1) & 1);
+                waiter.wait_lite(bar(B_OSTAGED + (j & 1)), (j >> 1) & 1);
                 if (*abort_flag) break;
-                if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
+                if (ci == cur.nch) { read_item(items, cur); cur.b = ring[items & 7].b; cur.h = ring[items & 7].h; ++items; ci = 0; }
                 if (cur.nch == 0) break;
                 const int c = chunk_of(cur, ci);
-                const int t0 = cur.seg * W_SEG + c * CHUNK, b = cur.bh / p.H, h = cur.bh % p.H;
+                const int t0 = cur.seg * W_SEG + c * CHUNK, b = cur.b, h = cur.h;
                 const int w_other = nseg - 1 - cur.w;
                 const bool first = ndir == 1 || cur.w < w_other || (cur.w == w_other && cur.dir == 0);
                 uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * nseg * W_SEG_CHUNKS + cur.seg * W_SEG_CHUNKS + c;
-                const uint32_t src = sbase + (j % 3) * W_STAGE_B + WS_Q;
+                const uint32_t src = sbase + WO_X;
                 if (first) {
                     tma_store_4d(&maps.o, 0, t0, h, b, src);     // rows past L are clipped by the tensor map
                 } else {
-                    global_wait(flag, 1u, abort_flag, p.status); // the other direction's half must be in place
+                    global_wait(flag, 1u, abort_flag); // the other direction's half must be in place
                     tma_reduce_add_4d(&maps.o, 0, t0, h, b, src);
                 }
                 bulk_commit();
                 bulk_store_wait_read();
-                mbar_arrive_plain(bar(B_SFREE + j % 3));        // the stage may be refilled (with the MMA warp's commit)
+                mbar_arrive_plain(bar(B_XFREE));                 // the tile may take the next iteration's scores
                 if (first && ndir == 2) {                      // publish my half of the chunk once it is written
                     bulk_store_wait_all();
                     __threadfence();
@@ -371,12 +335,12 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait(bar(B_FULL + s), (m / 3) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
-            if (cur.nch == 0) {                               // end marker: pass it on to the prefix warp, the MMA warp and the state warps
-                if (lane == 0) { mbar_arrive_plain(bar(B_PART + (m & 1))); mbar_arrive_plain(bar(B_PREPPED + s)); }
+            if (cur.nch == 0) {                               // end marker: pass it on to the MMA warp and the state warps
+                if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s));
                 break;
             }
             uint8_t* stg = smem + s * W_STAGE_B;
@@ -422,7 +386,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive_plain(bar(B_PART + (m & 1)));
             }
-            // ---- raw operand tiles into registers while the prefix warp turns the group sums into offsets ----
+            // ---- raw operand rows into registers while the other warps finish their group sums ----
             uint2 rk[4], rq[4];
             uint32_t offs[4];
 #pragma unroll
@@ -432,12 +396,39 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 rk[u] = *reinterpret_cast<const uint2*>(stg + WS_K + offs[u]);
                 rq[u] = *reinterpret_cast<const uint2*>(stg + WS_Q + offs[u]);
             }
-            if (lane == 0) waiter.wait(bar(B_PREFIX + (m & 1)), (m >> 1) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_PART + (m & 1)), (m >> 1) & 1);     // all sixteen group sums are in
             __syncwarp();
             if (*abort_flag) break;
+            // ---- my group's offset: (sum of the groups scanned before mine) - G_ref, G_ref = sum of the first 8 groups in
+            // scan order.  Half-warp gq reads groups 8 gq .. 8 gq + 7 (scan order) for its 4 channels; one exchange. ----
+            float4 off;
+            {
+                const float4* part = reinterpret_cast<const float4*>(smem + WO_PART) + (m & 1) * (W_PREP_WARPS * 16) + c4l;
+                const int flip = cur.dir ? W_PREP_WARPS - 1 : 0;          // scan position go <-> group go ^ flip
+                const int mygo = grp ^ flip;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f), bef = sum;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int go = half * 8 + i;
+                    const float4 t = part[(go ^ flip) * 16];
+                    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+                    const float k = go < mygo ? 1.f : 0.f;
+                    bef.x = fmaf(k, t.x, bef.x); bef.y = fmaf(k, t.y, bef.y); bef.z = fmaf(k, t.z, bef.z); bef.w = fmaf(k, t.w, bef.w);
+                }
+                float4 osum, obef;
+                osum.x = __shfl_xor_sync(0xffffffffu, sum.x, 16); osum.y = __shfl_xor_sync(0xffffffffu, sum.y, 16);
+                osum.z = __shfl_xor_sync(0xffffffffu, sum.z, 16); osum.w = __shfl_xor_sync(0xffffffffu, sum.w, 16);
+                obef.x = __shfl_xor_sync(0xffffffffu, bef.x, 16); obef.y = __shfl_xor_sync(0xffffffffu, bef.y, 16);
+                obef.z = __shfl_xor_sync(0xffffffffu, bef.z, 16); obef.w = __shfl_xor_sync(0xffffffffu, bef.w, 16);
+                const float4 gref = half ? osum : sum;                    // the half-warp that read the first 8 groups has it
+                off = make_float4(bef.x + obef.x - gref.x, bef.y + obef.y - gref.y, bef.z + obef.z - gref.z, bef.w + obef.w - gref.w);
+                if (grp == 0 && half == 0) {                              // [G_ref | G_last] of this iteration for the state warps
+                    float4* ve = reinterpret_cast<float4*>(vec + (m & 3) * 128) + c4l;
+                    ve[0] = gref;
+                    ve[16] = make_float4(sum.x + osum.x, sum.y + osum.y, sum.z + osum.z, sum.w + osum.w);
+                }
+            }
             // ---- scale phase ----
-            const float* part = reinterpret_cast<const float*>(smem + WO_PART) + (m & 1) * (W_PREP_WARPS * WDK);
-            const float4 off = reinterpret_cast<const float4*>(part)[grp * 16 + c4l];
             // Log-gates are <= 0, so a lane's exponents are monotone along its 4 tokens: the largest magnitude is at one
             // of the two ends.  Beyond the range the factorisation covers, exponents are clamped and the call is flagged.
             float worst = fmaxf(fmaxf(fabsf(off.x + gl[0].x), fabsf(off.y + gl[0].y)), fmaxf(fabsf(off.z + gl[0].z), fabsf(off.w + gl[0].w)));
@@ -475,13 +466,13 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         const float o_sign = p.qscale;                        // scale * out_scale, applied to the finished accumulators
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
         int items = 0, ci = 0;
-        // output of iteration j: accumulator slot j & 1 -> 16-bit tile (128-byte swizzle) over the dead q tile of the
-        // iteration's stage; the store thread sends it out
+        // output of iteration j: accumulator slot j & 1 -> 16-bit tile (128-byte swizzle) in the tile that held the score
+        // columns 64..127, which the iteration's last product has read by then; the store thread sends it out
         auto epilogue = [&](uint32_t j) {
-            if (lane == 0) waiter.wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
             __syncwarp();
             tc_fence_after();
-            uint8_t* orow = smem + (j % 3) * W_STAGE_B + WS_Q + row * 128;
+            uint8_t* orow = smem + WO_X + row * 128;
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
                 float a[32];
@@ -506,7 +497,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         };
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
-            if (lane == 0) waiter.wait(bar(B_PFULL), m & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_PFULL), m & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -521,8 +512,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             const uint32_t dmask_bits = dir ? ~((1u << lane) - 1u) : (lane == 31 ? 0xffffffffu : (2u << lane) - 1u);
 #pragma unroll 1
             for (int cb = 0; cb < 4; ++cb) {                  // key block: keys 32*cb .. 32*cb+31
-                if (cb == 2 && m > 0) {                       // the second tile is free once the previous iteration's MMAs are done
-                    if (lane == 0) waiter.wait(bar(B_OFULL + ((m - 1) & 1)), ((m - 1) >> 1) & 1);
+                if (cb == 2 && m > 0) {                       // the second tile is free once the store thread has sent the previous output
+                    if (lane == 0) waiter.wait_lite(bar(B_XFREE), (m - 1) & 1);
                     __syncwarp();
                 }
                 const bool all_zero = dir ? cb < quad : cb > quad;
@@ -553,8 +544,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
             }
-            if (m > 0) epilogue(m - 1);                       // one iteration behind: the MMAs of m - 1 finish meanwhile
             if (at_end) { if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (m & 1))); break; }   // end marker for the store thread
+            epilogue(m);                                      // the next iteration's scores cannot be there before this iteration's last product is issued
         }
     } else if (warp < W_CTRL_WARP0) {
         // =============================== state warps ===============================
@@ -573,7 +564,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait(bar(B_PREPPED + s), (m / 3) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -586,7 +577,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     gacc = 0.f;
                 } else {
                     uint32_t* cnt = wp.chain_cnt + cur.bh * 2 + cur.dir;
-                    if (lane == 0) global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag, p.status);
+                    if (lane == 0) global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag);
                     __syncwarp();
                     const float* box = wp.mailbox + (((size_t)cur.bh * 2 + cur.dir) * 2 + ((cur.w - 1) & 1)) * SLOT;
                     src = box;
@@ -601,7 +592,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             const float* ve = vec + (m & 3) * 128;             // [G_ref | G_last] of this iteration, log2 units
             if (m > 0) {                                      // the previous iteration's state product has read the operand
-                if (lane == 0) waiter.wait(bar(B_STFREE), (m - 1) & 1);
+                if (lane == 0) waiter.wait_lite(bar(B_STFREE), (m - 1) & 1);
                 __syncwarp();
             }
             if (!s_zero) {                                    // bf16(2^G_ref * S_in), MN-major [channel][value]
@@ -617,7 +608,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_STREADY));
-            if (lane == 0) waiter.wait(bar(B_UFULL + (m & 1)), (m >> 1) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_UFULL + (m & 1)), (m >> 1) & 1);
             __syncwarp();
             tc_fence_after();
             {
@@ -668,6 +659,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     // ---- teardown: every role has left its loop; all MMAs were waited for by their consumers ----
     tc_fence_before();
     __syncthreads();
+    if (tid == 32 && *abort_flag && p.status) atomicOr(p.status, 1);   // a bounded wait ran out somewhere in this CTA
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(WT_COLS) : "memory");
@@ -685,6 +677,8 @@ int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream
     WaveParams wp;
     wp.p = p;
     wp.nseg = nseg;
+    wp.inv_per_step = 1.0f / (float)(BH * (p.dir_mask == 3 ? 2 : 1));
+    wp.inv_H = 1.0f / (float)p.H;
     wp.ticket = reinterpret_cast<uint32_t*>(ws);
     wp.chain_cnt = wp.ticket + 1;
     wp.chunk_flag = wp.chain_cnt + 2 * (size_t)BH;
@@ -716,6 +710,7 @@ bool bigla_wave_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
     if (p.dv != WDV || p.dk != WDK || !p.o || !p.q || p.B * p.H < 1 || p.L < 1) return false;
     if (p.dir_mask < 1 || p.dir_mask > 3) return false;
+    if ((long long)p.B * p.H * 2 * ((p.L + W_SEG - 1) / W_SEG) >= (1ll << 24)) return false;   // tickets are decoded in fp32
     if (!tc::tma_ok(p.q, p.sq, p.B, p.H) || !tc::tma_ok(p.k, p.sk, p.B, p.H) || !tc::tma_ok(p.v, p.sv, p.B, p.H)) return false;
     if ((p.dir_mask & 1) && (!p.gf || !tc::tma_ok(p.gf, p.sgf, p.B, p.H))) return false;
     if ((p.dir_mask & 2) && (!p.gb || !tc::tma_ok(p.gb, p.sgb, p.B, p.H))) return false;

@@ -84,7 +84,8 @@ __global__ void __launch_bounds__(EW_THREADS) dwconv3x3_kernel(const T* __restri
 template <typename T, int RUN>
 __global__ void __launch_bounds__(EW_THREADS, 2) dwconv3x3_rows_kernel(const T* __restrict__ x, const T* __restrict__ wt,
                                                                     const T* __restrict__ bias, T* __restrict__ y,
-                                                                    int B, int h, int w, int C, int act) {
+                                                                    int B, int h, int w, int C, int act,
+                                                                    const T* __restrict__ top, const T* __restrict__ bottom) {
     using P2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
     const uint32_t cq = C / 4, nrun = (w + RUN - 1) / RUN;
     const uint32_t total = (uint32_t)B * h * nrun * cq;
@@ -111,6 +112,10 @@ __global__ void __launch_bounds__(EW_THREADS, 2) dwconv3x3_rows_kernel(const T* 
         const int y2 = yy + ky - 1;
         rok[ky] = y2 >= 0 && y2 < h;
         rowp[ky] = x + (((size_t)b * h + (rok[ky] ? y2 : yy)) * w) * C + c0;
+        // rows just outside the slab come from the halo rows ([B, w, C]) when the caller has them: the slab is then a
+        // band of a taller image whose other rows live elsewhere (another GPU); without them the slab is the whole image
+        if (y2 < 0 && top) { rok[ky] = true; rowp[ky] = top + ((size_t)b * w) * C + c0; }
+        if (y2 >= h && bottom) { rok[ky] = true; rowp[ky] = bottom + ((size_t)b * w) * C + c0; }
     }
     auto load_col = [&](int xx, uint2* raw) {                 // the three inputs of image column xx (zeros outside the image)
 #pragma unroll
@@ -480,9 +485,11 @@ inline int grid_for(int64_t items, int per_block) {
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T>
-int dwconv_t(const void* x, const void* wt, const void* bias, void* y, int B, int h, int w, int C, int act, cudaStream_t s) {
+int dwconv_t(const void* x, const void* wt, const void* bias, void* y, int B, int h, int w, int C, int act, cudaStream_t s,
+             const void* top = nullptr, const void* bottom = nullptr) {
     constexpr int V = DType<T>::VEC;
     if (C % V) return VIG_ERR_SHAPE;
+    if ((top || bottom) && !(sizeof(T) == 2 && C % 4 == 0)) return VIG_ERR_SHAPE;   // halo rows: 16-bit sliding-window form only
     const int64_t items = (int64_t)B * h * w * (C / V);
     if (items >= (1ll << 31)) return VIG_ERR_SHAPE;                             // 32-bit index arithmetic in the kernel
     if (sizeof(T) == 2 && C % 4 == 0) {                     // sliding-window form: 4 channels x RUN tokens per thread
@@ -490,9 +497,10 @@ int dwconv_t(const void* x, const void* wt, const void* bias, void* y, int B, in
         const int64_t threads = (int64_t)B * h * ((w + RUN - 1) / RUN) * (C / 4);
         if (threads < (1ll << 31)) {
             dwconv3x3_rows_kernel<T, RUN><<<(unsigned)((threads + EW_THREADS - 1) / EW_THREADS), EW_THREADS, 0, s>>>(
-                (const T*)x, (const T*)wt, (const T*)bias, (T*)y, B, h, w, C, act);
+                (const T*)x, (const T*)wt, (const T*)bias, (T*)y, B, h, w, C, act, (const T*)top, (const T*)bottom);
             return (int)cudaGetLastError();
         }
+        if (top || bottom) return VIG_ERR_SHAPE;
     }
     dwconv3x3_kernel<T><<<grid_for(items, EW_THREADS), EW_THREADS, 0, s>>>((const T*)x, (const T*)wt, (const T*)bias, (T*)y, B, h, w, C, act);
     return (int)cudaGetLastError();
@@ -577,6 +585,17 @@ extern "C" int vig_dwconv3x3_fwd(const void* x, const void* wt, const void* bias
     if (B == 0) return VIG_OK;
     if (!aligned16(x) || !aligned16(wt) || !aligned16(y) || (bias && !aligned16(bias))) return VIG_ERR_ALIGN;
     VIG_DISPATCH(dtype, dwconv_t<T>(x, wt, bias, y, B, h, w, C, act_silu, (cudaStream_t)stream))
+}
+
+extern "C" int vig_dwconv3x3_halo_fwd(const void* x, const void* top, const void* bottom, const void* wt, const void* bias, void* y,
+                                      int B, int h, int w, int C, int act_silu, int dtype, void* stream) {
+    if (!x || !wt || !y) return VIG_ERR_NULL;
+    if (B < 0 || h <= 0 || w <= 0 || C <= 0) return VIG_ERR_SHAPE;
+    if (dtype != VIG_DTYPE_BF16 && dtype != VIG_DTYPE_F16) return VIG_ERR_DTYPE;
+    if (B == 0) return VIG_OK;
+    if (!aligned16(x) || !aligned16(wt) || !aligned16(y) || (bias && !aligned16(bias)) || (top && !aligned16(top)) ||
+        (bottom && !aligned16(bottom))) return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, dwconv_t<T>(x, wt, bias, y, B, h, w, C, act_silu, (cudaStream_t)stream, top, bottom))
 }
 
 extern "C" int vig_gate_inject_fwd(const void* o, const int64_t* strides_o, const void* local, const void* gate_logits,

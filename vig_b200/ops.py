@@ -330,14 +330,24 @@ def fused_recurrent_gla(q, k, v, gk=None, gv=None, scale=-1, initial_state=None,
 
 
 # --------------------------------------------------------------------------------------------------
-def dwconv3x3(x, weight_tap_major, bias, hw, act_silu, out=None):
-    """Depthwise 3x3 (+SiLU) on ``[B, h*w, C]`` tokens; ``weight_tap_major`` is ``[9, C]``."""
-    _lib.require_cuda(x, weight_tap_major)
+def dwconv3x3(x, weight_tap_major, bias, hw, act_silu, out=None, top=None, bottom=None):
+    """Depthwise 3x3 (+SiLU) on ``[B, h*w, C]`` tokens; ``weight_tap_major`` is ``[9, C]``.  ``top`` / ``bottom``
+    (``[B, w, C]``, 16-bit types): the image rows just above / below when ``x`` is a band of a taller image."""
+    _lib.require_cuda(x, weight_tap_major, top, bottom)
     B, L, C = x.shape
     h, w = hw
     if h * w != L or not x.is_contiguous():
         raise ValueError("x must be contiguous [B, h*w, C]")
     y = torch.empty_like(x) if out is None else out
+    if top is not None or bottom is not None:
+        for t in (top, bottom):
+            if t is not None and (t.shape != (B, w, C) or not t.is_contiguous() or t.dtype != x.dtype):
+                raise ValueError("halo rows must be contiguous [B, w, C] tensors of x's dtype")
+        st = _lib.lib().vig_dwconv3x3_halo_fwd(_lib.ptr(x), _lib.ptr(top), _lib.ptr(bottom), _lib.ptr(weight_tap_major),
+                                               _lib.ptr(bias), _lib.ptr(y), B, h, w, C, int(bool(act_silu)),
+                                               _lib.dtype_code(x), _lib.stream_ptr())
+        _lib.check(st, "vig_dwconv3x3_halo_fwd")
+        return y
     st = _lib.lib().vig_dwconv3x3_fwd(_lib.ptr(x), _lib.ptr(weight_tap_major), _lib.ptr(bias), _lib.ptr(y),
                                       B, h, w, C, int(bool(act_silu)), _lib.dtype_code(x), _lib.stream_ptr())
     _lib.check(st, "vig_dwconv3x3_fwd")

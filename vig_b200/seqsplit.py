@@ -35,28 +35,47 @@ def unpack_summary(msg, dk, dv):
 
 
 def fold(summaries, rank, dk, dv, init_fwd=None, init_bwd=None):
-    """Entering states of slice ``rank`` from the gathered summaries (list over ranks, slice order = rank order).
+    """Entering states of slice ``rank`` from the gathered summaries (list over ranks, or one stacked
+    ``[world, B, H, 2, dk*dv+dk]`` tensor; slice order = rank order).
 
     forward:  S = init_fwd; for r < rank:            S = exp(D_f[r]) * S + U_f[r]
     backward: S = init_bwd; for r > rank, descending: S = exp(D_b[r]) * S + U_b[r]
+
+    Unrolled, S = sum_r w_r * U_r with w_r = exp(sum of the log-decays of the slices between r and this one): two
+    cumulative sums over the rank axis and one weighted sum per direction, a handful of launches whatever the world size.
     """
-    u_f0, _, _, _ = unpack_summary(summaries[0], dk, dv)
-    s_f = torch.zeros_like(u_f0) if init_fwd is None else init_fwd.float().clone()
-    s_b = torch.zeros_like(u_f0) if init_bwd is None else init_bwd.float().clone()
-    for r in range(rank):
-        u, d, _, _ = unpack_summary(summaries[r], dk, dv)
-        s_f = s_f * d.exp().unsqueeze(-1) + u
-    for r in range(len(summaries) - 1, rank, -1):
-        _, _, u, d = unpack_summary(summaries[r], dk, dv)
-        s_b = s_b * d.exp().unsqueeze(-1) + u
+    msgs = summaries if torch.is_tensor(summaries) else torch.stack(list(summaries))
+    world = msgs.shape[0]
+    u = msgs[..., :dk * dv].reshape(*msgs.shape[:-1], dk, dv)          # [world, B, H, 2, dk, dv]
+    d = msgs[..., dk * dv:]                                            # [world, B, H, 2, dk]
+    zero_d = torch.zeros_like(d[0, :, :, 0])
+
+    def chain(us, ds, init):
+        """us/ds: the slices the state passes through, in scan order (nearest to this slice last)."""
+        n = us.shape[0]
+        if n == 0:
+            return torch.zeros_like(u[0, :, :, 0]) if init is None else init.float().clone()
+        # decay applied to U of slice i: the slices after it in scan order; suffix sums of the log-decays, exclusive
+        after = torch.flip(torch.cumsum(torch.flip(ds, [0]), 0), [0]) - ds
+        state = (us * after.exp().unsqueeze(-1)).sum(0)
+        if init is not None:
+            state = state + init.float() * ds.sum(0).exp().unsqueeze(-1)
+        return state
+
+    s_f = chain(u[:rank, :, :, 0], d[:rank, :, :, 0], init_fwd)
+    s_b = chain(torch.flip(u[rank + 1:, :, :, 1], [0]), torch.flip(d[rank + 1:, :, :, 1], [0]), init_bwd)
+    del zero_d, world
     return s_f.contiguous(), s_b.contiguous()
 
 
 def exchange(msg, group=None):
-    """All-gather of the per-rank summaries; returns the list over ranks."""
+    """All-gather of the per-rank summaries into one ``[world, ...]`` tensor (one collective, one output buffer)."""
     world = dist.get_world_size(group)
-    out = [torch.empty_like(msg) for _ in range(world)]
-    dist.all_gather(out, msg, group=group)
+    out = torch.empty((world,) + tuple(msg.shape), dtype=msg.dtype, device=msg.device)
+    if msg.is_cuda:
+        dist.all_gather_into_tensor(out, msg.contiguous(), group=group)
+    else:                                                   # gloo (CPU ranks in the tests) has only the list form
+        dist.all_gather(list(out.unbind(0)), msg.contiguous(), group=group)
     return out
 
 
@@ -97,21 +116,37 @@ def row_range(h, rank, world):
     return r0, r0 + base + (1 if rank < extra else 0)
 
 
+def exchange_halo_rows(x, w, group, rank, world):
+    """Send my first image row up and my last row down, receive the neighbours' rows next to mine: two point-to-point
+    transfers per neighbour, nothing from the ranks further away.  Returns ``(top, bottom)``, ``None`` at the image border."""
+    B, L, C = x.shape
+    first, last = x[:, :w].contiguous(), x[:, L - w:].contiguous()
+    top = torch.empty_like(first) if rank > 0 else None
+    bottom = torch.empty_like(first) if rank + 1 < world else None
+    peer = lambda r: dist.get_global_rank(group, r) if group is not None else r
+    ops_ = []
+    if rank > 0:
+        ops_ += [dist.P2POp(dist.isend, first, peer(rank - 1), group), dist.P2POp(dist.irecv, top, peer(rank - 1), group)]
+    if rank + 1 < world:
+        ops_ += [dist.P2POp(dist.isend, last, peer(rank + 1), group), dist.P2POp(dist.irecv, bottom, peer(rank + 1), group)]
+    for req in dist.batch_isend_irecv(ops_) if ops_ else []:
+        req.wait()
+    return top, bottom
+
+
 def _halo_local_fn(group, rank, world):
-    """Depthwise conv over this rank's rows with one row of halo gathered from the neighbours."""
+    """Depthwise conv over this rank's rows with one row of halo from each neighbour, read in place by the kernel."""
     from . import ops
 
     def local_fn(x, taps, bias, hw, act):
         rows, w = hw
-        B, L, C = x.shape
-        edges = torch.stack([x[:, :w], x[:, L - w:]], dim=0).contiguous()          # my first and last row
-        gathered = [torch.empty_like(edges) for _ in range(world)]
-        dist.all_gather(gathered, edges, group=group)
-        top = gathered[rank - 1][1] if rank > 0 else torch.zeros_like(edges[0])        # zero rows = the conv's padding
-        bot = gathered[rank + 1][0] if rank + 1 < world else torch.zeros_like(edges[0])
-        padded = torch.cat([top, x, bot], dim=1)
-        y = ops.dwconv3x3(padded, taps, bias, (rows + 2, w), act)
-        return y[:, w:L + w].contiguous()
+        top, bottom = exchange_halo_rows(x, w, group, rank, world)
+        if x.dtype == torch.float32:                         # the halo form of the kernel is 16-bit only: pad and slice
+            B, L, C = x.shape
+            z = torch.zeros_like(x[:, :w])
+            padded = torch.cat([z if top is None else top, x, z if bottom is None else bottom], dim=1)
+            return ops.dwconv3x3(padded, taps, bias, (rows + 2, w), act)[:, w:L + w].contiguous()
+        return ops.dwconv3x3(x, taps, bias, hw, act, top=top, bottom=bottom)
     return local_fn
 
 
