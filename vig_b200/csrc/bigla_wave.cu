@@ -564,7 +564,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);
+            // The work item is known as soon as its loads are under way: the state entering a new segment is fetched
+            // from the mailbox while the prep warps still work on the iteration (two trips to L2 that would otherwise
+            // sit in front of the state product).
+            if (lane == 0) waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -590,6 +593,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     S[j] = t4.x; S[j + 1] = t4.y; S[j + 2] = t4.z; S[j + 3] = t4.w;
                 }
             }
+            if (lane == 0) waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);   // G_ref, G_last of this iteration are written
+            __syncwarp();
+            if (*abort_flag) break;
             const float* ve = vec + (m & 3) * 128;             // [G_ref | G_last] of this iteration, log2 units
             if (m > 0) {                                      // the previous iteration's state product has read the operand
                 if (lane == 0) waiter.wait_lite(bar(B_STFREE), (m - 1) & 1);
