@@ -14,4 +14,4 @@ from .gla import naive_gla, naive_bi_gla, chunked_bi_gla_f64      # noqa: F401
 from .block import (rms_norm, swiglu, dwconv3x3_nlc, gate_inject,  # noqa: F401
                     gla_attention_forward, mlp_forward, block_forward, vig_forward,
                     patch_embed_v2, resize_pos_embed)
-from .weights import ViGShape, PRESETS, make_state_dict, make_images, make_bigla_inputs  # noqa: F401
+from .weights import ViGShape, PRESETS, make_state_dict, make_images, make_bigla_inputs, seeded_like  # noqa: F401

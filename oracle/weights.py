@@ -119,3 +119,23 @@ def make_bigla_inputs(B, H, L, dk, dv, seed=0, gate_normalizer=16.0):
     g_fwd = torch.nn.functional.logsigmoid(torch.randn(B, H, L, dk, generator=gen)) / gate_normalizer
     g_bwd = torch.nn.functional.logsigmoid(torch.randn(B, H, L, dk, generator=gen)) / gate_normalizer
     return q, k, v, g_fwd, g_bwd
+
+
+def seeded_like(template, seed=0):
+    """Deterministic values for every entry of ``template`` (a state dict: name -> tensor), keyed by NAME, so that two
+    implementations with the same parameter names get the same weights whatever their parameter order: matrices and
+    convolution kernels N(0, 1/fan_in), vectors named ``*.bias`` N(0, 0.02^2), other vectors (norm weights) 1 + N(0, 0.1^2)."""
+    import zlib
+    out = {}
+    for name, t in template.items():
+        rng = np.random.default_rng([seed, zlib.crc32(name.encode())])
+        shape = tuple(t.shape)
+        if len(shape) >= 2:
+            fan_in = int(np.prod(shape[1:]))
+            v = rng.standard_normal(size=shape) / math.sqrt(fan_in)
+        elif name.endswith("bias"):
+            v = 0.02 * rng.standard_normal(size=shape)
+        else:
+            v = 1.0 + 0.1 * rng.standard_normal(size=shape)
+        out[name] = torch.from_numpy(v.astype(np.float32))
+    return out

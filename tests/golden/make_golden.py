@@ -1,8 +1,8 @@
 """Generate the golden vectors in this folder from the REFERENCE's own Python code on CPU.
 
 Run once, in a container that has the reference checkout, as
-    python tests/golden/make_golden.py /path/to/reference [ops] [blocks] [full]
-(no selection = all three files: ``bigla_ref.npz``, ``block_ref.npz``, ``model_ref.npz``; ``full`` alone takes
+    python tests/golden/make_golden.py /path/to/reference [ops] [blocks] [full] [hier]
+(no selection = all four files: ``bigla_ref.npz``, ``block_ref.npz``, ``model_ref.npz``, ``hier_ref.npz``; ``full`` alone takes
 about a quarter of an hour on 8 cores, most of it the 16384-token case).
 It cannot run where the reference is absent; the committed ``.npz`` files are what the
 tests read.  What is executed on the reference side:
@@ -115,9 +115,46 @@ def full_models(vig):
     np.savez_compressed(os.path.join(HERE, "model_ref.npz"), **out)
 
 
+# Hierarchical model (classification/models/vig_h.py): two tiny four-stage models, one per layout of the reference
+# (channels first with LayerNorm2d / gated MLP / v2 stem / v3 downsampling as in configs/vig-h/*.yaml, and channels last
+# with plain LayerNorm / GELU MLP / v1 stem / v2 downsampling), weights from oracle.seeded_like (keyed by parameter name).
+HIER_CASES = {
+    "cf": dict(depths=[1, 1, 2, 1], dims=96, num_heads=[3, 6, 12, 24], norm_layer="ln2d", patchembed_version="v2",
+               downsample_version="v3", gmlp=True, use_act_in_conv=False, use_out_act=False, num_classes=12, drop_path_rate=0.0),
+    "cl": dict(depths=[1, 1, 1, 1], dims=64, num_heads=[2, 4, 8, 16], norm_layer="ln", patchembed_version="v1",
+               downsample_version="v2", gmlp=False, use_act_in_conv=True, use_out_act=True, num_classes=12, drop_path_rate=0.0,
+               expand_k=1.0),
+}
+
+
+def hier_models(ref_root, vig):
+    def mk(name, **attrs):
+        m = types.ModuleType(name); m.__dict__.update(attrs); sys.modules[name] = m; return m
+    mk("fvcore"); mk("fvcore.nn", FlopCountAnalysis=object, flop_count_str=None, flop_count=None, parameter_count=None)
+    mk("torchvision"); mk("torchvision.models", VisionTransformer=object)
+    spec = importlib.util.spec_from_file_location("ref_vig_h", os.path.join(ref_root, "classification", "models", "vig_h.py"))
+    vh = importlib.util.module_from_spec(spec); spec.loader.exec_module(vh)
+    vh.bid_fused_recurrent_gla = vig.bid_fused_recurrent_gla          # the naive recurrence / 2, as for the plain model
+    out = {}
+    for tag, kw in HIER_CASES.items():
+        model = vh.HierViG(**kw).eval()
+        sd = oracle.seeded_like(model.state_dict(), seed=5)
+        model.load_state_dict(sd, strict=True)
+        images = oracle.make_images(2, 64, seed=9)
+        out[f"hier_{tag}_logits"] = model(images).numpy().astype(np.float32)
+        x = model.patch_embed(images)
+        x = model.layers[0].blocks(x)                                 # the first stage, before its downsampling
+        if kw["norm_layer"] == "ln2d":
+            x = x.permute(0, 2, 3, 1)
+        out[f"hier_{tag}_stage0"] = x.reshape(2, -1, x.shape[-1]).numpy().astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "hier_ref.npz"), **out)
+
+
 def main(ref_root, only=()):
     vig, naive = load_reference(ref_root)
     torch.set_grad_enabled(False)
+    if not only or "hier" in only:
+        hier_models(ref_root, vig)
     if not only or "ops" in only:
         operator_pins(naive)
     if not only or "blocks" in only:
@@ -172,5 +209,5 @@ def block_pins(vig):
 
 if __name__ == "__main__":
     if len(sys.argv) < 2:
-        sys.exit("usage: make_golden.py /path/to/reference [ops] [blocks] [full]")
+        sys.exit("usage: make_golden.py /path/to/reference [ops] [blocks] [full] [hier]")
     main(sys.argv[1], tuple(sys.argv[2:]))

@@ -1,0 +1,53 @@
+"""Hierarchical ViG (``HierViG`` / ``GLA2D`` / ``VSSBlock``, classification/models/vig_h.py) on the CUDA operators against
+vectors produced by the reference's own classes (tests/golden/make_golden.py, section ``hier``): both layouts of the
+reference, weights keyed by parameter name so that the same state dict loads into both sides."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import GOLDEN, rel_err
+
+# the constructor arguments of tests/golden/make_golden.py::HIER_CASES
+HIER_CASES = {
+    "cf": dict(depths=[1, 1, 2, 1], dims=96, num_heads=[3, 6, 12, 24], norm_layer="ln2d", patchembed_version="v2",
+               downsample_version="v3", gmlp=True, use_act_in_conv=False, use_out_act=False, num_classes=12),
+    "cl": dict(depths=[1, 1, 1, 1], dims=64, num_heads=[2, 4, 8, 16], norm_layer="ln", patchembed_version="v1",
+               downsample_version="v2", gmlp=False, use_act_in_conv=True, use_out_act=True, num_classes=12, expand_k=1.0),
+}
+
+
+def test_parameter_names_follow_the_reference():
+    import vig_b200
+    model = vig_b200.HierViG(**HIER_CASES["cf"])
+    names = set(model.state_dict())
+    for expected in ("patch_embed.0.weight", "patch_embed.2.weight", "patch_embed.5.weight", "patch_embed.7.bias",
+                     "layers.0.blocks.0.norm.weight", "layers.0.blocks.0.op.in_proj.0.weight", "layers.0.blocks.0.op.qkv_proj.weight",
+                     "layers.0.blocks.0.op.gk_proj.1.bias", "layers.0.blocks.0.op.g_norm.weight", "layers.0.blocks.0.op.o_proj.weight",
+                     "layers.0.blocks.0.norm2.bias", "layers.0.blocks.0.mlp.fc1.weight", "layers.0.downsample.1.weight",
+                     "layers.0.downsample.3.weight", "layers.2.blocks.1.mlp.fc2.weight", "classifier.norm.weight", "classifier.head.bias"):
+        assert expected in names, expected
+    assert model.layers[0].blocks[0].op.head_qk_dim == 16 and model.layers[3].blocks[0].op.head_v_dim == 32
+    model.load_state_dict(oracle.seeded_like(model.state_dict(), seed=5), strict=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tag", ["cf", "cl"])
+def test_hier_vig_matches_reference_vectors(tag, dtype):
+    import vig_b200
+    golden = np.load(os.path.join(GOLDEN, "hier_ref.npz"))
+    model = vig_b200.HierViG(**HIER_CASES[tag])
+    model.load_state_dict(oracle.seeded_like(model.state_dict(), seed=5), strict=True)
+    model = model.to("cuda", dtype).eval()
+    images = oracle.make_images(2, 64, seed=9).to("cuda", dtype)
+    with torch.no_grad():
+        stage0 = model.forward_features(images, return_stages=True)[0][0]
+        logits = model(images)
+    vig_b200.check_status()
+    e_stage, e_logits = rel_err(stage0.float(), golden[f"hier_{tag}_stage0"]), rel_err(logits.float(), golden[f"hier_{tag}_logits"])
+    print(f"HierViG {tag} {dtype}: first stage {e_stage:.2e}, logits {e_logits:.2e}")
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert e_stage < tol and e_logits < tol

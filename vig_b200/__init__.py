@@ -4,3 +4,4 @@ from .ops import (bi_gla, bi_gla_backward, bid_fused_recurrent_gla, fused_chunk_
                   check_status, status_word)
 from .modules import RMSNorm, GatedLinearAttention, GLAMLP, GLABlock  # noqa: F401
 from .vig import ViG, build_vig  # noqa: F401
+from .hier import HierViG, GLA2D, VSSBlock  # noqa: F401

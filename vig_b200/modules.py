@@ -55,6 +55,9 @@ class GatedLinearAttention(nn.Module):
         self.l_norm = RMSNorm(self.head_v_dim, eps=layernorm_eps)
         self.g_proj = nn.Linear(d_model, self.value_dim, bias=True)
         self._packed = None
+        # scale of the summed directions: the operator wrapper halves the sum (recurrent_fuse.py:442) and ViG's eval branch
+        # halves it again (vig.py:443); GLA2D of the hierarchical model keeps the single halving (vig_h.py:577-578)
+        self.out_scale = 0.25
         # inference-time weight folding of the gate bottleneck (16-bit runs only; fp32 keeps the reference's two steps)
         self.fold_gate_bottleneck = True
 
@@ -109,7 +112,7 @@ class GatedLinearAttention(nn.Module):
         g_fwd, g_bwd = heads(gk[..., :kd], dk), heads(gk[..., kd:], dk)
         o = torch.empty(B, L, H, dv, dtype=x.dtype, device=x.device).permute(0, 2, 1, 3)
         # reference: (o_f + o_b) / 2 in the operator wrapper, / 2 again in the eval branch (vig.py:443)
-        scan_kw = dict(out_scale=0.25, out=o, gate_logit_normalizer=float(self.gate_logit_normalizer), clamp_min=self.clamp_min)
+        scan_kw = dict(out_scale=self.out_scale, out=o, gate_logit_normalizer=float(self.gate_logit_normalizer), clamp_min=self.clamp_min)
         if scan_fn is None:
             ops.bi_gla(q, k, v, g_fwd, g_bwd, **scan_kw)
         else:
