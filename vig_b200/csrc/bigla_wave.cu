@@ -85,7 +85,7 @@ template <> struct RedAdd<__half> {
 };
 
 // Bounded wait on a global counter (one lane polls).
-__device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, volatile int* abort_flag, int32_t* status) {
+__device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, volatile int* abort_flag) {
 #pragma unroll 1
     for (uint32_t i = 0; i < (1u << 21); ++i) {
         if (ld_acquire_u32(ctr) >= need) return;
@@ -93,7 +93,6 @@ __device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, 
         __nanosleep(64);
     }
     *abort_flag = 1;
-    if (status) atomicOr(status, 1);
 }
 
 
@@ -175,7 +174,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     l_ci = 0;
                 }
                 const uint32_t s = lm % 3;
-                if (lm >= 3) waiter.wait(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
+                if (lm >= 3) waiter.wait_lite(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
                 if (*abort_flag) break;
                 if (lcur.nch == 0) { mbar_arrive_plain(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
                 const int t0 = lcur.seg * W_SEG + chunk_of(lcur, l_ci) * CHUNK;
@@ -194,7 +193,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             #pragma unroll 1
             for (uint32_t m = 0;; ++m, ++m_ci) {
                 const uint32_t s = m % 3, st = sbase + s * W_STAGE_B;
-                waiter.wait(bar(B_PREPPED + s), (m / 3) & 1);  // also orders the read of the work item after its write
+                waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);  // also orders the read of the work item after its write
                 if (*abort_flag) break;
                 if (m_ci == mcur.nch) { read_item(m_items, mcur); ++m_items; m_ci = 0; }
                 if (mcur.nch == 0) { mbar_arrive_plain(bar(B_PFULL)); break; }      // end marker: wakes the score warps
@@ -207,15 +206,15 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 for (int k4 = 0; k4 < WDK / 16; ++k4) tc_mma(tmem + WT_P, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
                 tc_commit(bar(B_PFULL));
                 // (b) product with the entering state
-                waiter.wait(bar(B_STREADY), m & 1);
-                if (m >= 2) waiter.wait(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
+                waiter.wait_lite(bar(B_STREADY), m & 1);
+                if (m >= 2) waiter.wait_lite(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
                 tc_fence_after();
                 if (!s_zero) {
 #pragma unroll 1
                     for (int k4 = 0; k4 < WDK / 16; ++k4) tc_mma(o_acc, make_desc(qt + k4 * 32), make_desc(stt + k4 * 2048), IDESC_OV, k4 > 0);
                 }
                 // (c) masked scores x v, state update
-                waiter.wait(bar(B_PREADY), m & 1);
+                waiter.wait_lite(bar(B_PREADY), m & 1);
                 tc_fence_after();
 #pragma unroll 1
                 for (int k8 = 0; k8 < CHUNK / 16; ++k8)
@@ -241,7 +240,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait(bar(B_FULL + s), (m / 3) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -298,7 +297,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             // the prep warps meet on an mbarrier, not a named barrier: its wait is bounded like every other wait here
             __syncwarp();
-            if (lane == 0) { mbar_arrive_plain(bar(B_PART)); waiter.wait(bar(B_PART), m & 1); }
+            if (lane == 0) { mbar_arrive_plain(bar(B_PART)); waiter.wait_lite(bar(B_PART), m & 1); }
             __syncwarp();
             float4 off = half_off, gref = make_float4(0.f, 0.f, 0.f, 0.f), glast = gref;
 #pragma unroll 2
@@ -367,7 +366,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         int items = 0, ci = 0, prev_ci = 0;
         // output of iteration j: accumulator slot j & 1 -> global
         auto epilogue = [&](uint32_t j, const Item& it, int jci) {
-            if (lane == 0) waiter.wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
             __syncwarp();
             tc_fence_after();
             const int c = chunk_of(it, jci);
@@ -376,7 +375,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             const bool first = ndir == 1 || it.w < w_other || (it.w == w_other && it.dir == 0);
             uint32_t* flag = wp.chunk_flag + (size_t)it.bh * nseg * W_SEG_CHUNKS + it.seg * W_SEG_CHUNKS + c;
             if (!first) {                                     // the other direction's half must be in place
-                if (lane == 0) global_wait(flag, 4u, abort_flag, p.status);
+                if (lane == 0) global_wait(flag, 4u, abort_flag);
                 __syncwarp();
             }
             T* obase = reinterpret_cast<T*>(p.o) + (it.bh / p.H) * p.so[0] + (it.bh % p.H) * p.so[1] + (int64_t)tok * p.so[2];
@@ -408,7 +407,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         };
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
-            if (lane == 0) waiter.wait(bar(B_PFULL), m & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_PFULL), m & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -424,11 +423,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
 #pragma unroll 1
             for (int cb = 0; cb < 4; ++cb) {                  // key block: keys 32*cb .. 32*cb+31
                 if (cb == 2 && m > 0) {                       // the second tile is free once the previous iteration's MMAs are done
-                    if (lane == 0) waiter.wait(bar(B_UFULL), (m - 1) & 1);
+                    if (lane == 0) waiter.wait_lite(bar(B_UFULL), (m - 1) & 1);
                     __syncwarp();
                 }
                 const bool all_zero = dir ? cb < quad : cb > quad;
-                const uint32_t keep_bits = cb == quad ? dmask_bits : 0xffffffffu;
                 uint8_t* prow = (cb < 2 ? p0 : p1) + row * 128;
                 const uint32_t chunk0 = (uint32_t)(cb & 1) * 4;           // first 16-byte chunk of this block in the 128-byte row
                 if (all_zero) {
@@ -438,14 +436,15 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     float a[32];
                     tc_ld32(tmem + lane_base + WT_P + 32 * cb, a);
                     tc_wait_ld();
+                    if (cb == quad) {                                     // the diagonal block: per-element mask
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) a[e] = (dmask_bits >> e) & 1u ? a[e] : 0.f;
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        float mk[8];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) mk[e] = (keep_bits >> (8 * j + e)) & 1u ? a[8 * j + e] : 0.f;
                         uint4 w4;
-                        w4.x = Pack2<T>::pack(mk[0], mk[1]); w4.y = Pack2<T>::pack(mk[2], mk[3]);
-                        w4.z = Pack2<T>::pack(mk[4], mk[5]); w4.w = Pack2<T>::pack(mk[6], mk[7]);
+                        w4.x = Pack2<T>::pack(a[8 * j], a[8 * j + 1]); w4.y = Pack2<T>::pack(a[8 * j + 2], a[8 * j + 3]);
+                        w4.z = Pack2<T>::pack(a[8 * j + 4], a[8 * j + 5]); w4.w = Pack2<T>::pack(a[8 * j + 6], a[8 * j + 7]);
                         *reinterpret_cast<uint4*>(prow + (((chunk0 + j) ^ (row & 7)) << 4)) = w4;
                     }
                 }
@@ -475,7 +474,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait(bar(B_PREPPED + s), (m / 3) & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -488,7 +487,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     gacc = 0.f;
                 } else {
                     uint32_t* cnt = wp.chain_cnt + cur.bh * 2 + cur.dir;
-                    if (lane == 0) global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag, p.status);
+                    if (lane == 0) global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag);
                     __syncwarp();
                     const float* box = wp.mailbox + (((size_t)cur.bh * 2 + cur.dir) * 2 + ((cur.w - 1) & 1)) * SLOT;
                     src = box;
@@ -515,7 +514,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_STREADY));
-            if (lane == 0) waiter.wait(bar(B_UFULL), m & 1);
+            if (lane == 0) waiter.wait_lite(bar(B_UFULL), m & 1);
             __syncwarp();
             tc_fence_after();
             {
@@ -565,6 +564,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     // ---- teardown: every role has left its loop; all MMAs were waited for by their consumers ----
     tc_fence_before();
     __syncthreads();
+    if (tid == 32 && *abort_flag && p.status) atomicOr(p.status, 1);   // a bounded wait ran out somewhere in this CTA
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(WT_COLS) : "memory");

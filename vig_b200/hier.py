@@ -30,6 +30,15 @@ class GLA2D(GatedLinearAttention):
         self.out_scale = 0.5
 
 
+def _conv(conv, x):
+    """Convolution through the library; fp32 inputs keep fp32 arithmetic (cuDNN would otherwise pick TF32, which misses
+    the 1e-4 bar of the fp32 path)."""
+    if x.dtype == torch.float32:
+        with torch.backends.cudnn.flags(enabled=True, allow_tf32=False):
+            return conv(x)
+    return conv(x)
+
+
 def _layer_norm(x, norm):
     """LayerNorm over the channels of token-major activations with the library's kernel."""
     return ops.layernorm_act(x.contiguous(), norm.weight, norm.bias, norm.eps)
@@ -89,7 +98,7 @@ class _Conv(nn.Module):
 
     def forward(self, x, hw):
         B, _, C = x.shape
-        y = self.conv(x.view(B, hw[0], hw[1], C).permute(0, 3, 1, 2))
+        y = _conv(self.conv, x.view(B, hw[0], hw[1], C).permute(0, 3, 1, 2))
         return y.permute(0, 2, 3, 1).reshape(B, -1, y.shape[1]), (y.shape[2], y.shape[3])
 
 
@@ -143,7 +152,7 @@ class HierViG(nn.Module):
         y = images.contiguous(memory_format=torch.channels_last)
         for m in pe:
             if isinstance(m, nn.Conv2d):
-                y = m(y)
+                y = _conv(m, y)
             elif isinstance(m, nn.LayerNorm):
                 y = F.layer_norm(y.permute(0, 2, 3, 1), m.normalized_shape, m.weight, m.bias, m.eps).permute(0, 3, 1, 2)
             elif isinstance(m, nn.GELU):
