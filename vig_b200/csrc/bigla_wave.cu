@@ -5,14 +5,18 @@
 // the state that enters an item was produced by an item with a smaller ticket, which is running or done.  States
 // pass from segment to segment through a two-slot mailbox per (sequence, direction) in global memory; the two
 // directions of a chunk meet in the output tensor: the direction that is scheduled first stores its half, the other
-// adds to it with a vector reduction once the first has raised the chunk's flag.
+// adds to it with a TMA reduction once the first has raised the chunk's flag.
 //
 // One persistent CTA per SM runs a pipeline over its stream of chunk iterations, roles decoupled by mbarriers:
 //
 //   load thread       work tickets; TMA loads of q, k, gates, v into a 3-stage ring
-//   MMA thread        all tcgen05.mma issue (both threads sit in a fifth warpgroup that is otherwise idle)
-//   8 prep warps      cumulative log-gates, q * 2^(G_i - G_ref) and k * 2^(G_ref - G_j) IN PLACE over the raw tiles
-//   4 score warps     scores TMEM -> masked bf16 tiles; output accumulators TMEM -> global (store or reduction)
+//   MMA thread        all tcgen05.mma issue
+//   16 prep warps     gate transform and cumulative log-gates (in registers), then q * 2^(G_i - G_ref) and
+//                     k * 2^(G_ref - G_j) IN PLACE over the raw tiles
+//                     (group sums exchanged through shared memory; every warp forms its own offset from them: code that
+//                     all sixteen run stays in the instruction cache, a seventeenth warp's would not)
+//   4 score warps     scores TMEM -> masked bf16 tiles; output accumulators TMEM -> 16-bit tile in shared memory
+//   store thread      output tile -> global by TMA (store, or reduction onto the other direction's half); chunk flags
 //   4 state warps     S <- 2^G_last S + 2^(G_last - G_ref) K~^T V in registers; bf16 state operand; mailbox
 //
 // Per iteration m (one chunk of 128 tokens, one direction), on the tensor core:
@@ -34,31 +38,37 @@ using namespace tc;
 
 constexpr int WDK = 64, WDV = 64;
 constexpr int W_SEG_CHUNKS = 2, W_SEG = CHUNK * W_SEG_CHUNKS;
-constexpr int W_PREP_WARPS = 8, W_THREADS = 20 * 32;      // five warpgroups: prep, prep, score, state, control
+// six warpgroups: workers x4, state, control (MMA warp, load thread, store thread)
+constexpr int W_PREP_WARPS = 16, W_STATE_WARP0 = 16, W_CTRL_WARP0 = 20, W_THREADS = 24 * 32;
+constexpr int W_MMA_WARP = W_CTRL_WARP0, W_LOAD_WARP = W_CTRL_WARP0 + 1, W_STORE_WARP = W_CTRL_WARP0 + 2;
 constexpr int W_STAGES = 3;
-// Registers per thread.  The kernel is compiled and launched with W_REGS_BASE for all five warpgroups (five warps
-// per scheduler allow no more); the control warpgroup gives most of its share back and the prep and score warpgroups
-// take it.  An increase waits until the registers are there, so the shares must never add up to more than was
-// launched with.
-constexpr int W_REGS_BASE = 96, W_REGS_PREP = 112, W_REGS_SCORE = 120, W_REGS_STATE = W_REGS_BASE, W_REGS_CTRL = 40;
-static_assert(2 * W_REGS_PREP + W_REGS_SCORE + W_REGS_STATE + W_REGS_CTRL <= 5 * W_REGS_BASE, "register shares exceed the launch allocation");
+// Registers per thread.  The kernel is compiled and launched with W_REGS_BASE for all six warpgroups; the control
+// warpgroup gives most of its share back and the state warpgroup takes it.  An increase waits until the registers are
+// there, so the shares must never add up to more than was launched with.
+constexpr int W_REGS_BASE = 80, W_REGS_WORK = W_REGS_BASE, W_REGS_STATE = 96, W_REGS_CTRL = 40;
+static_assert(4 * W_REGS_WORK + W_REGS_STATE + W_REGS_CTRL <= 6 * W_REGS_BASE, "register shares exceed the launch allocation");
 constexpr int W_TILE = CHUNK * 128;                           // 16 KB: 128 rows x 128 B
 constexpr int W_STAGE_B = 4 * W_TILE;                         // q | k | gates | v
 constexpr int WS_Q = 0, WS_K = W_TILE, WS_G = 2 * W_TILE, WS_V = 3 * W_TILE;
 constexpr int WO_X = W_STAGES * W_STAGE_B;                    // score tile of key columns 64..127 (0..63 go over the dead gate tile)
 constexpr int WO_ST = WO_X + W_TILE;                          // bf16 state operand, 64 rows x 128 B
-constexpr int WO_PART = WO_ST + 64 * 128;                     // fp32 [2][8][64] group sums of log-gates
-constexpr int WO_VEC = WO_PART + 2 * 8 * 64 * 4;              // fp32 [4][4][64]: 2^G_last, 2^(G_last-G_ref), G_ref, G_last per iteration
-constexpr int WO_ITEMS = WO_VEC + 4 * 4 * 64 * 4;             // ring of 8 work items x 8 ints
+constexpr int WO_PART = WO_ST + 64 * 128;                     // fp32 [2][16][64]: group sums of log-gates, turned in place into group offsets
+constexpr int WO_VEC = WO_PART + 2 * W_PREP_WARPS * 64 * 4;   // fp32 [4][2][64]: G_ref, G_last per iteration
+constexpr int WO_ITEMS = WO_VEC + 4 * 2 * 64 * 4;             // ring of 8 work items x 8 ints
 constexpr int WO_BAR = WO_ITEMS + 8 * 32;
 constexpr int WO_MISC = WO_BAR + 32 * 8;                      // tmem base, abort flag
-constexpr int W_SMEM_BYTES = WO_MISC + 16 + 1024;             // + slack for the manual 1024-byte alignment
+constexpr int W_SMEM_BYTES = WO_MISC + 16;                    // the dynamic shared memory must start on a 1024-byte boundary
+static_assert(W_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 // TMEM columns (fp32): scores, state update, two output slots
-constexpr uint32_t WT_P = 0, WT_U = 128, WT_O = 192, WT_COLS = 512;
+constexpr uint32_t WT_P = 0, WT_U = 128, WT_O = 256, WT_COLS = 512;   // U and O are double buffered (64 columns each)
 
 // mbarrier indices
-enum { B_FULL = 0, B_SFREE = 3, B_PREPPED = 6, B_PFULL = 9, B_PREADY = 10, B_STREADY = 11, B_UFULL = 12, B_OFULL = 13, B_OFREE = 15, B_PART = 17, B_COUNT = 18 };
+enum { B_FULL = 0, B_SFREE = 3, B_PREPPED = 6, B_PFULL = 9, B_PREADY = 10, B_STREADY = 11, B_UFULL = 12, B_OFULL = 14, B_OFREE = 16,
+       B_PART = 18, B_XFREE = 20, B_STFREE = 22, B_OSTAGED = 23, B_COUNT = 25 };
+static_assert(B_COUNT <= 32, "barrier slots");
+
+struct WaveMaps { CUtensorMap q, k, v, gf, gb, o; };
 
 struct WaveParams {
     BiglaParams p;
@@ -67,22 +77,19 @@ struct WaveParams {
     uint32_t* chunk_flag;  // [B*H][nseg*2]: score warps of the first direction that have stored the chunk (4 = done)
     float* mailbox;        // [B*H][2 dirs][2 slots][dk*dv + dk]
     int nseg;
+    float inv_per_step, inv_H;   // reciprocals for the ticket decode (a division costs twenty-odd instructions)
 };
 
-struct Item { int bh, seg, dir, nch, w, pad0, pad1, pad2; };
+// n / d and n % d for 0 <= n < 2^24 from a float reciprocal and two corrections.
+__device__ __forceinline__ void divmod(int n, int d, float inv_d, int& q, int& r) {
+    q = __float2int_rz(__int2float_rz(n) * inv_d);
+    r = n - q * d;
+    if (r >= d) { ++q; r -= d; }
+    if (r < 0) { --q; r += d; }
+}
 
+struct Item { int bh, seg, dir, nch, w, b, h, pad; };
 
-template <typename T> struct RedAdd;
-template <> struct RedAdd<__nv_bfloat16> {
-    __device__ static void v4(void* p, uint4 w) {
-        asm volatile("red.relaxed.gpu.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
-    }
-};
-template <> struct RedAdd<__half> {
-    __device__ static void v4(void* p, uint4 w) {
-        asm volatile("red.relaxed.gpu.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
-    }
-};
 
 // Bounded wait on a global counter (one lane polls).
 __device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, volatile int* abort_flag) {
@@ -96,12 +103,34 @@ __device__ __forceinline__ void global_wait(const uint32_t* ctr, uint32_t need, 
 }
 
 
-template <typename T>
-__global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_constant__ TcMaps maps, const WaveParams wp) {
+// Operand scaling: a raw 16-bit pair times two fp32 scales.
+template <typename T> struct ScalePair;
+template <> struct ScalePair<__nv_bfloat16> {
+    // bf16 has fp32's exponent range, so the scales themselves fit: round them to bf16 and multiply packed (two
+    // roundings per operand element instead of one, no unpack / repack: the preparation warps are bound by issue slots)
+    __device__ static uint32_t mul(uint32_t raw, float s0, float s1) {
+        const __nv_bfloat162 sc = __floats2bfloat162_rn(s0, s1);
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&raw), sc);
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+};
+template <> struct ScalePair<__half> {
+    // fp16 cannot hold the scales (up to 2^115): product in fp32, one rounding
+    __device__ static uint32_t mul(uint32_t raw, float s0, float s1) {
+        const float2 f = Pack2<__half>::unpack(raw);
+        return Pack2<__half>::pack(f.x * s0, f.y * s1);
+    }
+};
+
+template <typename T, bool RAW, bool CLAMP>
+__global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_constant__ WaveMaps maps, const WaveParams wp) {
     const BiglaParams& p = wp.p;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
+    if (sbase & 1023u) {                                      // the swizzled tiles need it; never seen, but checked
+        if (threadIdx.x == 0 && p.status) atomicOr(p.status, 1);
+        return;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nseg = wp.nseg;
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, ndir = (p.dir_mask == 3) ? 2 : 1;
@@ -116,9 +145,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
 
     if (tid == 0) {
         for (int i = 0; i < 3; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_SFREE + i), 1); mbar_init(bar(B_PREPPED + i), W_PREP_WARPS); }
-        mbar_init(bar(B_PART), W_PREP_WARPS);
-        mbar_init(bar(B_PFULL), 1); mbar_init(bar(B_PREADY), 4); mbar_init(bar(B_STREADY), 4); mbar_init(bar(B_UFULL), 1);
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_OFULL + i), 1); mbar_init(bar(B_OFREE + i), 4); }
+        for (int i = 0; i < 2; ++i) mbar_init(bar(B_PART + i), W_PREP_WARPS);
+        mbar_init(bar(B_XFREE), 1);
+        mbar_init(bar(B_PFULL), 1); mbar_init(bar(B_PREADY), W_PREP_WARPS); mbar_init(bar(B_STREADY), 4); mbar_init(bar(B_STFREE), 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_OFULL + i), 1); mbar_init(bar(B_OFREE + i), W_PREP_WARPS); mbar_init(bar(B_UFULL + i), 1); mbar_init(bar(B_OSTAGED + i), W_PREP_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -143,42 +173,58 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     constexpr uint32_t IDESC_OV = make_idesc(Pack2<T>::FMT, 0, 1, 128, 64);
     constexpr uint32_t IDESC_U = make_idesc(Pack2<T>::FMT, 1, 1, 64, 64);
 
-    if (warp >= 16) {
+    if (warp >= W_CTRL_WARP0) {
         // =============================== control warpgroup ===============================
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(W_REGS_CTRL));
-        if (tid == 17 * 32) {
+        if (tid == W_LOAD_WARP * 32) {
             // ---- load thread: work tickets and TMA loads, up to W_STAGES iterations ahead of the tensor core ----
+            auto decode = [&](int t, Item& it) {               // ticket -> work item (nch = 0: no more work)
+                it.nch = 0;
+                if (t < total) {
+                    int r;
+                    divmod(t, per_step, wp.inv_per_step, it.w, r);
+                    it.bh = ndir == 2 ? r >> 1 : r;
+                    it.dir = dir_first + (ndir == 2 ? r & 1 : 0);
+                    divmod(it.bh, p.H, wp.inv_H, it.b, it.h);
+                    it.seg = it.dir ? nseg - 1 - it.w : it.w;
+                    it.nch = min(W_SEG_CHUNKS, (p.L - it.seg * W_SEG + CHUNK - 1) / CHUNK);
+                }
+            };
+            // A ticket is drawn two items before its loads are issued.  One item before, when its value has long arrived,
+            // it is decoded and its tiles are asked into L2, so the loads that fill the 3-stage ring later find them there
+            // (the ring alone does not cover DRAM latency).
+            Item lcur, lnext;
+            lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = lcur.b = lcur.h = 0; lnext = lcur;
             int tk = (int)atomicAdd(wp.ticket, 1u);
-            int tk_next = (int)atomicAdd(wp.ticket, 1u);       // consumed one item later: its round trip costs no stall
-            Item lcur; lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = 0;
-            int l_items = 0, l_ci = 0;
+            int l_items = -1, l_ci = 0;                        // the first pass through the item block only fills lnext
             #pragma unroll 1
             for (uint32_t lm = 0;; ++lm, ++l_ci) {
-                if (l_ci == lcur.nch) {                        // next work item
-                    const int t = tk;
-                    tk = tk_next;
-                    tk_next = (int)atomicAdd(wp.ticket, 1u);
-                    if (t < total) {
-                        lcur.w = t / per_step;
-                        const int r = t % per_step;
-                        lcur.bh = r / ndir;
-                        lcur.dir = dir_first + r % ndir;
-                        lcur.seg = lcur.dir ? nseg - 1 - lcur.w : lcur.w;
-                        lcur.nch = min(W_SEG_CHUNKS, (p.L - lcur.seg * W_SEG + CHUNK - 1) / CHUNK);
-                    } else {
-                        lcur.nch = 0;
+                while (l_ci == lcur.nch) {                     // next work item (twice at the start)
+                    lcur = lnext;
+                    if (l_items >= 0) {
+                        volatile Item* r = ring + (l_items & 7);
+                        r->bh = lcur.bh; r->seg = lcur.seg; r->dir = lcur.dir; r->nch = lcur.nch; r->w = lcur.w; r->b = lcur.b; r->h = lcur.h;
                     }
-                    volatile Item* r = ring + (l_items & 7);
-                    r->bh = lcur.bh; r->seg = lcur.seg; r->dir = lcur.dir; r->nch = lcur.nch; r->w = lcur.w;
                     ++l_items;
                     l_ci = 0;
+                    decode(tk, lnext);                         // the item after this one
+                    tk = (int)atomicAdd(wp.ticket, 1u);        // and the ticket of the one after that: consumed an item later
+#pragma unroll 1
+                    for (int c = 0; c < lnext.nch; ++c) {
+                        const int t0 = lnext.seg * W_SEG + c * CHUNK;
+                        tma_prefetch_4d(&maps.k, 0, t0, lnext.h, lnext.b);
+                        tma_prefetch_4d(lnext.dir ? &maps.gb : &maps.gf, 0, t0, lnext.h, lnext.b);
+                        tma_prefetch_4d(&maps.q, 0, t0, lnext.h, lnext.b);
+                        tma_prefetch_4d(&maps.v, 0, t0, lnext.h, lnext.b);
+                    }
+                    if (l_items > 0) break;                    // a real item is in lcur (an empty one ends the stream below)
                 }
                 const uint32_t s = lm % 3;
                 if (lm >= 3) waiter.wait_lite(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
                 if (*abort_flag) break;
                 if (lcur.nch == 0) { mbar_arrive_plain(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
                 const int t0 = lcur.seg * W_SEG + chunk_of(lcur, l_ci) * CHUNK;
-                const int b = lcur.bh / p.H, h = lcur.bh % p.H;
+                const int b = lcur.b, h = lcur.h;
                 const uint32_t dst = sbase + s * W_STAGE_B, fb = bar(B_FULL + s);
                 mbar_expect_tx(fb, W_STAGE_B);
                 tma_load_4d(dst + WS_K, &maps.k, 0, t0, h, b, fb);
@@ -186,280 +232,325 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 tma_load_4d(dst + WS_Q, &maps.q, 0, t0, h, b, fb);
                 tma_load_4d(dst + WS_V, &maps.v, 0, t0, h, b, fb);
             }
-        } else if (tid == 16 * 32) {
-            // ---- MMA thread ----
+        } else if (warp == W_MMA_WARP) {
+            // ---- MMA warp: all 32 lanes walk the loop (uniform control flow keeps the descriptor arithmetic in the
+            // uniform datapath, off the issuing lane's critical path); lane 0 issues ----
             Item mcur; mcur.nch = 0; mcur.bh = mcur.seg = mcur.dir = mcur.w = 0;
             int m_items = 0, m_ci = 0;
+            const uint32_t st_lo = make_desc(sbase + WO_ST);
             #pragma unroll 1
             for (uint32_t m = 0;; ++m, ++m_ci) {
                 const uint32_t s = m % 3, st = sbase + s * W_STAGE_B;
                 waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);  // also orders the read of the work item after its write
                 if (*abort_flag) break;
                 if (m_ci == mcur.nch) { read_item(m_items, mcur); ++m_items; m_ci = 0; }
-                if (mcur.nch == 0) { mbar_arrive_plain(bar(B_PFULL)); break; }      // end marker: wakes the score warps
-                const uint32_t qt = st + WS_Q, kt = st + WS_K, vt = st + WS_V, p0 = st + WS_G, p1 = sbase + WO_X, stt = sbase + WO_ST;
-                const uint32_t o_acc = tmem + WT_O + 64u * (m & 1u);
+                if (mcur.nch == 0) break;
+                // descriptor low words (16-byte units): +2 = 32 bytes along K inside a 128-byte row, +128 = 16 rows
+                const uint32_t q_lo = make_desc(st + WS_Q), k_lo = make_desc(st + WS_K), v_lo = make_desc(st + WS_V), p0_lo = make_desc(st + WS_G);
+                const uint32_t p1_lo = k_lo;                   // masked scores of key columns 64..127 go over the k tile once U has read it
+                const uint32_t o_acc = tmem + WT_O + 64u * (m & 1u), u_acc = tmem + WT_U + 64u * (m & 1u);
                 const bool s_zero = state_zero(mcur, m_ci);
-                // (a) scores
                 tc_fence_after();
+                if (lane == 0) {
+                    // (a) scores, and right behind them the state update: it needs only the prepared tiles, and the
+                    // state chain -- the one sequential dependency of the kernel -- waits for nothing else
 #pragma unroll 1
-                for (int k4 = 0; k4 < WDK / 16; ++k4) tc_mma(tmem + WT_P, make_desc(qt + k4 * 32), make_desc(kt + k4 * 32), IDESC_QK, k4 > 0);
-                tc_commit(bar(B_PFULL));
+                    for (uint32_t k4 = 0; k4 < WDK / 16; ++k4) tc_mma(tmem + WT_P, q_lo + 2 * k4, k_lo + 2 * k4, IDESC_QK, k4 > 0);
+                    tc_commit(bar(B_PFULL));
+#pragma unroll 1
+                    for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) tc_mma(u_acc, k_lo + 128 * k8, v_lo + 128 * k8, IDESC_U, k8 > 0);
+                    tc_commit(bar(B_UFULL + (m & 1u)));
+                }
                 // (b) product with the entering state
                 waiter.wait_lite(bar(B_STREADY), m & 1);
                 if (m >= 2) waiter.wait_lite(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
                 tc_fence_after();
-                if (!s_zero) {
+                if (lane == 0) {
+                    if (!s_zero) {
 #pragma unroll 1
-                    for (int k4 = 0; k4 < WDK / 16; ++k4) tc_mma(o_acc, make_desc(qt + k4 * 32), make_desc(stt + k4 * 2048), IDESC_OV, k4 > 0);
+                        for (uint32_t k4 = 0; k4 < WDK / 16; ++k4) tc_mma(o_acc, q_lo + 2 * k4, st_lo + 128 * k4, IDESC_OV, k4 > 0);
+                    }
+                    tc_commit(bar(B_STFREE));                  // the state operand may be overwritten
                 }
-                // (c) masked scores x v, state update
+                // (c) masked scores x v
                 waiter.wait_lite(bar(B_PREADY), m & 1);
                 tc_fence_after();
+                if (lane == 0) {
 #pragma unroll 1
-                for (int k8 = 0; k8 < CHUNK / 16; ++k8)
-                    tc_mma(o_acc, make_desc((k8 < 4 ? p0 : p1) + (k8 & 3) * 32), make_desc(vt + k8 * 2048), IDESC_OV, !s_zero || k8 > 0);
-                tc_commit(bar(B_OFULL + (m & 1)));
-#pragma unroll 1
-                for (int k8 = 0; k8 < CHUNK / 16; ++k8)
-                    tc_mma(tmem + WT_U, make_desc(kt + k8 * 2048), make_desc(vt + k8 * 2048), IDESC_U, k8 > 0);
-                tc_commit(bar(B_UFULL));
-                tc_commit(bar(B_SFREE + s));
+                    for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8)
+                        tc_mma(o_acc, (k8 < 4 ? p0_lo : p1_lo) + 2 * (k8 & 3), v_lo + 128 * k8, IDESC_OV, !s_zero || k8 > 0);
+                    tc_commit(bar(B_OFULL + (m & 1)));
+                    tc_commit(bar(B_SFREE + s));
+                }
+                __syncwarp();
             }
+        } else if (tid == W_STORE_WARP * 32) {
+            // ---- store thread: the output tile of iteration j, staged by the score warps, goes out as one TMA store (first direction to reach the chunk) or one TMA reduction (second).
+            // The global-memory latencies of the hand-over between the directions (write complete -> flag; flag -> add)
+            // are spent here, by a thread that has nothing else to do.
+            Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
+            int items = 0, ci = 0;
+            #pragma unroll 1
+            for (uint32_t j = 0;; ++j, ++ci) {
+                waiter.wait_lite(bar(B_OSTAGED + (j & 1)), (j >> 1) & 1);
+                if (*abort_flag) break;
+                if (ci == cur.nch) { read_item(items, cur); cur.b = ring[items & 7].b; cur.h = ring[items & 7].h; ++items; ci = 0; }
+                if (cur.nch == 0) break;
+                const int c = chunk_of(cur, ci);
+                const int t0 = cur.seg * W_SEG + c * CHUNK, b = cur.b, h = cur.h;
+                const int w_other = nseg - 1 - cur.w;
+                const bool first = ndir == 1 || cur.w < w_other || (cur.w == w_other && cur.dir == 0);
+                uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * nseg * W_SEG_CHUNKS + cur.seg * W_SEG_CHUNKS + c;
+                const uint32_t src = sbase + WO_X;
+                if (first) {
+                    tma_store_4d(&maps.o, 0, t0, h, b, src);     // rows past L are clipped by the tensor map
+                } else {
+                    global_wait(flag, 1u, abort_flag); // the other direction's half must be in place
+                    tma_reduce_add_4d(&maps.o, 0, t0, h, b, src);
+                }
+                bulk_commit();
+                bulk_store_wait_read();
+                mbar_arrive_plain(bar(B_XFREE));                 // the tile may take the next iteration's scores
+                if (first && ndir == 2) {                      // publish my half of the chunk once it is written
+                    bulk_store_wait_all();
+                    __threadfence();
+                    atomicAdd(flag, 1u);
+                }
+            }
+            bulk_store_wait_all();
         }
     } else if (warp < W_PREP_WARPS) {
         // =============================== prep warps: gates and operand scaling, in place ===============================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(W_REGS_PREP));
-        constexpr int NG = 8;                                 // groups (of 16 tokens, one per warp) per chunk
+        // A warp owns 8 tokens (one group), a half-warp 4 consecutive scan positions, a lane 4 channels of them
+        // (8-byte shared-memory accesses: a half-warp covers one 128-byte token row).  Scan position sp = 4*half + u is
+        // token 8*warp + (sp ^ dmask): the same code serves both directions.  Gate form (raw logits or log-gates) and the
+        // lower clamp are template parameters: the token loops carry no branch, so their 16 elements overlap.
         const int grp = warp;
-        const bool raw_logits = p.gate_norm > 0.f;
-        const float inv_norm = raw_logits ? 1.f / p.gate_norm : 1.f;
-        const float clamp_lo = (p.clamp_min == p.clamp_min) ? p.clamp_min * LOG2E : -INFINITY;
+        const float coef = RAW ? -1.f / p.gate_norm : LOG2E;  // log2-gate = coef * (RAW ? log2(1 + 2^(-x log2 e)) : x)
+        const float clamp_lo = CLAMP ? p.clamp_min * LOG2E : -INFINITY;
+        const int half = lane >> 4, c4l = lane & 15;          // my half of the group, my 4 channels: 4*c4l .. 4*c4l+3
+        const uint32_t sw_in = (uint32_t)(c4l & 1) * 8, chunk = (uint32_t)c4l >> 1;
+        // The same warps mask the scores of the iteration before and stage the output of the one before that (a warp owns
+        // the 32 query rows of its TMEM lane quadrant and a quarter of the columns): by the time a trip reaches them the
+        // tensor core has long finished what they need, sixteen warps share work that four would serialise, and the SM
+        // runs one big instruction stream instead of two.
+        const int quad = warp & 3, sub = warp >> 2;           // my TMEM lane quadrant; my quarter of the key blocks / output columns
+        const int row = 32 * quad + lane;
+        const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
+        const float o_sign = p.qscale;                        // scale * out_scale, applied to the finished accumulators
         Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
-        int items = 0, ci = 0;
+        int items = 0, ci = -1, dir_prev = 0;
+        bool ended = false;
+        uint32_t end_m = 0;                                   // first iteration that does not exist
         #pragma unroll 1
-        for (uint32_t m = 0;; ++m, ++ci) {
+        for (uint32_t m = 0;; ++m) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
+            bool have = false;
+            const int dir_mask_it = dir_prev;                 // direction of iteration m - 1 (the one whose scores are masked in this trip)
+            if (!ended) {
+            waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
-            if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
-            if (cur.nch == 0) { if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s)); break; }
+            ++ci;
+            if (ci == cur.nch || cur.nch == 0) { read_item(items, cur); ++items; ci = 0; }
+            if (cur.nch == 0) {                               // end marker: pass it on to the MMA warp and the state warps
+                if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s));
+                ended = true; end_m = m;
+            } else {
+            have = true;
+            dir_prev = cur.dir;
             uint8_t* stg = smem + s * W_STAGE_B;
-            const uint32_t* sg = reinterpret_cast<const uint32_t*>(stg + WS_G);
-            float* part = reinterpret_cast<float*>(smem + WO_PART) + (m & 1) * (NG * WDK);
             const int t0 = cur.seg * W_SEG + chunk_of(cur, ci) * CHUNK;
             const int n_valid = p.L - t0;                     // rows at or past it are padding: decay 1
-            // ONE code path for both directions and for clamped / padded chunks (runtime selects instead of template
-            // variants): the five roles of this CTA run different code at the same time, and what does not fit the
-            // instruction cache stalls all of them.
-            // A warp owns 16 tokens (one group); a half-warp covers one token row with 4 channels per lane (8-byte
-            // accesses), so a lane handles 8 consecutive scan positions x 4 channels and the per-token overhead
-            // (addresses, padding test) is paid once per 4 channels.  Scan position sp = 8*half + u is token
-            // 16*warp + (sp ^ dmask).
-            const int dir = cur.dir;
-            const int dmask = dir ? 15 : 0;
-            const int half = lane >> 4, c4l = lane & 15;      // my half of the group, my 4 channels: 4*c4l .. 4*c4l+3
-            const uint32_t sw_chunk = (uint32_t)c4l >> 1, sw_in = (uint32_t)(c4l & 1) * 8;
-            float4 half_off;                                  // sum of the other half-warp's tokens when they precede mine in the scan
-            // The 8 tokens of a lane are handled as two halves of 4 by loops that run twice; the cumulative gates of the
-            // halves rotate through two register arrays (glA = first half, glB = second), so the loop bodies are half the
-            // code of a full unroll while four tokens x four channels still overlap their latencies.
-            float4 glA[4], glB[4];
+            const int dmask = cur.dir ? 7 : 0;
+            // ---- gate phase: transform, running sums over my 4 tokens, group sum published ----
+            float4 gl[4];                                     // cumulative log2-gates of my 4 tokens, from the group's first token
             {
+                uint2 raw[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    raw[u] = *reinterpret_cast<const uint2*>(stg + WS_G + (grp * 8 + ((half * 4 + u) ^ dmask)) * 128 + c4l * 8);
                 float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-                for (int hh = 0; hh < 2; ++hh) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) glA[i] = glB[i];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int tok = warp * 16 + ((half * 8 + hh * 4 + i) ^ dmask);
-                        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(sg) + tok * 128 + c4l * 8);
-                        const float2 a = Pack2<T>::unpack(raw.x), b2 = Pack2<T>::unpack(raw.y);
-                        float4 g;
-                        g.x = fmaxf(gate2_short(a.x, raw_logits, -inv_norm), clamp_lo);
-                        g.y = fmaxf(gate2_short(a.y, raw_logits, -inv_norm), clamp_lo);
-                        g.z = fmaxf(gate2_short(b2.x, raw_logits, -inv_norm), clamp_lo);
-                        g.w = fmaxf(gate2_short(b2.y, raw_logits, -inv_norm), clamp_lo);
-                        if (tok >= n_valid) g = make_float4(0.f, 0.f, 0.f, 0.f);
-                        run.x += g.x; run.y += g.y; run.z += g.z; run.w += g.w;
-                        glB[i] = run;
+                for (int u = 0; u < 4; ++u) {
+                    const float2 a = Pack2<T>::unpack(raw[u].x), b2 = Pack2<T>::unpack(raw[u].y);
+                    float4 t = make_float4(a.x, a.y, b2.x, b2.y);
+                    if (RAW) {                                // log2(1 + 2^(-x log2 e)) = -log2 sigmoid(x)
+                        t.x = lg2(1.f + ex2(t.x * -LOG2E)); t.y = lg2(1.f + ex2(t.y * -LOG2E));
+                        t.z = lg2(1.f + ex2(t.z * -LOG2E)); t.w = lg2(1.f + ex2(t.w * -LOG2E));
                     }
+                    const float cu = grp * 8 + ((half * 4 + u) ^ dmask) < n_valid ? coef : 0.f;   // padding rows: gate 0
+                    if (CLAMP) {
+                        run.x += fmaxf(t.x * cu, clamp_lo); run.y += fmaxf(t.y * cu, clamp_lo);
+                        run.z += fmaxf(t.z * cu, clamp_lo); run.w += fmaxf(t.w * cu, clamp_lo);
+                    } else {
+                        run.x = fmaf(t.x, cu, run.x); run.y = fmaf(t.y, cu, run.y);
+                        run.z = fmaf(t.z, cu, run.z); run.w = fmaf(t.w, cu, run.w);
+                    }
+                    gl[u] = run;
                 }
                 // the second half-warp continues the first half-warp's sum; it also knows the group's total
                 float4 first;
                 first.x = __shfl_sync(0xffffffffu, run.x, c4l); first.y = __shfl_sync(0xffffffffu, run.y, c4l);
                 first.z = __shfl_sync(0xffffffffu, run.z, c4l); first.w = __shfl_sync(0xffffffffu, run.w, c4l);
-                if (half) reinterpret_cast<float4*>(part)[grp * 16 + c4l] = make_float4(run.x + first.x, run.y + first.y, run.z + first.z, run.w + first.w);
-                if (!half) first = make_float4(0.f, 0.f, 0.f, 0.f);
-                half_off = first;                             // joins the group offset below
-            }
-            // the prep warps meet on an mbarrier, not a named barrier: its wait is bounded like every other wait here
-            __syncwarp();
-            if (lane == 0) { mbar_arrive_plain(bar(B_PART)); waiter.wait_lite(bar(B_PART), m & 1); }
-            __syncwarp();
-            float4 off = half_off, gref = make_float4(0.f, 0.f, 0.f, 0.f), glast = gref;
-#pragma unroll 2
-            for (int g2 = 0; g2 < NG; ++g2) {
-                const float4 s4 = reinterpret_cast<const float4*>(part)[g2 * 16 + c4l];
-                const bool before = dir ? g2 > grp : g2 < grp;            // scanned before my group
-                const bool in_ref = dir ? g2 >= NG / 2 : g2 < NG / 2;     // part of the cumulative gate at the middle token
-                if (before) { off.x += s4.x; off.y += s4.y; off.z += s4.z; off.w += s4.w; }
-                if (in_ref) { gref.x += s4.x; gref.y += s4.y; gref.z += s4.z; gref.w += s4.w; }
-                glast.x += s4.x; glast.y += s4.y; glast.z += s4.z; glast.w += s4.w;
-            }
-            off.x -= gref.x; off.y -= gref.y; off.z -= gref.z; off.w -= gref.w;
-            // Log-gates are <= 0, so a lane's exponents are monotone along its 8 tokens: the largest magnitude (for the
-            // status flag; every exponent is clamped regardless) is at one of the two ends.
-            float worst = fmaxf(fmaxf(fabsf(off.x + glA[0].x), fabsf(off.y + glA[0].y)), fmaxf(fabsf(off.z + glA[0].z), fabsf(off.w + glA[0].w)));
-            worst = fmaxf(worst, fmaxf(fmaxf(fabsf(off.x + glB[3].x), fabsf(off.y + glB[3].y)), fmaxf(fabsf(off.z + glB[3].z), fabsf(off.w + glB[3].w))));
-            auto clampx = [](float e) { return fminf(fmaxf(e, -MAX_EXPONENT2), MAX_EXPONENT2); };
-#pragma unroll 1
-            for (int hh = 0; hh < 2; ++hh) {
-                uint2 rk[4], rq[4];
-                uint32_t offs[4];
+                float* part = reinterpret_cast<float*>(smem + WO_PART) + (m & 1) * (W_PREP_WARPS * WDK);
+                if (half) {
+                    reinterpret_cast<float4*>(part)[grp * 16 + c4l] = make_float4(run.x + first.x, run.y + first.y, run.z + first.z, run.w + first.w);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {                 // all reads before the writes: the tiles alias for the compiler
-                    const uint32_t tok = (uint32_t)(warp * 16 + ((half * 8 + hh * 4 + i) ^ dmask));
-                    offs[i] = tok * 128 + ((sw_chunk ^ (tok & 7)) << 4) + sw_in;
-                    rk[i] = *reinterpret_cast<const uint2*>(stg + WS_K + offs[i]);
-                    rq[i] = *reinterpret_cast<const uint2*>(stg + WS_Q + offs[i]);
+                    for (int u = 0; u < 4; ++u) { gl[u].x += first.x; gl[u].y += first.y; gl[u].z += first.z; gl[u].w += first.w; }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_PART + (m & 1)));
+            }
+            // ---- raw operand rows into registers while the other warps finish their group sums ----
+            uint2 rk[4], rq[4];
+            uint32_t offs[4];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float ex = clampx(off.x + glA[i].x), ey = clampx(off.y + glA[i].y), ez = clampx(off.z + glA[i].z), ew = clampx(off.w + glA[i].w);
-                    // fp32 products, one rounding to the 16-bit operand; scale * out_scale is applied to the output instead
-                    const float2 k0 = Pack2<T>::unpack(rk[i].x), k1 = Pack2<T>::unpack(rk[i].y);
-                    const float2 q0 = Pack2<T>::unpack(rq[i].x), q1 = Pack2<T>::unpack(rq[i].y);
-                    uint2 ko, qo;
-                    ko.x = Pack2<T>::pack(k0.x * ex2(-ex), k0.y * ex2(-ey)); ko.y = Pack2<T>::pack(k1.x * ex2(-ez), k1.y * ex2(-ew));
-                    qo.x = Pack2<T>::pack(q0.x * ex2(ex), q0.y * ex2(ey)); qo.y = Pack2<T>::pack(q1.x * ex2(ez), q1.y * ex2(ew));
-                    *reinterpret_cast<uint2*>(stg + WS_K + offs[i]) = ko;
-                    *reinterpret_cast<uint2*>(stg + WS_Q + offs[i]) = qo;
+            for (int u = 0; u < 4; ++u) {
+                const uint32_t r7 = (uint32_t)((half * 4 + u) ^ dmask);
+                offs[u] = (uint32_t)(grp * 8 + r7) * 128 + ((chunk ^ r7) << 4) + sw_in;
+                rk[u] = *reinterpret_cast<const uint2*>(stg + WS_K + offs[u]);
+                rq[u] = *reinterpret_cast<const uint2*>(stg + WS_Q + offs[u]);
+            }
+            waiter.wait_lite(bar(B_PART + (m & 1)), (m >> 1) & 1);     // all sixteen group sums are in
+            __syncwarp();
+            if (*abort_flag) break;
+            // ---- my group's offset: (sum of the groups scanned before mine) - G_ref, G_ref = sum of the first 8 groups in
+            // scan order.  Half-warp gq reads groups 8 gq .. 8 gq + 7 (scan order) for its 4 channels; one exchange. ----
+            float4 off;
+            {
+                const float4* part = reinterpret_cast<const float4*>(smem + WO_PART) + (m & 1) * (W_PREP_WARPS * 16) + c4l;
+                const int flip = cur.dir ? W_PREP_WARPS - 1 : 0;          // scan position go <-> group go ^ flip
+                const int mygo = grp ^ flip;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f), bef = sum;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int go = half * 8 + i;
+                    const float4 t = part[(go ^ flip) * 16];
+                    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+                    const float k = go < mygo ? 1.f : 0.f;
+                    bef.x = fmaf(k, t.x, bef.x); bef.y = fmaf(k, t.y, bef.y); bef.z = fmaf(k, t.z, bef.z); bef.w = fmaf(k, t.w, bef.w);
                 }
+                float4 osum, obef;
+                osum.x = __shfl_xor_sync(0xffffffffu, sum.x, 16); osum.y = __shfl_xor_sync(0xffffffffu, sum.y, 16);
+                osum.z = __shfl_xor_sync(0xffffffffu, sum.z, 16); osum.w = __shfl_xor_sync(0xffffffffu, sum.w, 16);
+                obef.x = __shfl_xor_sync(0xffffffffu, bef.x, 16); obef.y = __shfl_xor_sync(0xffffffffu, bef.y, 16);
+                obef.z = __shfl_xor_sync(0xffffffffu, bef.z, 16); obef.w = __shfl_xor_sync(0xffffffffu, bef.w, 16);
+                const float4 gref = half ? osum : sum;                    // the half-warp that read the first 8 groups has it
+                off = make_float4(bef.x + obef.x - gref.x, bef.y + obef.y - gref.y, bef.z + obef.z - gref.z, bef.w + obef.w - gref.w);
+                if (grp == 0 && half == 0) {                              // [G_ref | G_last] of this iteration for the state warps
+                    float4* ve = reinterpret_cast<float4*>(vec + (m & 3) * 128) + c4l;
+                    ve[0] = gref;
+                    ve[16] = make_float4(sum.x + osum.x, sum.y + osum.y, sum.z + osum.z, sum.w + osum.w);
+                }
+            }
+            // ---- scale phase ----
+            // Log-gates are <= 0, so a lane's exponents are monotone along its 4 tokens: the largest magnitude is at one
+            // of the two ends.  Beyond the range the factorisation covers, exponents are clamped and the call is flagged.
+            float worst = fmaxf(fmaxf(fabsf(off.x + gl[0].x), fabsf(off.y + gl[0].y)), fmaxf(fabsf(off.z + gl[0].z), fabsf(off.w + gl[0].w)));
+            worst = fmaxf(worst, fmaxf(fmaxf(fabsf(off.x + gl[3].x), fabsf(off.y + gl[3].y)), fmaxf(fabsf(off.z + gl[3].z), fabsf(off.w + gl[3].w))));
+            const bool out_of_range = __any_sync(0xffffffffu, !(worst <= MAX_EXPONENT2));
+            if (out_of_range) {                               // rare: clamp in place, flag the call
+                if (lane == 0 && p.status) atomicOr(p.status, 2);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) glA[i] = glB[i];
+                for (int u = 0; u < 4; ++u) {
+                    gl[u].x = fminf(fmaxf(off.x + gl[u].x, -MAX_EXPONENT2), MAX_EXPONENT2) - off.x;
+                    gl[u].y = fminf(fmaxf(off.y + gl[u].y, -MAX_EXPONENT2), MAX_EXPONENT2) - off.y;
+                    gl[u].z = fminf(fmaxf(off.z + gl[u].z, -MAX_EXPONENT2), MAX_EXPONENT2) - off.z;
+                    gl[u].w = fminf(fmaxf(off.w + gl[u].w, -MAX_EXPONENT2), MAX_EXPONENT2) - off.w;
+                }
             }
-            if (grp == 0 && half == 0) {                      // per-channel factors of this iteration for the state warps
-                float* ve = vec + (m & 3) * 256 + 4 * c4l;
-                *reinterpret_cast<float4*>(ve) = make_float4(ex2(glast.x), ex2(glast.y), ex2(glast.z), ex2(glast.w));
-                *reinterpret_cast<float4*>(ve + 64) = make_float4(ex2(glast.x - gref.x), ex2(glast.y - gref.y), ex2(glast.z - gref.z), ex2(glast.w - gref.w));
-                *reinterpret_cast<float4*>(ve + 128) = gref;
-                *reinterpret_cast<float4*>(ve + 192) = glast;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float ex = off.x + gl[u].x, ey = off.y + gl[u].y, ez = off.z + gl[u].z, ew = off.w + gl[u].w;
+                uint2 ko, qo;                                 // scale * out_scale is applied to the output instead
+                ko.x = ScalePair<T>::mul(rk[u].x, ex2(-ex), ex2(-ey)); ko.y = ScalePair<T>::mul(rk[u].y, ex2(-ez), ex2(-ew));
+                qo.x = ScalePair<T>::mul(rq[u].x, ex2(ex), ex2(ey)); qo.y = ScalePair<T>::mul(rq[u].y, ex2(ez), ex2(ew));
+                *reinterpret_cast<uint2*>(stg + WS_K + offs[u]) = ko;
+                *reinterpret_cast<uint2*>(stg + WS_Q + offs[u]) = qo;
             }
-            const bool out_of_range = worst > MAX_EXPONENT2;
-            if (out_of_range && p.status) atomicOr(p.status, 2);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s));
-        }
-    } else if (warp < W_PREP_WARPS + 4) {
-        // =============================== score warps: masking, output ===============================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(W_REGS_SCORE));
-        const int quad = warp & 3;                            // my 32 query rows and TMEM lanes
-        const int row = 32 * quad + lane;
-        const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
-        const float o_sign = p.qscale;                        // scale * out_scale, applied to the finished accumulators
-        Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
-        Item prev = cur;
-        int items = 0, ci = 0, prev_ci = 0;
-        // output of iteration j: accumulator slot j & 1 -> global
-        auto epilogue = [&](uint32_t j, const Item& it, int jci) {
-            if (lane == 0) waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
-            __syncwarp();
-            tc_fence_after();
-            const int c = chunk_of(it, jci);
-            const int tok = it.seg * W_SEG + c * CHUNK + row;
-            const int w_other = nseg - 1 - it.w;
-            const bool first = ndir == 1 || it.w < w_other || (it.w == w_other && it.dir == 0);
-            uint32_t* flag = wp.chunk_flag + (size_t)it.bh * nseg * W_SEG_CHUNKS + it.seg * W_SEG_CHUNKS + c;
-            if (!first) {                                     // the other direction's half must be in place
-                if (lane == 0) global_wait(flag, 4u, abort_flag);
+            }
+            }
+            (void)have;
+            // ---- scores of iteration j = m - 1: TMEM -> masked 16-bit tiles (my 32 rows x key block `sub`) ----
+            if (m >= 1 && (!ended || m - 1 < end_m)) {
+                const uint32_t j = m - 1;
+                waiter.wait_lite(bar(B_PFULL), j & 1);
                 __syncwarp();
-            }
-            T* obase = reinterpret_cast<T*>(p.o) + (it.bh / p.H) * p.so[0] + (it.bh % p.H) * p.so[1] + (int64_t)tok * p.so[2];
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-                float a[32];
-                tc_ld32(tmem + lane_base + WT_O + 64u * (j & 1u) + 32 * half, a);
-                tc_wait_ld();
-                if (half == 1) {                              // the slot is read: hand it back before the global traffic
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_plain(bar(B_OFREE + (j & 1)));
-                }
-                if (tok < p.L) {
-#pragma unroll
-                    for (int q4 = 0; q4 < 32; q4 += 8) {
-                        uint4 w4;
-                        w4.x = Pack2<T>::pack(o_sign * a[q4], o_sign * a[q4 + 1]); w4.y = Pack2<T>::pack(o_sign * a[q4 + 2], o_sign * a[q4 + 3]);
-                        w4.z = Pack2<T>::pack(o_sign * a[q4 + 4], o_sign * a[q4 + 5]); w4.w = Pack2<T>::pack(o_sign * a[q4 + 6], o_sign * a[q4 + 7]);
-                        T* dst = obase + 32 * half + q4;
-                        if (first) *reinterpret_cast<uint4*>(dst) = w4; else RedAdd<T>::v4(dst, w4);
-                    }
-                }
-            }
-            if (first && ndir == 2) {                         // publish my half of the chunk
-                __syncwarp();
-                if (lane == 0) { __threadfence(); atomicAdd(flag, 1u); }
-            }
-        };
-        #pragma unroll 1
-        for (uint32_t m = 0;; ++m, ++ci) {
-            if (lane == 0) waiter.wait_lite(bar(B_PFULL), m & 1);
-            __syncwarp();
-            if (*abort_flag) break;
-            if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
-            const bool at_end = cur.nch == 0;
-            if (!at_end) {
-            tc_fence_after();
-            uint8_t* p0 = smem + (m % 3) * W_STAGE_B + WS_G;  // keys 0..63 over the dead gate tile
-            uint8_t* p1 = smem + WO_X;                        // keys 64..127
-            // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test); on the
-            // diagonal, bit j of `dmask_bits` says whether key j of the block is kept for my query row.
-            const int dir = cur.dir;
-            const uint32_t dmask_bits = dir ? ~((1u << lane) - 1u) : (lane == 31 ? 0xffffffffu : (2u << lane) - 1u);
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {                  // key block: keys 32*cb .. 32*cb+31
-                if (cb == 2 && m > 0) {                       // the second tile is free once the previous iteration's MMAs are done
-                    if (lane == 0) waiter.wait_lite(bar(B_UFULL), (m - 1) & 1);
+                if (*abort_flag) break;
+                tc_fence_after();
+                const int cb = sub, dir = dir_mask_it;
+                uint8_t* stj = smem + (j % 3) * W_STAGE_B;
+                if (cb >= 2) {                                // keys 64..127 go over the k tile: the state update must have read it
+                    waiter.wait_lite(bar(B_UFULL + (j & 1)), (j >> 1) & 1);
                     __syncwarp();
                 }
-                const bool all_zero = dir ? cb < quad : cb > quad;
-                uint8_t* prow = (cb < 2 ? p0 : p1) + row * 128;
+                uint8_t* prow = stj + (cb < 2 ? WS_G : WS_K) + row * 128;
                 const uint32_t chunk0 = (uint32_t)(cb & 1) * 4;           // first 16-byte chunk of this block in the 128-byte row
+                // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test)
+                const bool all_zero = dir ? cb < quad : cb > quad;
                 if (all_zero) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(prow + (((chunk0 + j) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                 } else {
                     float a[32];
                     tc_ld32(tmem + lane_base + WT_P + 32 * cb, a);
                     tc_wait_ld();
-                    if (cb == quad) {                                     // the diagonal block: per-element mask
+                    if (cb == quad) {                                     // the diagonal block: bit e says whether key e is kept for my row
+                        const uint32_t keep = dir ? ~((1u << lane) - 1u) : (lane == 31 ? 0xffffffffu : (2u << lane) - 1u);
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) a[e] = (dmask_bits >> e) & 1u ? a[e] : 0.f;
+                        for (int e = 0; e < 32; ++e) a[e] = (keep >> e) & 1u ? a[e] : 0.f;
                     }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
+                    for (int i = 0; i < 4; ++i) {
                         uint4 w4;
-                        w4.x = Pack2<T>::pack(a[8 * j], a[8 * j + 1]); w4.y = Pack2<T>::pack(a[8 * j + 2], a[8 * j + 3]);
-                        w4.z = Pack2<T>::pack(a[8 * j + 4], a[8 * j + 5]); w4.w = Pack2<T>::pack(a[8 * j + 6], a[8 * j + 7]);
-                        *reinterpret_cast<uint4*>(prow + (((chunk0 + j) ^ (row & 7)) << 4)) = w4;
+                        w4.x = Pack2<T>::pack(a[8 * i], a[8 * i + 1]); w4.y = Pack2<T>::pack(a[8 * i + 2], a[8 * i + 3]);
+                        w4.z = Pack2<T>::pack(a[8 * i + 4], a[8 * i + 5]); w4.w = Pack2<T>::pack(a[8 * i + 6], a[8 * i + 7]);
+                        *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = w4;
                     }
                 }
+                tc_fence_before();
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
             }
-            tc_fence_before();
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
+            // ---- output of iteration j = m - 2: accumulator slot -> 16-bit staging tile (my 32 rows x 16 columns) ----
+            if (m >= 2 && (!ended || m - 2 < end_m)) {
+                const uint32_t j = m - 2;
+                waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
+                if (j > 0) waiter.wait_lite(bar(B_XFREE), (j - 1) & 1);        // the store thread has sent the previous tile
+                __syncwarp();
+                if (*abort_flag) break;
+                tc_fence_after();
+                float a[16];
+                tc_ld16(tmem + lane_base + WT_O + 64u * (j & 1u) + 16 * sub, a);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_OFREE + (j & 1)));   // the slot is read: hand it back
+                uint8_t* orow = smem + WO_X + row * 128;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    uint4 w4;
+                    w4.x = Pack2<T>::pack(o_sign * a[8 * i], o_sign * a[8 * i + 1]); w4.y = Pack2<T>::pack(o_sign * a[8 * i + 2], o_sign * a[8 * i + 3]);
+                    w4.z = Pack2<T>::pack(o_sign * a[8 * i + 4], o_sign * a[8 * i + 5]); w4.w = Pack2<T>::pack(o_sign * a[8 * i + 6], o_sign * a[8 * i + 7]);
+                    *reinterpret_cast<uint4*>(orow + (((uint32_t)(2 * sub + i) ^ (row & 7)) << 4)) = w4;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (j & 1)));
             }
-            if (m > 0) epilogue(m - 1, prev, prev_ci);       // one iteration behind: the MMAs of m - 1 finish meanwhile
-            if (at_end) break;
-            prev = cur; prev_ci = ci;
+            if (ended && m >= end_m + 1) {                    // everything that exists is masked and staged: tell the store thread
+                if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (end_m & 1)));
+                break;
+            }
         }
-    } else if (warp < W_PREP_WARPS + 8) {
+    } else if (warp < W_CTRL_WARP0) {
         // =============================== state warps ===============================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(W_REGS_STATE));
         const int quad = warp & 3;
         const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
         const int st_row = 16 * quad + (lane & 15);           // key channel: an M=64 accumulator puts row r in lane (r%16) + 32*(r/16)
@@ -474,7 +565,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         #pragma unroll 1
         for (uint32_t m = 0;; ++m, ++ci) {
             const uint32_t s = m % 3;
-            if (lane == 0) waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);
+            // The work item is known as soon as its loads are under way: the state entering a new segment is fetched
+            // from the mailbox while the prep warps still work on the iteration (two trips to L2 that would otherwise
+            // sit in front of the state product).
+            waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
             if (*abort_flag) break;
             if (ci == cur.nch) { read_item(items, cur); ++items; ci = 0; }
@@ -500,9 +594,16 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     S[j] = t4.x; S[j + 1] = t4.y; S[j + 2] = t4.z; S[j + 3] = t4.w;
                 }
             }
-            const float* ve = vec + (m & 3) * 256;
+            waiter.wait_lite(bar(B_PREPPED + s), (m / 3) & 1);   // G_ref, G_last of this iteration are written
+            __syncwarp();
+            if (*abort_flag) break;
+            const float* ve = vec + (m & 3) * 128;             // [G_ref | G_last] of this iteration, log2 units
+            if (m > 0) {                                      // the previous iteration's state product has read the operand
+                waiter.wait_lite(bar(B_STFREE), (m - 1) & 1);
+                __syncwarp();
+            }
             if (!s_zero) {                                    // bf16(2^G_ref * S_in), MN-major [channel][value]
-                const float eg = ex2(ve[128 + st_row]);
+                const float eg = ex2(ve[st_row]);
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
                     uint4 w4;
@@ -514,15 +615,16 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_STREADY));
-            if (lane == 0) waiter.wait_lite(bar(B_UFULL), m & 1);
+            waiter.wait_lite(bar(B_UFULL + (m & 1)), (m >> 1) & 1);
             __syncwarp();
             tc_fence_after();
             {
-                const float e_last = ve[st_row], e_rel = ve[64 + st_row];
+                const float g_ref = ve[st_row], g_last = ve[64 + st_row];
+                const float e_last = ex2(g_last), e_rel = ex2(g_last - g_ref);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     float u[32];
-                    tc_ld32(tmem + lane_base + WT_U + 32 * half, u);   // rows live in lanes 0-15 of the warp
+                    tc_ld32(tmem + lane_base + WT_U + 64u * (m & 1u) + 32 * half, u);   // rows live in lanes 0-15 of the warp
                     tc_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -531,7 +633,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                         S[16 * half + j] = fmaf(S[16 * half + j], e_last, e_rel * mine);
                     }
                 }
-                gacc += ve[192 + st_row];
+                gacc += g_last;
             }
             tc_fence_before();
             s_zero = false;
@@ -575,13 +677,15 @@ size_t wave_counter_bytes(int B, int H, int nseg) {
     return ((1 + 2 * (size_t)B * H + (size_t)B * H * nseg * W_SEG_CHUNKS) * sizeof(uint32_t) + 255) & ~(size_t)255;
 }
 
-template <typename T>
-int launch_wave(const BiglaParams& p, const TcMaps& maps, void* ws, cudaStream_t stream) {
+template <typename T, bool RAW, bool CLAMP>
+int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream_t stream) {
     const int nseg = (p.L + W_SEG - 1) / W_SEG;
     const int BH = p.B * p.H;
     WaveParams wp;
     wp.p = p;
     wp.nseg = nseg;
+    wp.inv_per_step = 1.0f / (float)(BH * (p.dir_mask == 3 ? 2 : 1));
+    wp.inv_H = 1.0f / (float)p.H;
     wp.ticket = reinterpret_cast<uint32_t*>(ws);
     wp.chain_cnt = wp.ticket + 1;
     wp.chunk_flag = wp.chain_cnt + 2 * (size_t)BH;
@@ -593,7 +697,7 @@ int launch_wave(const BiglaParams& p, const TcMaps& maps, void* ws, cudaStream_t
     int dev = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return VIG_ERR_DEVICE;
-    auto kern = bigla_wave_kernel<T>;
+    auto kern = bigla_wave_kernel<T, RAW, CLAMP>;
     if (!sm_count[dev]) {
         int sms = 0;
         if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
@@ -613,6 +717,7 @@ bool bigla_wave_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
     if (p.dv != WDV || p.dk != WDK || !p.o || !p.q || p.B * p.H < 1 || p.L < 1) return false;
     if (p.dir_mask < 1 || p.dir_mask > 3) return false;
+    if ((long long)p.B * p.H * 2 * ((p.L + W_SEG - 1) / W_SEG) >= (1ll << 24)) return false;   // tickets are decoded in fp32
     if (!tc::tma_ok(p.q, p.sq, p.B, p.H) || !tc::tma_ok(p.k, p.sk, p.B, p.H) || !tc::tma_ok(p.v, p.sv, p.B, p.H)) return false;
     if ((p.dir_mask & 1) && (!p.gf || !tc::tma_ok(p.gf, p.sgf, p.B, p.H))) return false;
     if ((p.dir_mask & 2) && (!p.gb || !tc::tma_ok(p.gb, p.sgb, p.B, p.H))) return false;
@@ -644,7 +749,7 @@ size_t bigla_wave_workspace(int B, int H, int L, int dk, int dv) {
 
 int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
     if (!ws || ws_bytes < bigla_wave_workspace(p.B, p.H, p.L, p.dk, p.dv)) return VIG_ERR_WORKSPACE;
-    tc::TcMaps maps;
+    WaveMaps maps;
     const void* gfs = p.gf ? p.gf : p.gb;
     const int64_t* gfst = p.gf ? p.sgf : p.sgb;
     const void* gbs = p.gb ? p.gb : p.gf;
@@ -653,10 +758,17 @@ int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStrea
         !tc::make_map(&maps.k, p.k, p.sk, p.B, p.H, p.L, p.dk, p.dtype, true) ||
         !tc::make_map(&maps.v, p.v, p.sv, p.B, p.H, p.L, p.dv, p.dtype, true) ||
         !tc::make_map(&maps.gf, gfs, gfst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
-        !tc::make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false))
+        !tc::make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
+        !tc::make_map(&maps.o, p.o, p.so, p.B, p.H, p.L, p.dv, p.dtype, true))
         return VIG_ERR_DEVICE;
-    if (p.dtype == VIG_DTYPE_BF16) return launch_wave<__nv_bfloat16>(p, maps, ws, stream);
-    return launch_wave<__half>(p, maps, ws, stream);
+    // gate form and clamp are compile-time properties of the kernel: no branch inside its token loops
+    const bool raw = p.gate_norm > 0.f, clamp = p.clamp_min == p.clamp_min;
+#define VIG_WAVE(TT)                                                                   \
+    if (raw) return clamp ? launch_wave<TT, true, true>(p, maps, ws, stream) : launch_wave<TT, true, false>(p, maps, ws, stream); \
+    return clamp ? launch_wave<TT, false, true>(p, maps, ws, stream) : launch_wave<TT, false, false>(p, maps, ws, stream);
+    if (p.dtype == VIG_DTYPE_BF16) { VIG_WAVE(__nv_bfloat16) }
+    VIG_WAVE(__half)
+#undef VIG_WAVE
 }
 
 }  // namespace vig
