@@ -347,6 +347,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             const uint32_t s = m % 3;
             bool have = false;
             const int dir_mask_it = dir_prev;                 // direction of iteration m - 1 (the one whose scores are masked in this trip)
+            float4 gl[4];                                     // cumulative log2-gates of my 4 tokens, from the group's first token
+            uint8_t* stg = smem + s * W_STAGE_B;
+            int dmask = 0;
             if (!ended) {
             waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
@@ -359,12 +362,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             } else {
             have = true;
             dir_prev = cur.dir;
-            uint8_t* stg = smem + s * W_STAGE_B;
             const int t0 = cur.seg * W_SEG + chunk_of(cur, ci) * CHUNK;
             const int n_valid = p.L - t0;                     // rows at or past it are padding: decay 1
-            const int dmask = cur.dir ? 7 : 0;
+            dmask = cur.dir ? 7 : 0;
             // ---- gate phase: transform, running sums over my 4 tokens, group sum published ----
-            float4 gl[4];                                     // cumulative log2-gates of my 4 tokens, from the group's first token
             {
                 uint2 raw[4];
 #pragma unroll
@@ -402,7 +403,80 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive_plain(bar(B_PART + (m & 1)));
             }
-            // ---- raw operand rows into registers while the other warps finish their group sums ----
+            }
+            }
+            // ---- scores of iteration j = m - 1: TMEM -> masked 16-bit tiles (my 32 rows x key block `sub`) ----
+            if (m >= 1 && (!ended || m - 1 < end_m)) {
+                const uint32_t j = m - 1;
+                waiter.wait_lite(bar(B_PFULL), j & 1);
+                __syncwarp();
+                if (*abort_flag) break;
+                tc_fence_after();
+                const int cb = sub, dir = dir_mask_it;
+                uint8_t* stj = smem + (j % 3) * W_STAGE_B;
+                if (cb >= 2) {                                // keys 64..127 go over the k tile: the state update must have read it
+                    waiter.wait_lite(bar(B_UFULL + (j & 1)), (j >> 1) & 1);
+                    __syncwarp();
+                }
+                uint8_t* prow = stj + (cb < 2 ? WS_G : WS_K) + row * 128;
+                const uint32_t chunk0 = (uint32_t)(cb & 1) * 4;           // first 16-byte chunk of this block in the 128-byte row
+                // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test)
+                const bool all_zero = dir ? cb < quad : cb > quad;
+                if (all_zero) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                } else {
+                    float a[32];
+                    tc_ld32(tmem + lane_base + WT_P + 32 * cb, a);
+                    tc_wait_ld();
+                    if (cb == quad) {                                     // the diagonal block: bit e says whether key e is kept for my row
+                        const uint32_t keep = dir ? ~((1u << lane) - 1u) : (lane == 31 ? 0xffffffffu : (2u << lane) - 1u);
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) a[e] = (keep >> e) & 1u ? a[e] : 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 w4;
+                        w4.x = Pack2<T>::pack(a[8 * i], a[8 * i + 1]); w4.y = Pack2<T>::pack(a[8 * i + 2], a[8 * i + 3]);
+                        w4.z = Pack2<T>::pack(a[8 * i + 4], a[8 * i + 5]); w4.w = Pack2<T>::pack(a[8 * i + 6], a[8 * i + 7]);
+                        *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = w4;
+                    }
+                }
+                tc_fence_before();
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
+            }
+            // ---- output of iteration j = m - 2: accumulator slot -> 16-bit staging tile (my 32 rows x 16 columns) ----
+            if (m >= 2 && (!ended || m - 2 < end_m)) {
+                const uint32_t j = m - 2;
+                waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
+                if (j > 0) waiter.wait_lite(bar(B_XFREE), (j - 1) & 1);        // the store thread has sent the previous tile
+                __syncwarp();
+                if (*abort_flag) break;
+                tc_fence_after();
+                float a[16];
+                tc_ld16(tmem + lane_base + WT_O + 64u * (j & 1u) + 16 * sub, a);
+                tc_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_OFREE + (j & 1)));   // the slot is read: hand it back
+                uint8_t* orow = smem + WO_X + row * 128;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    uint4 w4;
+                    w4.x = Pack2<T>::pack(o_sign * a[8 * i], o_sign * a[8 * i + 1]); w4.y = Pack2<T>::pack(o_sign * a[8 * i + 2], o_sign * a[8 * i + 3]);
+                    w4.z = Pack2<T>::pack(o_sign * a[8 * i + 4], o_sign * a[8 * i + 5]); w4.w = Pack2<T>::pack(o_sign * a[8 * i + 6], o_sign * a[8 * i + 7]);
+                    *reinterpret_cast<uint4*>(orow + (((uint32_t)(2 * sub + i) ^ (row & 7)) << 4)) = w4;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (j & 1)));
+            }
+            // ---- second half of the preparation of iteration m: by now the other warps' group sums are in (the masking and
+            // staging above ran while they arrived), so the wait below is a formality ----
+            if (have) {
+            // raw operand rows into registers
             uint2 rk[4], rq[4];
             uint32_t offs[4];
 #pragma unroll
@@ -473,76 +547,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s));
             }
-            }
-            (void)have;
-            // ---- scores of iteration j = m - 1: TMEM -> masked 16-bit tiles (my 32 rows x key block `sub`) ----
-            if (m >= 1 && (!ended || m - 1 < end_m)) {
-                const uint32_t j = m - 1;
-                waiter.wait_lite(bar(B_PFULL), j & 1);
-                __syncwarp();
-                if (*abort_flag) break;
-                tc_fence_after();
-                const int cb = sub, dir = dir_mask_it;
-                uint8_t* stj = smem + (j % 3) * W_STAGE_B;
-                if (cb >= 2) {                                // keys 64..127 go over the k tile: the state update must have read it
-                    waiter.wait_lite(bar(B_UFULL + (j & 1)), (j >> 1) & 1);
-                    __syncwarp();
-                }
-                uint8_t* prow = stj + (cb < 2 ? WS_G : WS_K) + row * 128;
-                const uint32_t chunk0 = (uint32_t)(cb & 1) * 4;           // first 16-byte chunk of this block in the 128-byte row
-                // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test)
-                const bool all_zero = dir ? cb < quad : cb > quad;
-                if (all_zero) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-                } else {
-                    float a[32];
-                    tc_ld32(tmem + lane_base + WT_P + 32 * cb, a);
-                    tc_wait_ld();
-                    if (cb == quad) {                                     // the diagonal block: bit e says whether key e is kept for my row
-                        const uint32_t keep = dir ? ~((1u << lane) - 1u) : (lane == 31 ? 0xffffffffu : (2u << lane) - 1u);
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) a[e] = (keep >> e) & 1u ? a[e] : 0.f;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 w4;
-                        w4.x = Pack2<T>::pack(a[8 * i], a[8 * i + 1]); w4.y = Pack2<T>::pack(a[8 * i + 2], a[8 * i + 3]);
-                        w4.z = Pack2<T>::pack(a[8 * i + 4], a[8 * i + 5]); w4.w = Pack2<T>::pack(a[8 * i + 6], a[8 * i + 7]);
-                        *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = w4;
-                    }
-                }
-                tc_fence_before();
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
-            }
-            // ---- output of iteration j = m - 2: accumulator slot -> 16-bit staging tile (my 32 rows x 16 columns) ----
-            if (m >= 2 && (!ended || m - 2 < end_m)) {
-                const uint32_t j = m - 2;
-                waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
-                if (j > 0) waiter.wait_lite(bar(B_XFREE), (j - 1) & 1);        // the store thread has sent the previous tile
-                __syncwarp();
-                if (*abort_flag) break;
-                tc_fence_after();
-                float a[16];
-                tc_ld16(tmem + lane_base + WT_O + 64u * (j & 1u) + 16 * sub, a);
-                tc_wait_ld();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_plain(bar(B_OFREE + (j & 1)));   // the slot is read: hand it back
-                uint8_t* orow = smem + WO_X + row * 128;
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    uint4 w4;
-                    w4.x = Pack2<T>::pack(o_sign * a[8 * i], o_sign * a[8 * i + 1]); w4.y = Pack2<T>::pack(o_sign * a[8 * i + 2], o_sign * a[8 * i + 3]);
-                    w4.z = Pack2<T>::pack(o_sign * a[8 * i + 4], o_sign * a[8 * i + 5]); w4.w = Pack2<T>::pack(o_sign * a[8 * i + 6], o_sign * a[8 * i + 7]);
-                    *reinterpret_cast<uint4*>(orow + (((uint32_t)(2 * sub + i) ^ (row & 7)) << 4)) = w4;
-                }
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (j & 1)));
-            }
             if (ended && m >= end_m + 1) {                    // everything that exists is masked and staged: tell the store thread
                 if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (end_m & 1)));
                 break;
@@ -581,8 +585,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     gacc = 0.f;
                 } else {
                     uint32_t* cnt = wp.chain_cnt + cur.bh * 2 + cur.dir;
-                    if (lane == 0) global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag);
-                    __syncwarp();
+                    global_wait(cnt, 4u * (uint32_t)cur.w, abort_flag);     // taken by the whole warp, like every wait here
                     const float* box = wp.mailbox + (((size_t)cur.bh * 2 + cur.dir) * 2 + ((cur.w - 1) & 1)) * SLOT;
                     src = box;
                     gacc = __ldcg(box + NE + st_row);

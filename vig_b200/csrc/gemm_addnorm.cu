@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
             uint4 rr[NV];
 #pragma unroll
             for (int v = 0; v < NV; ++v) rr[v] = (live && residual) ? __ldg(reinterpret_cast<const uint4*>(residual + row * NT) + v) : make_uint4(0u, 0u, 0u, 0u);
-            if (lane == 0) waiter.wait(bar_acc_full + 8 * buf, use & 1u);
+            waiter.wait(bar_acc_full + 8 * buf, use & 1u);     // by the whole warp: a wait by one lane with the others parked at a warp barrier resumes microseconds late
             __syncwarp();
             if (*abort_flag) break;
             tc_fence_after();

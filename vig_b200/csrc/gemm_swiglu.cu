@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
                 const int row0 = (tile / nsplit) * BM + r_in_tile;
                 for (int nb = nb_begin(tile); nb < nb_end(tile); ++nb, ++acc_it) {
                     const uint32_t buf = acc_it & 1u;
-                    if (lane == 0) waiter.wait(bar_acc_full + 8 * buf, (acc_it >> 1) & 1u);
+                    waiter.wait(bar_acc_full + 8 * buf, (acc_it >> 1) & 1u);   // by the whole warp: a wait by one lane with the others parked at a warp barrier resumes microseconds late
                     __syncwarp();
                     tc_fence_after();
                     const uint32_t acc = tmem + lane_base + buf * (uint32_t)(S * 128) + (uint32_t)sub * 128u;
