@@ -251,37 +251,35 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const uint32_t o_acc = tmem + WT_O + 64u * (m & 1u), u_acc = tmem + WT_U + 64u * (m & 1u);
                 const bool s_zero = state_zero(mcur, m_ci);
                 tc_fence_after();
-                if (lane == 0) {
-                    // (a) scores, and right behind them the state update: it needs only the prepared tiles, and the
-                    // state chain -- the one sequential dependency of the kernel -- waits for nothing else
-#pragma unroll 1
-                    for (uint32_t k4 = 0; k4 < WDK / 16; ++k4) tc_mma(tmem + WT_P, q_lo + 2 * k4, k_lo + 2 * k4, IDESC_QK, k4 > 0);
-                    tc_commit(bar(B_PFULL));
-#pragma unroll 1
-                    for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) tc_mma(u_acc, k_lo + 128 * k8, v_lo + 128 * k8, IDESC_U, k8 > 0);
-                    tc_commit(bar(B_UFULL + (m & 1u)));
-                }
+                // The loops are walked by the whole warp and only the issuing instruction is predicated on the lane: the
+                // control flow stays convergent, so loop counters and descriptor arithmetic run in the uniform datapath
+                // instead of on the issuing lane (a lane-0 branch around the loops made every MMA cost ~150 cycles to issue).
+                const bool issuer = lane == 0;
+                // (a) scores, and right behind them the state update: it needs only the prepared tiles, and the
+                // state chain -- the one sequential dependency of the kernel -- waits for nothing else
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < WDK / 16; ++k4) { if (issuer) tc_mma(tmem + WT_P, q_lo + 2 * k4, k_lo + 2 * k4, IDESC_QK, k4 > 0); }
+                if (issuer) tc_commit(bar(B_PFULL));
+#pragma unroll
+                for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) { if (issuer) tc_mma(u_acc, k_lo + 128 * k8, v_lo + 128 * k8, IDESC_U, k8 > 0); }
+                if (issuer) tc_commit(bar(B_UFULL + (m & 1u)));
                 // (b) product with the entering state
                 waiter.wait_lite(bar(B_STREADY), m & 1);
                 if (m >= 2) waiter.wait_lite(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
                 tc_fence_after();
-                if (lane == 0) {
-                    if (!s_zero) {
-#pragma unroll 1
-                        for (uint32_t k4 = 0; k4 < WDK / 16; ++k4) tc_mma(o_acc, q_lo + 2 * k4, st_lo + 128 * k4, IDESC_OV, k4 > 0);
-                    }
-                    tc_commit(bar(B_STFREE));                  // the state operand may be overwritten
+                if (!s_zero) {
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < WDK / 16; ++k4) { if (issuer) tc_mma(o_acc, q_lo + 2 * k4, st_lo + 128 * k4, IDESC_OV, k4 > 0); }
                 }
+                if (issuer) tc_commit(bar(B_STFREE));          // the state operand may be overwritten
                 // (c) masked scores x v
                 waiter.wait_lite(bar(B_PREADY), m & 1);
                 tc_fence_after();
-                if (lane == 0) {
-#pragma unroll 1
-                    for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8)
-                        tc_mma(o_acc, (k8 < 4 ? p0_lo : p1_lo) + 2 * (k8 & 3), v_lo + 128 * k8, IDESC_OV, !s_zero || k8 > 0);
-                    tc_commit(bar(B_OFULL + (m & 1)));
-                    tc_commit(bar(B_SFREE + s));
+#pragma unroll
+                for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) {
+                    if (issuer) tc_mma(o_acc, (k8 < 4 ? p0_lo : p1_lo) + 2 * (k8 & 3), v_lo + 128 * k8, IDESC_OV, !s_zero || k8 > 0);
                 }
+                if (issuer) { tc_commit(bar(B_OFULL + (m & 1))); tc_commit(bar(B_SFREE + s)); }
                 __syncwarp();
             }
         } else if (tid == W_STORE_WARP * 32) {
