@@ -164,10 +164,11 @@ VIG_API int vig_bigla_fwd_noalloc(const void* q, const void* k, const void* v, c
  * optional bias, optional SiLU.  Replaces `in_proj` = nn.Conv2d(C, C, 3, padding=1, groups=C) [+ SiLU]
  * and the two NCHW<->NLC copies around it (classification/models/vig.py:291-294, 428-430).
  * weight_tap_major: [9][C] (tap = 3*ky + kx), i.e. the reference's [C,1,3,3] parameter transposed;
- * same dtype as x.  C must be a multiple of 16 bytes / element size.
+ * same dtype as x.  C must be a multiple of 16 bytes / element size.  status_dev: optional int32 on the device,
+ * bit 0 = a bounded wait ran out (large 16-bit inputs run a TMA-fed kernel with a shared-memory pipeline).
  */
 VIG_API int vig_dwconv3x3_fwd(const void* x, const void* weight_tap_major, const void* bias, void* y,
-                      int B, int h, int w, int C, int act_silu, int dtype, void* stream);
+                      int B, int h, int w, int C, int act_silu, int dtype, int32_t* status_dev, void* stream);
 
 /*
  * The same convolution on a horizontal band of a taller image (rows [r0, r0 + h) of the token grid): `top` and `bottom`

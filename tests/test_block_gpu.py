@@ -44,6 +44,35 @@ def test_dwconv3x3(dtype, hw, C, act, bias):
     assert rel_err(y.float(), ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,hw,C,act,bias", [(8, (64, 64), 192, True, False), (8, (33, 47), 384, True, True), (2, (61, 130), 768, False, False),
+                                             (8, (50, 60), 200, True, True), (4, (3, 700), 512, True, False)])
+def test_dwconv3x3_tma_form(dtype, B, hw, C, act, bias):
+    """Inputs of 4M elements and more run the TMA-fed kernel (tiles of 2 rows with a zero-filled border): against the
+    oracle at the type's bar, and bit for bit against the sliding-window kernel, reached through the halo entry point
+    with no halo rows.  Shapes: the headline one, ragged widths and heights, channel counts cut into chunks of 256 / 192
+    channels, a width cut into several column blocks."""
+    import vig_b200
+    from vig_b200 import _lib
+    h, w = hw
+    assert B * h * w * C >= 1 << 22
+    g = torch.Generator().manual_seed(C + h)
+    x = torch.randn(B, h * w, C, generator=g).to(dtype)
+    wt = (0.3 * torch.randn(C, 1, 3, 3, generator=g)).to(dtype)
+    b = torch.randn(C, generator=g).to(dtype) if bias else None
+    taps = wt.reshape(C, 9).t().contiguous().cuda()
+    xc, bc = x.cuda(), (b.cuda() if bias else None)
+    y = vig_b200.dwconv3x3(xc, taps, bc, hw, act)
+    vig_b200.check_status()
+    ref = oracle.dwconv3x3_nlc(x.float(), wt.float(), b.float() if bias else None, hw, act)
+    assert rel_err(y.float(), ref) < TOL[dtype]
+    y_rows = torch.empty_like(xc)
+    st = _lib.lib().vig_dwconv3x3_halo_fwd(_lib.ptr(xc), None, None, _lib.ptr(taps), _lib.ptr(bc), _lib.ptr(y_rows), B, h, w, C,
+                                           int(act), _lib.dtype_code(xc), _lib.stream_ptr())
+    _lib.check(st, "vig_dwconv3x3_halo_fwd")
+    assert torch.equal(y, y_rows)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("out_act", [False, True])
 def test_gate_inject(dtype, out_act):

@@ -27,7 +27,7 @@ _SIGNATURES = {
     "vig_bigla_bwd": (c_int, [c_void_p] * 11 + [c_int] * 6 + [_P64] * 6 + [c_float, c_float, c_int, c_void_p, c_size_t, c_void_p]),
     "vig_bigla_noalloc_scratch_bytes": (c_size_t, []),
     "vig_bigla_fwd_noalloc": (c_int, [c_void_p] * 6 + [c_int] * 6 + [_P64] * 6 + [c_float] * 4 + [c_int, c_void_p, c_void_p]),
-    "vig_dwconv3x3_fwd": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_void_p]),
+    "vig_dwconv3x3_fwd": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_void_p] * 2),
     "vig_dwconv3x3_halo_fwd": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
     "vig_gate_inject_fwd": (c_int, [c_void_p, _P64] + [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_float, c_int, c_int, c_void_p]),
     "vig_add_rmsnorm_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_void_p]),

@@ -100,5 +100,9 @@ bool bigla_wave_supported(const BiglaParams& p);
 bool bigla_wave_preferred(const BiglaParams& p);
 size_t bigla_wave_workspace(int B, int H, int L, int dk, int dv);
 int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream);
+// TMA-fed depthwise conv: launches and returns a status, or VIG_DWCONV_NOT_TAKEN when the shape is left to the other forms
+constexpr int VIG_DWCONV_NOT_TAKEN = -1000;
+int dwconv_tma_try(const void* x, const void* wt, const void* bias, void* y, int B, int h, int w, int C, int act, int dtype,
+                   int32_t* status, cudaStream_t stream);
 
 }  // namespace vig

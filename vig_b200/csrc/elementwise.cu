@@ -579,11 +579,14 @@ using namespace vig;
     }
 
 extern "C" int vig_dwconv3x3_fwd(const void* x, const void* wt, const void* bias, void* y, int B, int h, int w, int C,
-                                 int act_silu, int dtype, void* stream) {
+                                 int act_silu, int dtype, int32_t* status_dev, void* stream) {
     if (!x || !wt || !y) return VIG_ERR_NULL;
     if (B < 0 || h <= 0 || w <= 0 || C <= 0) return VIG_ERR_SHAPE;
     if (B == 0) return VIG_OK;
     if (!aligned16(x) || !aligned16(wt) || !aligned16(y) || (bias && !aligned16(bias))) return VIG_ERR_ALIGN;
+    // large 16-bit problems: the TMA-fed form (bit-identical results); everything else: the register sliding-window forms
+    const int taken = dwconv_tma_try(x, wt, bias, y, B, h, w, C, act_silu, dtype, status_dev, (cudaStream_t)stream);
+    if (taken != VIG_DWCONV_NOT_TAKEN) return taken;
     VIG_DISPATCH(dtype, dwconv_t<T>(x, wt, bias, y, B, h, w, C, act_silu, (cudaStream_t)stream))
 }
 

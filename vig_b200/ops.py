@@ -349,7 +349,7 @@ def dwconv3x3(x, weight_tap_major, bias, hw, act_silu, out=None, top=None, botto
         _lib.check(st, "vig_dwconv3x3_halo_fwd")
         return y
     st = _lib.lib().vig_dwconv3x3_fwd(_lib.ptr(x), _lib.ptr(weight_tap_major), _lib.ptr(bias), _lib.ptr(y),
-                                      B, h, w, C, int(bool(act_silu)), _lib.dtype_code(x), _lib.stream_ptr())
+                                      B, h, w, C, int(bool(act_silu)), _lib.dtype_code(x), _status_ptr(None, x.device), _lib.stream_ptr())
     _lib.check(st, "vig_dwconv3x3_fwd")
     return y
 
