@@ -208,7 +208,8 @@ def test_model_with_norms_fused_into_projection_epilogues_matches_default_path()
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("M,K,I", [(392, 192, 512), (1000, 384, 1024), (128, 64, 64), (70, 192, 128), (5000, 192, 512)])
+@pytest.mark.parametrize("M,K,I", [(392, 192, 512), (1000, 384, 1024), (128, 64, 64), (70, 192, 128), (5000, 192, 512),
+                                   (40000, 192, 512), (38000, 64, 128), (37930, 128, 384)])   # the last three: the N = 256 form (many row tiles)
 def test_linear_swiglu_fused_gemm(dtype, M, K, I):
     import vig_b200
     g = torch.Generator().manual_seed(M + K)

@@ -3,13 +3,22 @@
 // (classification/models/vig.py:494-497: gate_proj -> chunk -> swiglu) never goes to HBM.
 //
 // tcgen05 GEMM.  A persistent CTA owns tiles of BM = 128*S rows of x; the tile's whole K extent stays resident
-// in shared memory (TMA, 128-byte swizzle), the weights stream through a ring of 16 KB stages holding 64 gate
+// in shared memory (TMA, 128-byte swizzle), the weights stream through a 96 KB ring holding, per k box, 64 gate
 // rows and the 64 matching y rows, so one M128 N128 MMA per subtile fills an accumulator [128 x (64 gate | 64 y)]
 // in tensor memory.  Accumulators are double buffered: while the MMA warp works on feature block n+1, the
-// epilogue warps read block n with tcgen05.ld and apply silu(g)*y.  Each warp packs its [32 rows x 64 features] piece
-// into a swizzled 4 KB box of shared memory and lane 0 sends it out with one TMA store: a thread owns a row, so direct
-// 16-byte stores would touch 32 lines per request and fill only half of each 32-byte sector.
-// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2.. epilogue.  Every wait is bounded.
+// epilogue warps read block n with tcgen05.ld and apply silu(g)*y.
+//
+// What the timeline of the MMA warp showed, and what the organisation answers:
+//  * tcgen05.mma issue is synchronous with the tensor pipe (a 128x128x16 MMA costs ~80 cycles to issue back to back),
+//    so every cycle the issuing warp spends elsewhere is a cycle the tensor pipe idles.  A wait on an already completed
+//    mbarrier costs ~200 cycles and a lane-0 branch around the issue another ~200 to reconverge: the ring is therefore
+//    handed over in groups of up to 3 k boxes (one wait and one commit per group instead of per box), and the loops
+//    are walked by the whole warp with only the issuing instruction predicated on the lane.
+//  * an epilogue warp works through its piece in one dependent chain (TMEM load -> 64 sigmoids -> pack -> store), so
+//    eight warps took ~4000 cycles per feature block, longer than its MMAs.  Sixteen warps now share a block, each
+//    with [32 rows x 32 features]; a warp packs its piece into a 2 KB box of shared memory and lane 0 sends it out
+//    with one TMA store (a thread owns a row, so direct stores would touch 32 lines per request).
+// Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2..17 epilogue.  Every wait is bounded.
 #include "tc_common.cuh"
 
 namespace vig {
@@ -19,35 +28,23 @@ using namespace tc;
 
 constexpr int BK = 64;                         // k elements per stage row (128 bytes)
 constexpr int BNF = 64;                        // features per block: 64 gate rows + 64 y rows -> MMA N = 128
-constexpr int NSTAGE = 6;                      // weight stages in flight (16 KB each)
+constexpr int NSTAGE = 6;                      // weight k boxes in flight (16 KB each)
 constexpr int MAX_KB = 6;                      // k boxes of an x tile (K <= 384)
 constexpr int A_BOX_BYTES = 128 * BK * 2;      // one [128 rows x 64 k] box
 constexpr int B_STAGE_BYTES = 2 * BNF * BK * 2;
 constexpr int MAX_A_BYTES = 96 * 1024;
-constexpr int GS_THREADS = 64 + 256;
-constexpr int OUT_BOX_BYTES = 32 * BNF * 2;    // one epilogue warp's [32 rows x 64 features] box
-constexpr int OUT_STAGE_BYTES = 8 * OUT_BOX_BYTES;
+constexpr int GS_EPI_WARPS = 16;
+constexpr int GS_THREADS = 64 + 32 * GS_EPI_WARPS;
+constexpr int OUT_BOX_BYTES = 32 * 32 * 2;     // one epilogue warp's [32 rows x 32 features] box
+constexpr int OUT_STAGE_BYTES = GS_EPI_WARPS * OUT_BOX_BYTES;
 
 // sigmoid(x) = 0.5 tanh(x / 2) + 0.5 with the single-instruction tanh: one MUFU per element instead of two
-// (exp + reciprocal), which is what bounds the epilogue; its error (~2^-11) is below the bf16 / fp16 output step.
+// (exp + reciprocal); its error (~2^-11) is below the bf16 / fp16 output step.
 __device__ __forceinline__ float sigmoid_tanh(float x) {
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
     return fmaf(t, 0.5f, 0.5f);
 }
-
-struct GsWaiter {
-    volatile int* abort_flag;
-    int32_t* status;
-    __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity) const {
-        for (uint32_t i = 0; i < (1u << 22); ++i) {
-            if (mbar_try_wait(bar, parity)) return;
-            if (i > 64) { if (*abort_flag) return; __nanosleep(32); }
-        }
-        *abort_flag = 1;
-        if (status) atomicOr(status, 1);
-    }
-};
 
 template <typename T> struct Pk;
 template <> struct Pk<__nv_bfloat16> { static constexpr uint32_t FMT = 1;
@@ -57,9 +54,50 @@ template <> struct Pk<__half> { static constexpr uint32_t FMT = 0;
 
 struct GsMaps { CUtensorMap x, w, o; };
 
-// S = subtiles of 128 rows per CTA tile (1 or 2); KB = K / 64.
+// silu(g) * y for 32 features of a row, packed to 16-bit pairs.  The arithmetic runs two-wide (mul / fma .f32x2 on register
+// pairs: the epilogue warps are bound by instruction issue); each lane of those is the scalar IEEE operation.
 template <typename T>
-__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __grid_constant__ GsMaps maps, int M, int I, int KB, int S, int nsplit, int32_t* status) {
+__device__ __forceinline__ void swiglu_pack(const float* g, const float* y, uint32_t* pk) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        unsigned long long g2, y2, h2, half2, s2, r2;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(g2) : "f"(g[e]), "f"(g[e + 1]));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(y2) : "f"(y[e]), "f"(y[e + 1]));
+        asm("mov.b64 %0, {%1, %1};" : "=l"(half2) : "f"(0.5f));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(h2) : "l"(g2), "l"(half2));
+        float h0, h1, t0, t1;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(h0), "=f"(h1) : "l"(h2));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t0) : "f"(h0));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t1) : "f"(h1));
+        asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "f"(t0), "f"(t1));
+        asm("fma.rn.f32x2 %0, %1, %2, %2;" : "=l"(s2) : "l"(s2), "l"(half2));   // sigmoid = 0.5 tanh(g / 2) + 0.5
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r2) : "l"(g2), "l"(y2));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r2) : "l"(r2), "l"(s2));
+        float r0, r1;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(r0), "=f"(r1) : "l"(r2));
+        pk[e / 2] = Pk<T>::pack(r0, r1);
+    }
+}
+
+// A warp's [32 rows x 32 features] piece goes out through its 2 KB box of shared memory (64-byte rows) as one TMA store.
+__device__ __forceinline__ void send_box(uint8_t* my_row, uint32_t box_u32, const uint32_t* pk, const CUtensorMap* map, int col, int row,
+                                         bool in_range, int lane) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the box
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        *reinterpret_cast<uint4*>(my_row + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0 && in_range) {
+        tma_store_2d(map, col, row, box_u32);      // rows past M are clipped by the tensor map
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+}
+
+// S = subtiles of 128 rows per CTA tile (1 or 2); KB = K / 64; G = k boxes handed over together (a divisor of KB, <= 3).
+template <typename T>
+__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __grid_constant__ GsMaps maps, int M, int I, int KB, int S, int G, int nsplit, int32_t* status) {
     extern __shared__ uint8_t gs_smem_raw[];
     uint8_t* smem = gs_smem_raw + ((1024u - (smem_u32(gs_smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
@@ -69,16 +107,18 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
     const uint32_t off_out = off_b + NSTAGE * B_STAGE_BYTES;
     const uint32_t off_bar = off_out + OUT_STAGE_BYTES;
     const uint32_t bar_a_full = sbase + off_bar, bar_a_empty = bar_a_full + 8 * MAX_KB;   // one pair per k box of the x tile
-    const uint32_t bar_b_full = bar_a_empty + 8 * MAX_KB, bar_b_empty = bar_b_full + 8 * NSTAGE;
+    const uint32_t bar_b_full = bar_a_empty + 8 * MAX_KB, bar_b_empty = bar_b_full + 8 * NSTAGE;   // one pair per group stage
     const uint32_t bar_acc_full = bar_b_empty + 8 * NSTAGE, bar_acc_empty = bar_acc_full + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (2 * MAX_KB + 2 * NSTAGE + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const GsWaiter waiter{abort_flag, status};
+    const Waiter waiter{abort_flag, status};
+    const int NG = NSTAGE / G;                     // group stages in the ring
+    const int groups = KB / G;                     // groups per feature block
 
     if (tid == 0) {
         for (int kb = 0; kb < MAX_KB; ++kb) { mbar_init(bar_a_full + 8 * kb, 1); mbar_init(bar_a_empty + 8 * kb, 1); }
         for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar_b_full + 8 * s, 1); mbar_init(bar_b_empty + 8 * s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 128 * S); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, 8 * S); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -96,122 +136,297 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
     const int nblocks_all = I / BNF;
     auto nb_begin = [&](int item) { return (int)((int64_t)(item % nsplit) * nblocks_all / nsplit); };
     auto nb_end = [&](int item) { return (int)((int64_t)(item % nsplit + 1) * nblocks_all / nsplit); };
-    constexpr uint32_t IDESC = (1u << 4) | (Pk<T>::FMT << 7) | (Pk<T>::FMT << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+    constexpr uint32_t IDESC = make_idesc(Pk<T>::FMT, 0, 0, 128, 128);
 
     if (warp == 0) {
         if (lane == 0) {                          // ---- TMA producer -------------------------------------------
             // The x tile is handed over per k box: box kb of the next tile is requested as soon as the last feature
-            // block of this tile has used box kb, just ahead of the weight stage that needs it.
+            // block of this tile has used box kb, just ahead of the weight group that needs it.
             uint32_t a_phase = 0, st = 0, b_phase = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
                 const int nb0 = nb_begin(tile), nb1 = nb_end(tile);
                 for (int nb = nb0; nb < nb1; ++nb)
-                    for (int kb = 0; kb < KB; ++kb) {
+                    for (int gi = 0; gi < groups; ++gi) {
                         if (nb == nb0) {
-                            waiter.wait(bar_a_empty + 8 * kb, a_phase ^ 1u);    // the previous tile's MMAs have read this box
-                            mbar_expect_tx(bar_a_full + 8 * kb, (uint32_t)S * A_BOX_BYTES);
-                            for (int s = 0; s < S; ++s)
-                                tma_load_2d(sbase + (s * KB + kb) * A_BOX_BYTES, &maps.x, kb * BK, (tile / nsplit) * BM + s * 128, bar_a_full + 8 * kb);
+                            for (int kb = gi * G; kb < (gi + 1) * G; ++kb) {
+                                waiter.wait(bar_a_empty + 8 * kb, a_phase ^ 1u);    // the previous tile's MMAs have read this box
+                                mbar_expect_tx(bar_a_full + 8 * kb, (uint32_t)S * A_BOX_BYTES);
+                                for (int s = 0; s < S; ++s)
+                                    tma_load_2d(sbase + (s * KB + kb) * A_BOX_BYTES, &maps.x, kb * BK, (tile / nsplit) * BM + s * 128, bar_a_full + 8 * kb);
+                            }
                         }
                         waiter.wait(bar_b_empty + 8 * st, b_phase ^ 1u);
-                        mbar_expect_tx(bar_b_full + 8 * st, B_STAGE_BYTES);
-                        const uint32_t dst = sbase + off_b + st * B_STAGE_BYTES;
-                        tma_load_2d(dst, &maps.w, kb * BK, nb * BNF, bar_b_full + 8 * st);                    // gate rows
-                        tma_load_2d(dst + BNF * BK * 2, &maps.w, kb * BK, I + nb * BNF, bar_b_full + 8 * st); // matching y rows
-                        if (++st == NSTAGE) { st = 0; b_phase ^= 1u; }
+                        mbar_expect_tx(bar_b_full + 8 * st, (uint32_t)G * B_STAGE_BYTES);
+                        for (int g = 0; g < G; ++g) {
+                            const int kb = gi * G + g;
+                            const uint32_t dst = sbase + off_b + (st * G + g) * B_STAGE_BYTES;
+                            tma_load_2d(dst, &maps.w, kb * BK, nb * BNF, bar_b_full + 8 * st);                    // gate rows
+                            tma_load_2d(dst + BNF * BK * 2, &maps.w, kb * BK, I + nb * BNF, bar_b_full + 8 * st); // matching y rows
+                        }
+                        if ((int)++st == NG) { st = 0; b_phase ^= 1u; }
                     }
                 a_phase ^= 1u;
             }
         }
     } else if (warp == 1) {                       // ---- MMA issuer ---------------------------------------------
-        // The whole warp walks the loop (uniform control flow keeps the descriptor arithmetic off the issuing lane's
-        // critical path); lane 0 issues.  Descriptors advance by adding to their 14-bit address field (16-byte units).
+        // Descriptors advance by adding to their 14-bit address field (16-byte units).
+        // A test of an mbarrier costs a few hundred cycles here even when its phase completed long ago (it queues behind the
+        // epilogue warps' shared-memory traffic), and while the warp waits for the answer nothing is issued to the tensor
+        // pipe.  The barriers of the next group (and of the next accumulator buffer) are therefore tested BEFORE the current
+        // group's last MMAs are issued (with the non-blocking test): the answer arrives while those are being issued, and the
+        // wait loop is entered only if it was "not yet".
+        const bool issuer = lane == 0;
         uint32_t a_phase = 0, st = 0, b_phase = 0, acc_it = 0;
         const uint32_t a_lo0 = make_desc(sbase), b_lo0 = make_desc(sbase + off_b);
         const uint32_t a_sub = (uint32_t)KB * (A_BOX_BYTES >> 4);
+        uint32_t pre_b = 0, pre_acc = 0;              // early answers for the next group's stage / the next block's buffer
         for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
             const int nb0 = nb_begin(tile), nb1 = nb_end(tile);
             for (int nb = nb0; nb < nb1; ++nb, ++acc_it) {
                 const uint32_t buf = acc_it & 1u;
-                waiter.wait(bar_acc_empty + 8 * buf, ((acc_it >> 1) & 1u) ^ 1u);    // the epilogue has drained this buffer
-                tc_fence_after();
+                if (!pre_acc) waiter.wait_lite(bar_acc_empty + 8 * buf, ((acc_it >> 1) & 1u) ^ 1u);    // the epilogue has drained this buffer
+                pre_acc = 0;
                 const uint32_t d0 = tmem + buf * (uint32_t)(S * 128);
-                uint32_t a_lo = a_lo0;
-                for (int kb = 0; kb < KB; ++kb) {
-                    if (nb == nb0) waiter.wait(bar_a_full + 8 * kb, a_phase);
-                    waiter.wait(bar_b_full + 8 * st, b_phase);
+                for (int gi = 0; gi < groups; ++gi) {
+                    if (nb == nb0)
+                        for (int kb = gi * G; kb < (gi + 1) * G; ++kb) waiter.wait_lite(bar_a_full + 8 * kb, a_phase);
+                    if (!pre_b) waiter.wait_lite(bar_b_full + 8 * st, b_phase);
                     tc_fence_after();
-                    const uint32_t b_lo = b_lo0 + st * (B_STAGE_BYTES >> 4);
-                    if (lane == 0) {
+                    const uint32_t st_next = (int)(st + 1) == NG ? 0u : st + 1, ph_next = (int)(st + 1) == NG ? b_phase ^ 1u : b_phase;
+                    for (int g = 0; g < G; ++g) {
+                        // early tests, put before the group's last k box (its MMAs give the answer time to arrive, and the
+                        // stage asked about has had the longest time to fill): the next group's stage, and before a
+                        // block's last group the next block's buffer
+                        if (g == G - 1) {
+                            pre_b = mbar_test_wait(bar_b_full + 8 * st_next, ph_next);
+                            if (gi == groups - 1) pre_acc = mbar_test_wait(bar_acc_empty + 8 * (buf ^ 1u), (((acc_it + 1) >> 1) & 1u) ^ 1u);
+                        }
+                        const int kb = gi * G + g;
+                        const uint32_t b_lo = b_lo0 + (st * G + g) * (B_STAGE_BYTES >> 4);
+                        const uint32_t a_lo = a_lo0 + kb * (A_BOX_BYTES >> 4);
                         for (int s = 0; s < S; ++s) {
                             const uint32_t a_s = a_lo + s * a_sub, d = d0 + (uint32_t)s * 128u;
-                            tc_mma(d, a_s, b_lo, IDESC, kb > 0 ? 1u : 0u);
-                            tc_mma(d, a_s + 2, b_lo + 2, IDESC, 1u);
-                            tc_mma(d, a_s + 4, b_lo + 4, IDESC, 1u);
-                            tc_mma(d, a_s + 6, b_lo + 6, IDESC, 1u);
+#pragma unroll
+                            for (uint32_t k4 = 0; k4 < 4; ++k4) { if (issuer) tc_mma(d, a_s + 2 * k4, b_lo + 2 * k4, IDESC, (kb | k4) > 0 ? 1u : 0u); }
                         }
-                        tc_commit(bar_b_empty + 8 * st);                // the stage is free when these MMAs are done
-                        if (nb == nb1 - 1) tc_commit(bar_a_empty + 8 * kb);   // and, in the tile's last block, so is the x box
                     }
-                    __syncwarp();
-                    a_lo += A_BOX_BYTES >> 4;
-                    if (++st == NSTAGE) { st = 0; b_phase ^= 1u; }
+                    if (issuer) tc_commit(bar_b_empty + 8 * st);        // the group's stage is free when these MMAs are done
+                    if (nb == nb1 - 1)                                  // and, in the tile's last block, so are its x boxes
+                        for (int kb = gi * G; kb < (gi + 1) * G; ++kb) { if (issuer) tc_commit(bar_a_empty + 8 * kb); }
+                    st = st_next; b_phase = ph_next;
                 }
-                if (lane == 0) tc_commit(bar_acc_full + 8 * buf);
-                __syncwarp();
+                if (issuer) tc_commit(bar_acc_full + 8 * buf);
+                if (*abort_flag) break;
             }
+            if (*abort_flag) break;
             a_phase ^= 1u;
         }
     } else {                                      // ---- epilogue: silu(gate) * y -> out ----------------------------
-        const int ew = warp - 2;                  // 0..7
-        const int sub = ew >> 2;                  // subtile
+        const int ew = warp - 2;                  // 0..15
+        const int sub = (ew >> 2) & 1;            // subtile
+        const int fh = ew >> 3;                   // which 32 of the block's 64 features
         if (sub < S) {
-            const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
+            const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;   // a warp reads the TMEM lanes of its quarter
             const int r_in_tile = sub * 128 + 32 * (warp & 3);          // first of this warp's 32 rows within the tile
-            uint8_t* box = smem + off_out + ew * OUT_BOX_BYTES;
+            uint8_t* my_row = smem + off_out + ew * OUT_BOX_BYTES + lane * 64;
             const uint32_t box_u32 = sbase + off_out + ew * OUT_BOX_BYTES;
-            uint8_t* my_row = box + lane * 128;
-            const uint32_t sw = (uint32_t)(lane & 7);
             uint32_t acc_it = 0;
             for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
                 const int row0 = (tile / nsplit) * BM + r_in_tile;
                 for (int nb = nb_begin(tile); nb < nb_end(tile); ++nb, ++acc_it) {
                     const uint32_t buf = acc_it & 1u;
-                    waiter.wait(bar_acc_full + 8 * buf, (acc_it >> 1) & 1u);   // by the whole warp: a wait by one lane with the others parked at a warp barrier resumes microseconds late
-                    __syncwarp();
+                    waiter.wait_lite(bar_acc_full + 8 * buf, (acc_it >> 1) & 1u);   // by the whole warp: a wait by one lane with the others parked at a warp barrier resumes microseconds late
+                    if (*abort_flag) break;
                     tc_fence_after();
-                    const uint32_t acc = tmem + lane_base + buf * (uint32_t)(S * 128) + (uint32_t)sub * 128u;
-                    uint32_t pk[BNF / 2];
-#pragma unroll
-                    for (int c = 0; c < BNF; c += 32) {
-                        float g[32], y[32];
-                        tc_ld32(acc + c, g);
-                        tc_ld32(acc + BNF + c, y);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2)
-                            pk[(c + e) / 2] = Pk<T>::pack(g[e] * y[e] * sigmoid_tanh(g[e]), g[e + 1] * y[e + 1] * sigmoid_tanh(g[e + 1]));
-                    }
+                    const uint32_t acc = tmem + lane_base + buf * (uint32_t)(S * 128) + (uint32_t)sub * 128u + 32u * fh;
+                    float g[32], y[32];
+                    tc_ld32(acc, g);
+                    tc_ld32(acc + BNF, y);
+                    tc_wait_ld();
                     tc_fence_before();
-                    mbar_arrive_plain(bar_acc_empty + 8 * buf);               // the accumulator is in registers: the MMA warp may refill it
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the box
                     __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < BNF / 8; ++j)
-                        *reinterpret_cast<uint4*>(my_row + (((uint32_t)j ^ sw) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0 && row0 < M) {
-                        tma_store_2d(&maps.o, nb * BNF, row0, box_u32);  // rows past M are clipped by the tensor map
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
+                    if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
+                    uint32_t pk[16];
+                    swiglu_pack<T>(g, y, pk);
+                    send_box(my_row, box_u32, pk, &maps.o, nb * BNF + 32 * fh, row0, row0 < M, lane);
                 }
+                if (*abort_flag) break;
             }
             if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA exits
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (tid == 0 && *abort_flag && status) atomicOr(status, 1);
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Wide form, for K <= 192 and I % 128 == 0 (the shipped MLP shapes at widths up to 192).
+//
+// A 128x128x16 MMA takes ~80-130 cycles here where a 128x256x16 one takes ~130: at N = 128 the tensor pipe runs at half its
+// rate.  This form multiplies one 128-row subtile by 128 gate rows and their 128 y rows at once (N = 256), so a unit of
+// work is (feature block of 128, subtile) and its accumulator [128 x 256] takes half of tensor memory; the two halves
+// double-buffer (unit u+1 is multiplied while unit u is read out).  Both subtiles of a tile use the same weight boxes,
+// which therefore stay in their ring slots for two units: a 96 KB ring of three 32 KB boxes holds exactly one block's
+// boxes at K = 192, so the reload of a box for the next block (from L2) starts when the second subtile has used it and
+// is only partly hidden -- still far cheaper than running the tensor pipe at half rate.  x boxes are released per
+// subtile, so the first subtile's part of the next tile streams in while the second subtile of the last block is multiplied.
+constexpr int WB_FEAT = 128;                         // features per block
+constexpr int WB_BOX_BYTES = 2 * WB_FEAT * BK * 2;   // one k box of weights: 128 gate rows + 128 y rows, 32 KB
+constexpr int WB_RING = 3;
+
+struct GsWideMaps { CUtensorMap x, w, o; };
+
+template <typename T>
+__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const __grid_constant__ GsWideMaps maps, int M, int I, int KB, int32_t* status) {
+    extern __shared__ uint8_t gs_smem_raw[];
+    uint8_t* smem = gs_smem_raw + ((1024u - (smem_u32(gs_smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t off_b = 2u * KB * A_BOX_BYTES;
+    const uint32_t off_out = off_b + WB_RING * WB_BOX_BYTES;
+    const uint32_t off_bar = off_out + OUT_STAGE_BYTES;
+    // barriers: x boxes per (subtile, k box): full / empty; weight ring slots: full / empty; accumulator halves: full / empty
+    const uint32_t bar_a_full = sbase + off_bar, bar_a_empty = bar_a_full + 8 * 6;
+    const uint32_t bar_b_full = bar_a_empty + 8 * 6, bar_b_empty = bar_b_full + 8 * WB_RING;
+    const uint32_t bar_acc_full = bar_b_empty + 8 * WB_RING, bar_acc_empty = bar_acc_full + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (12 + 2 * WB_RING + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const Waiter waiter{abort_flag, status};
+
+    if (tid == 0) {
+        for (int i = 0; i < 6; ++i) { mbar_init(bar_a_full + 8 * i, 1); mbar_init(bar_a_empty + 8 * i, 1); }
+        for (int i = 0; i < WB_RING; ++i) { mbar_init(bar_b_full + 8 * i, 1); mbar_init(bar_b_empty + 8 * i, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, GS_EPI_WARPS); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int ntiles = (M + 255) / 256;
+    const int nblocks = I / WB_FEAT;
+    constexpr uint32_t IDESC = make_idesc(Pk<T>::FMT, 0, 0, 128, 256);
+
+    if (warp == 0) {
+        if (lane == 0) {                          // ---- TMA producer -------------------------------------------
+            uint32_t a_phase = 0, slot = 0, b_phase = 0;
+            auto load_x = [&](int tile, int s, int kb) {
+                const uint32_t i = (uint32_t)(s * 3 + kb);
+                waiter.wait(bar_a_empty + 8 * i, a_phase ^ 1u);         // the previous tile's MMAs have read this box
+                mbar_expect_tx(bar_a_full + 8 * i, A_BOX_BYTES);
+                tma_load_2d(sbase + (s * KB + kb) * A_BOX_BYTES, &maps.x, kb * BK, tile * 256 + s * 128, bar_a_full + 8 * i);
+            };
+            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+                for (int nb = 0; nb < nblocks; ++nb) {
+                    for (int kb = 0; kb < KB; ++kb) {
+                        if (nb == 0) load_x(tile, 0, kb);               // first subtile's box just ahead of the weights that meet it
+                        waiter.wait(bar_b_empty + 8 * slot, b_phase ^ 1u);
+                        if (*abort_flag) { tile = ntiles; nb = nblocks; break; }
+                        mbar_expect_tx(bar_b_full + 8 * slot, WB_BOX_BYTES);
+                        const uint32_t dst = sbase + off_b + slot * WB_BOX_BYTES;
+                        tma_load_2d(dst, &maps.w, kb * BK, nb * WB_FEAT, bar_b_full + 8 * slot);                       // gate rows
+                        tma_load_2d(dst + WB_FEAT * BK * 2, &maps.w, kb * BK, I + nb * WB_FEAT, bar_b_full + 8 * slot); // matching y rows
+                        if (++slot == WB_RING) { slot = 0; b_phase ^= 1u; }
+                    }
+                    if (nb == 0)
+                        for (int kb = 0; kb < KB; ++kb) load_x(tile, 1, kb);
+                }
+                a_phase ^= 1u;
+            }
+        }
+    } else if (warp == 1) {                       // ---- MMA issuer ---------------------------------------------
+        const bool issuer = lane == 0;
+        uint32_t a_phase = 0, slot0 = 0, b_phase0 = 0, unit = 0;
+        const uint32_t a_lo0 = make_desc(sbase), b_lo0 = make_desc(sbase + off_b);
+        uint32_t pre_acc = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            for (int nb = 0; nb < nblocks; ++nb) {
+                for (int s = 0; s < 2; ++s, ++unit) {
+                    const uint32_t buf = unit & 1u;
+                    if (!pre_acc) waiter.wait_lite(bar_acc_empty + 8 * buf, ((unit >> 1) & 1u) ^ 1u);   // the epilogue has read this half out
+                    pre_acc = 0;
+                    if (*abort_flag) break;
+                    const uint32_t d = tmem + buf * 256u;
+                    uint32_t slot = slot0, b_phase = b_phase0;
+                    // the first subtile meets freshly loaded weight boxes: ask about all of them at once (one round trip)
+                    uint32_t have[3] = {1u, 1u, 1u};
+                    if (s == 0) {
+                        uint32_t sl = slot0, ph = b_phase0;
+                        for (int kb = 0; kb < KB; ++kb) {
+                            have[kb] = mbar_test_wait(bar_b_full + 8 * sl, ph);
+                            if (++sl == WB_RING) { sl = 0; ph ^= 1u; }
+                        }
+                    }
+                    for (int kb = 0; kb < KB; ++kb) {
+                        if (nb == 0) waiter.wait_lite(bar_a_full + 8 * (uint32_t)(s * 3 + kb), a_phase);
+                        if (!have[kb]) waiter.wait_lite(bar_b_full + 8 * slot, b_phase);
+                        tc_fence_after();
+                        // asked before the unit's last MMAs, answered while they are issued: is the other half free?
+                        if (kb == KB - 1) pre_acc = mbar_test_wait(bar_acc_empty + 8 * (buf ^ 1u), (((unit + 1) >> 1) & 1u) ^ 1u);
+                        const uint32_t a_lo = a_lo0 + (uint32_t)(s * KB + kb) * (A_BOX_BYTES >> 4);
+                        const uint32_t b_lo = b_lo0 + slot * (WB_BOX_BYTES >> 4);
+#pragma unroll
+                        for (uint32_t k4 = 0; k4 < 4; ++k4) { if (issuer) tc_mma(d, a_lo + 2 * k4, b_lo + 2 * k4, IDESC, (kb | k4) > 0 ? 1u : 0u); }
+                        if (s == 1) { if (issuer) tc_commit(bar_b_empty + 8 * slot); }                 // both subtiles have used the box
+                        if (nb == nblocks - 1) { if (issuer) tc_commit(bar_a_empty + 8 * (uint32_t)(s * 3 + kb)); }   // the tile's last use of the x box
+                        if (++slot == WB_RING) { slot = 0; b_phase ^= 1u; }
+                    }
+                    if (issuer) tc_commit(bar_acc_full + 8 * buf);
+                    if (s == 1) { slot0 = slot; b_phase0 = b_phase; }
+                }
+                if (*abort_flag) break;
+            }
+            if (*abort_flag) break;
+            a_phase ^= 1u;
+        }
+    } else {                                      // ---- epilogue: silu(gate) * y -> out ----------------------------
+        const int ew = warp - 2;                  // 0..15
+        const int fq = ew >> 2;                   // which 32 of the block's 128 features
+        const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;   // a warp reads the TMEM lanes of its quarter
+        uint8_t* my_row = smem + off_out + ew * OUT_BOX_BYTES + lane * 64;
+        const uint32_t box_u32 = sbase + off_out + ew * OUT_BOX_BYTES;
+        uint32_t unit = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+            for (int nb = 0; nb < nblocks; ++nb) {
+                for (int s = 0; s < 2; ++s, ++unit) {
+                    const uint32_t buf = unit & 1u;
+                    waiter.wait_lite(bar_acc_full + 8 * buf, (unit >> 1) & 1u);   // by the whole warp
+                    if (*abort_flag) break;
+                    tc_fence_after();
+                    const uint32_t acc = tmem + lane_base + buf * 256u + 32u * fq;
+                    float g[32], y[32];
+                    tc_ld32(acc, g);
+                    tc_ld32(acc + WB_FEAT, y);
+                    tc_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
+                    uint32_t pk[16];
+                    swiglu_pack<T>(g, y, pk);
+                    const int row0 = tile * 256 + s * 128 + 32 * (warp & 3);
+                    send_box(my_row, box_u32, pk, &maps.o, nb * WB_FEAT + 32 * fq, row0, row0 < M, lane);
+                }
+                if (*abort_flag) break;
+            }
+            if (*abort_flag) break;
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA exits
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag && status) atomicOr(status, 1);
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
@@ -222,6 +437,16 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
 }  // namespace vig
 
 using namespace vig;
+
+// [rows, cols] output with leading dimension ld: boxes of 32 rows x 32 columns (64-byte rows, no swizzle), one per epilogue warp
+static bool make_out_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int dtype) {
+    tc::MapKey key{};
+    key.base = base; key.rank = 2; key.dtype = dtype; key.swizzle = 0;
+    key.dims[0] = (uint64_t)cols; key.dims[1] = (uint64_t)rows;
+    key.strides[0] = (uint64_t)ld * 2;
+    key.box[0] = 32; key.box[1] = 32;
+    return tc::encode_cached(m, key);
+}
 
 extern "C" int vig_linear_swiglu_supported(int64_t M, int K, int I, int dtype) {
     if (dtype != VIG_DTYPE_BF16 && dtype != VIG_DTYPE_F16) return 0;
@@ -243,16 +468,36 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     if (!vig_linear_swiglu_supported(M, K, I, dtype)) return VIG_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) return VIG_ERR_ALIGN;
     if (ldx < K || ldo < I || (ldx * 2) % 16 || (ldo * 2) % 16 || M >= (1ll << 31)) return VIG_ERR_ARG;
-    GsMaps maps;
-    if (!tc::make_map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !tc::make_map_2d(&maps.w, w, 2 * (int64_t)I, K, K, BNF, dtype) ||
-        !tc::make_map_2d(&maps.o, out, M, I, ldo, 32, dtype)) return VIG_ERR_DEVICE;
     const int KB = K / BK;
-    const int S = ((int64_t)256 * K * 2 <= MAX_A_BYTES && M > 128) ? 2 : 1;
-    const int smem = S * KB * A_BOX_BYTES + NSTAGE * B_STAGE_BYTES + OUT_STAGE_BYTES + 8 * (2 * MAX_KB + 2 * NSTAGE + 4) + 16 + 1024;
     int dev = 0, sms = 0;
     cudaError_t e;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+    if (KB <= 3 && I % WB_FEAT == 0 && M >= 256 * (int64_t)sms) {
+        // wide form: N = 256 MMAs on tiles of 256 rows, when there are enough of them to fill the machine
+        GsWideMaps maps;
+        if (!tc::make_map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !tc::make_map_2d(&maps.w, w, 2 * (int64_t)I, K, K, WB_FEAT, dtype) ||
+            !make_out_map(&maps.o, out, M, I, ldo, dtype)) return VIG_ERR_DEVICE;
+        const int smem = 2 * KB * A_BOX_BYTES + WB_RING * WB_BOX_BYTES + OUT_STAGE_BYTES + 8 * (12 + 2 * WB_RING + 4) + 16 + 1024;
+        const int ntiles = (int)((M + 255) / 256);
+        const int grid = ntiles < sms ? ntiles : sms;
+        if (dtype == VIG_DTYPE_BF16) {
+            auto kfn = linear_swiglu_wide_kernel<__nv_bfloat16>;
+            if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
+            kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, status_dev);
+        } else {
+            auto kfn = linear_swiglu_wide_kernel<__half>;
+            if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
+            kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, status_dev);
+        }
+        return (int)cudaGetLastError();
+    }
+    GsMaps maps;
+    if (!tc::make_map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !tc::make_map_2d(&maps.w, w, 2 * (int64_t)I, K, K, BNF, dtype) ||
+        !make_out_map(&maps.o, out, M, I, ldo, dtype)) return VIG_ERR_DEVICE;
+    const int G = KB % 3 == 0 ? 3 : (KB % 2 == 0 ? 2 : 1);       // k boxes handed over together
+    const int S = ((int64_t)256 * K * 2 <= MAX_A_BYTES && M > 128) ? 2 : 1;
+    const int smem = S * KB * A_BOX_BYTES + NSTAGE * B_STAGE_BYTES + OUT_STAGE_BYTES + 8 * (2 * MAX_KB + 2 * NSTAGE + 4) + 16 + 1024;
     // few row tiles (small M): split the feature blocks of a tile over several work items so every SM has work
     const int mtiles = (int)((M + 128 * S - 1) / (128 * S));
     int nsplit = (3 * sms + mtiles - 1) / mtiles;
@@ -263,11 +508,11 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     if (dtype == VIG_DTYPE_BF16) {
         auto kfn = linear_swiglu_kernel<__nv_bfloat16>;
         if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
-        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, nsplit, status_dev);
+        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, G, nsplit, status_dev);
     } else {
         auto kfn = linear_swiglu_kernel<__half>;
         if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
-        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, nsplit, status_dev);
+        kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, S, G, nsplit, status_dev);
     }
     return (int)cudaGetLastError();
 }

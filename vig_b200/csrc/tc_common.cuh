@@ -30,6 +30,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+// Non-blocking test of a phase (try_wait may suspend the thread for a hardware-defined time when the phase is pending;
+// this form answers at once): for polls issued ahead of time, whose answer is looked at later.
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
 // The same test, but the hardware may park the thread for up to `ns` nanoseconds while the phase is pending and
 // wakes it when the phase completes: a waiting warp then issues almost no instructions.
 __device__ __forceinline__ uint32_t mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
