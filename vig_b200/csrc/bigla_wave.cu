@@ -255,6 +255,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 // control flow stays convergent, so loop counters and descriptor arithmetic run in the uniform datapath
                 // instead of on the issuing lane (a lane-0 branch around the loops made every MMA cost ~150 cycles to issue).
                 const bool issuer = lane == 0;
+                // the barriers of (b) are asked about before (a) and the state update are issued, that of (c) before (b)
+                const uint32_t pre_st = mbar_test_wait(bar(B_STREADY), m & 1);
+                const uint32_t pre_of = m >= 2 ? mbar_test_wait(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1) : 1u;
                 // (a) scores, and right behind them the state update: it needs only the prepared tiles, and the
                 // state chain -- the one sequential dependency of the kernel -- waits for nothing else
 #pragma unroll
@@ -264,8 +267,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) { if (issuer) tc_mma(u_acc, k_lo + 128 * k8, v_lo + 128 * k8, IDESC_U, k8 > 0); }
                 if (issuer) tc_commit(bar(B_UFULL + (m & 1u)));
                 // (b) product with the entering state
-                waiter.wait_lite(bar(B_STREADY), m & 1);
-                if (m >= 2) waiter.wait_lite(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
+                if (!pre_st) waiter.wait_lite(bar(B_STREADY), m & 1);
+                if (!pre_of) waiter.wait_lite(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1);
+                const uint32_t pre_pr = mbar_test_wait(bar(B_PREADY), m & 1);
                 tc_fence_after();
                 if (!s_zero) {
 #pragma unroll
@@ -273,7 +277,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 }
                 if (issuer) tc_commit(bar(B_STFREE));          // the state operand may be overwritten
                 // (c) masked scores x v
-                waiter.wait_lite(bar(B_PREADY), m & 1);
+                if (!pre_pr) waiter.wait_lite(bar(B_PREADY), m & 1);
                 tc_fence_after();
 #pragma unroll
                 for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) {
@@ -348,6 +352,13 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             float4 gl[4];                                     // cumulative log2-gates of my 4 tokens, from the group's first token
             uint8_t* stg = smem + s * W_STAGE_B;
             int dmask = 0;
+            // A test of an mbarrier costs a few hundred cycles even when its phase completed long ago (it queues behind the
+            // CTA's shared-memory traffic).  The barriers this trip will need are therefore all asked about here, at once and
+            // without blocking; the answers arrive during the gate phase, and a wait loop is entered later only on "not yet".
+            uint32_t pre_pfull = 0, pre_ufull = 0, pre_ofull = 0, pre_xfree = 0;
+            if (m >= 1) { pre_pfull = mbar_test_wait(bar(B_PFULL), (m - 1) & 1); pre_ufull = mbar_test_wait(bar(B_UFULL + ((m - 1) & 1)), ((m - 1) >> 1) & 1); }
+            if (m >= 2) pre_ofull = mbar_test_wait(bar(B_OFULL + (m & 1)), ((m - 2) >> 1) & 1);
+            if (m >= 3) pre_xfree = mbar_test_wait(bar(B_XFREE), (m - 3) & 1);
             if (!ended) {
             waiter.wait_lite(bar(B_FULL + s), (m / 3) & 1);
             __syncwarp();
@@ -406,14 +417,14 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // ---- scores of iteration j = m - 1: TMEM -> masked 16-bit tiles (my 32 rows x key block `sub`) ----
             if (m >= 1 && (!ended || m - 1 < end_m)) {
                 const uint32_t j = m - 1;
-                waiter.wait_lite(bar(B_PFULL), j & 1);
+                if (!pre_pfull) waiter.wait_lite(bar(B_PFULL), j & 1);
                 __syncwarp();
                 if (*abort_flag) break;
                 tc_fence_after();
                 const int cb = sub, dir = dir_mask_it;
                 uint8_t* stj = smem + (j % 3) * W_STAGE_B;
                 if (cb >= 2) {                                // keys 64..127 go over the k tile: the state update must have read it
-                    waiter.wait_lite(bar(B_UFULL + (j & 1)), (j >> 1) & 1);
+                    if (!pre_ufull) waiter.wait_lite(bar(B_UFULL + (j & 1)), (j >> 1) & 1);
                     __syncwarp();
                 }
                 uint8_t* prow = stj + (cb < 2 ? WS_G : WS_K) + row * 128;
@@ -448,8 +459,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // ---- output of iteration j = m - 2: accumulator slot -> 16-bit staging tile (my 32 rows x 16 columns) ----
             if (m >= 2 && (!ended || m - 2 < end_m)) {
                 const uint32_t j = m - 2;
-                waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
-                if (j > 0) waiter.wait_lite(bar(B_XFREE), (j - 1) & 1);        // the store thread has sent the previous tile
+                if (!pre_ofull) waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
+                if (j > 0 && !pre_xfree) waiter.wait_lite(bar(B_XFREE), (j - 1) & 1);        // the store thread has sent the previous tile
                 __syncwarp();
                 if (*abort_flag) break;
                 tc_fence_after();
@@ -477,6 +488,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // raw operand rows into registers
             uint2 rk[4], rq[4];
             uint32_t offs[4];
+            const uint32_t pre_part = mbar_test_wait(bar(B_PART + (m & 1)), (m >> 1) & 1);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const uint32_t r7 = (uint32_t)((half * 4 + u) ^ dmask);
@@ -484,7 +496,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 rk[u] = *reinterpret_cast<const uint2*>(stg + WS_K + offs[u]);
                 rq[u] = *reinterpret_cast<const uint2*>(stg + WS_Q + offs[u]);
             }
-            waiter.wait_lite(bar(B_PART + (m & 1)), (m >> 1) & 1);     // all sixteen group sums are in
+            if (!pre_part) waiter.wait_lite(bar(B_PART + (m & 1)), (m >> 1) & 1);     // all sixteen group sums are in
             __syncwarp();
             if (*abort_flag) break;
             // ---- my group's offset: (sum of the groups scanned before mine) - G_ref, G_ref = sum of the first 8 groups in
