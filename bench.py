@@ -143,7 +143,9 @@ def run_reference(args, rank):
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": workload_config(args, batch),
             "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": "port", "sample": sample},
-            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "reference_gpu_path": "not run: the reference's GPU operators are Triton kernels (fla/ops/gla/*.py), a tracing "
+                                  "compiler path this arm does not execute; this arm is its naive PyTorch recurrence on the host cores"}
     print(json.dumps(line), flush=True)
 
 
@@ -238,6 +240,10 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    # before anything is timed: the scan at the workload's shape, default routing against the three-launch tensor-core form
+    # on the same seeded inputs (two different kernels of the product; the oracle is not involved)
+    output_check = scan_self_check(vig_b200, batch, shape.num_heads, L, shape.key_dim // shape.num_heads,
+                                   shape.value_dim // shape.num_heads, dev)
     for _ in range(max(args.warmup, 3)):
         step()
     vops.check_status()          # no kernel reported a run-out wait or an out-of-range gate during warm-up
@@ -350,7 +356,7 @@ def main():
                 "data": "synthetic", "config": workload_config(args, batch), "clocks": clocks, "gpu_launches": launches,
                 "e2e": {"value": total_images / (ms_e2e * 1e-3), "unit": "images/s",
                         "h2d_bytes_per_step": host_images.numel() * 2, "d2h_bytes_per_step": host_logits.numel() * 2},
-                "roofline": roofline, "graph": bool(args.graph)}
+                "roofline": roofline, "graph": bool(args.graph), "output_check": output_check}
         if seq_split_line is not None:
             line["seq_split"] = seq_split_line
         if world == 1 and not args.no_cpu_baseline:
@@ -361,6 +367,27 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def scan_self_check(vig_b200, B, H, L, dk, dv, dev, bar=1e-2):
+    """The bi-GLA operator at the benchmark's shape: default routing vs ``IMPL_TC_SPLIT`` on seeded inputs laid out as the
+    block hands them over (strided views of packed projections, raw gate logits).  Raises if they differ by more than
+    ``bar`` (max-norm relative; both are bf16 kernels with different summation orders)."""
+    from vig_b200 import _lib
+    gen = torch.Generator(device=dev).manual_seed(7)
+    z = torch.randn(B, L, 2 * H * dk + H * dv, generator=gen, device=dev).to(torch.bfloat16)
+    x = (2.0 * torch.randn(B, L, 2 * H * dk, generator=gen, device=dev)).to(torch.bfloat16)
+    heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)
+    a = (heads(z[..., :H * dk], dk), heads(z[..., H * dk:2 * H * dk], dk), heads(z[..., 2 * H * dk:], dv),
+         heads(x[..., :H * dk], dk), heads(x[..., H * dk:], dk))
+    kw = dict(out_scale=0.25, gate_logit_normalizer=16.0)
+    o = vig_b200.bi_gla(*a, **kw).float()
+    o_ref = vig_b200.bi_gla(*a, impl=_lib.IMPL_TC_SPLIT, **kw).float()
+    vig_b200.check_status()
+    err = float((o - o_ref).abs().max() / o_ref.abs().max())
+    if not err < bar:
+        raise RuntimeError(f"scan self-check failed: default routing vs three-launch form differ by {err:.3e}")
+    return {"scan_default_vs_three_launch_rel_err": err, "bar": bar, "shape": [B, H, L, dk, dv]}
 
 
 def run_seq_split(vig_b200, vops, oracle, dev, rank, world, steps=5, warmup=3):

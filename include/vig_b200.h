@@ -181,6 +181,18 @@ VIG_API int vig_dwconv3x3_halo_fwd(const void* x, const void* top, const void* b
                            const void* bias, void* y, int B, int h, int w, int C, int act_silu, int dtype, void* stream);
 
 /*
+ * out[M, N] = x W^T + bias as one tensor-core GEMM with the bias added in fp32 before the rounding: the stacked input
+ * projection of the block -- qkv_proj, g_proj and gk_proj of GatedLinearAttention read the same conv output
+ * (classification/models/vig.py:283-290, 431-439), so their weights are stacked into one [N, K] matrix.
+ * x: [M, K] rows ldx elements apart, w: [N, K] contiguous, bias: [N] or NULL, out: [M, N] rows ldo apart; bf16 / fp16.
+ * vig_linear_bias_supported: K % 64 == 0, K <= 192, N % 8 == 0 and at least 256 rows per SM of the current device
+ * (smaller problems are left to a library GEMM).  status_dev: optional int32 on the device, bit 0 = a bounded wait ran out.
+ */
+VIG_API int vig_linear_bias_supported(int64_t M, int K, int N, int dtype);
+VIG_API int vig_linear_bias_fwd(const void* x, int64_t ldx, const void* w, const void* bias, void* out, int64_t ldo,
+                        int64_t M, int K, int N, int dtype, int32_t* status_dev, void* stream);
+
+/*
  * 2-D gating locality injection: y = RMSNorm_g(o) * sigmoid(gate_logits) + RMSNorm_l(local) * (1 - sigmoid),
  * head-wise norms over dv, optional swish on y.  Replaces l_norm, g_norm, sigmoid, the blend, out_act and
  * the `b h l d -> b l h d` transposes of classification/models/vig.py:444-457 (norm:

@@ -21,7 +21,8 @@ def declared_symbols():
 def test_header_declares_the_path():
     names = declared_symbols()
     for required in ("vig_bigla_fwd", "vig_bigla_workspace_bytes", "vig_dwconv3x3_fwd", "vig_gate_inject_fwd",
-                     "vig_add_rmsnorm_fwd", "vig_swiglu_fwd", "vig_version", "vig_strerror"):
+                     "vig_add_rmsnorm_fwd", "vig_swiglu_fwd", "vig_version", "vig_strerror", "vig_linear_bias_fwd",
+                     "vig_linear_bias_supported"):
         assert required in names
 
 

@@ -223,6 +223,30 @@ def test_linear_swiglu_fused_gemm(dtype, M, K, I):
     assert rel_err(out.float(), ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N,bias", [(40000, 192, 1152, True), (38000, 64, 96, True), (37930, 128, 320, False), (262144, 192, 1152, True)])
+def test_linear_bias_gemm(dtype, M, K, N, bias):
+    """The stacked input projection as the library's own tensor-core GEMM: against the fp32 product at the type's bar, and
+    against the vendor GEMM (same roundings: fp32 accumulate, bias added in fp32, one rounding) to a few output steps.
+    Shapes: the block's N = 1152 at a ragged M, a last column block that is mostly past N, no bias, the benchmark's M."""
+    import vig_b200
+    from vig_b200 import ops
+    g = torch.Generator().manual_seed(M + N)
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype).cuda()
+    b = torch.randn(N, generator=g).to(dtype).cuda() if bias else None
+    assert ops.linear_bias_supported(x, w)
+    out = ops.linear_bias(x.view(2, M // 2, K), w, b)
+    vig_b200.check_status()
+    assert out.shape == (2, M // 2, N)
+    out = out.view(M, N)
+    rows = torch.cat([torch.arange(0, 4096), torch.arange(M - 4096, M)]).cuda()      # both ends (the last tile is ragged)
+    ref = x[rows].float() @ w.float().t() + (b.float() if bias else 0.0)
+    assert rel_err(out[rows].float().cpu(), ref.cpu()) < TOL[dtype]
+    lib = torch.nn.functional.linear(x, w, b)
+    assert rel_err(out.float().cpu(), lib.float().cpu()) < (1.6e-2 if dtype == torch.bfloat16 else 2e-3)
+
+
 def _shape(preset):
     base = oracle.PRESETS[preset]
     return oracle.ViGShape(**{**base.__dict__, "depth": 2, "num_classes": 16})

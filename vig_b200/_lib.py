@@ -32,6 +32,8 @@ _SIGNATURES = {
     "vig_gate_inject_fwd": (c_int, [c_void_p, _P64] + [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_float, c_int, c_int, c_void_p]),
     "vig_add_rmsnorm_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_void_p]),
     "vig_layernorm_act_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_float, c_int, c_int, c_void_p]),
+    "vig_linear_bias_supported": (c_int, [c_int64, c_int, c_int, c_int]),
+    "vig_linear_bias_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
     "vig_linear_swiglu_supported": (c_int, [c_int64, c_int, c_int, c_int]),
     "vig_linear_swiglu_preferred": (c_int, [c_int64, c_int, c_int, c_int]),
     "vig_linear_swiglu_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -495,6 +495,34 @@ def linear_swiglu(x, weight):
     return out
 
 
+def linear_bias_supported(x, weight):
+    """True when ``linear_bias`` has a kernel for this input (bf16 / fp16, K % 64 == 0, K <= 192, N % 8 == 0, at least 256
+    rows per SM -- the stacked input projection of the block at widths up to 192 and large batches)."""
+    if not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or weight.dtype != x.dtype or not weight.is_contiguous():
+        return False
+    K, N = x.shape[-1], weight.shape[0]
+    with torch.cuda.device(x.device):
+        return bool(_lib.lib().vig_linear_bias_supported(x.numel() // K, K, N, _lib.dtype_code(x)))
+
+
+def linear_bias(x, weight, bias=None):
+    """``F.linear(x, weight, bias)`` as this library's tensor-core GEMM (the stacked ``qkv_proj`` / ``g_proj`` / ``gk_proj``
+    of ``GatedLinearAttention``, ``vig.py:283-290``): x ``[..., K]``, weight ``[N, K]``, bias ``[N]`` or None."""
+    _lib.require_cuda(x, weight, bias)
+    K, N = x.shape[-1], weight.shape[0]
+    x2 = x.reshape(-1, K)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    if bias is not None and (bias.dtype != x.dtype or not bias.is_contiguous() or bias.shape != (N,)):
+        raise ValueError("bias must be a contiguous [N] tensor of x's dtype")
+    out = torch.empty(*x.shape[:-1], N, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.lib().vig_linear_bias_fwd(_lib.ptr(x2), x2.stride(0), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(out), N, x2.shape[0],
+                                            K, N, _lib.dtype_code(x), _status_ptr(None, x.device), _lib.stream_ptr())
+    _lib.check(st, "vig_linear_bias_fwd")
+    return out
+
+
 def swiglu_linear(x, y, weight, bias):
     """``fla/modules/activations.py:150-174``: ``F.linear(swiglu(x, y), weight, bias)``."""
     return torch.nn.functional.linear(swiglu(x, y), weight, bias)
