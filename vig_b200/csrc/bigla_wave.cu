@@ -61,7 +61,7 @@ constexpr int W_SMEM_BYTES = WO_MISC + 16;                    // the dynamic sha
 static_assert(W_SMEM_BYTES <= 227 * 1024, "shared memory budget");
 
 // TMEM columns (fp32): scores, state update, two output slots
-constexpr uint32_t WT_P = 0, WT_U = 128, WT_O = 256, WT_COLS = 512;   // U and O are double buffered (64 columns each)
+constexpr uint32_t WT_P = 0, WT_U = 128, WT_O = 256, WT_P16 = 384, WT_COLS = 512;   // U and O are double buffered (64 columns each); P16: the masked scores as packed 16-bit pairs
 
 // mbarrier indices
 enum { B_FULL = 0, B_SFREE = 3, B_PREPPED = 6, B_PFULL = 9, B_PREADY = 10, B_STREADY = 11, B_UFULL = 12, B_OFULL = 14, B_OFREE = 16,
@@ -190,9 +190,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     it.nch = min(W_SEG_CHUNKS, (p.L - it.seg * W_SEG + CHUNK - 1) / CHUNK);
                 }
             };
-            // A ticket is drawn two items before its loads are issued.  One item before, when its value has long arrived,
-            // it is decoded and its tiles are asked into L2, so the loads that fill the 3-stage ring later find them there
-            // (the ring alone does not cover DRAM latency).
+            // A ticket is drawn two items before its loads are issued and decoded one item before, when its value has long
+            // arrived.  (Asking the next item's tiles into L2 at that point, with bulk prefetches, made the kernel 5 % slower:
+            // the TMA unit and the memory system are loaded enough that the extra requests cost more than the latency they hide.)
             Item lcur, lnext;
             lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = lcur.b = lcur.h = 0; lnext = lcur;
             int tk = (int)atomicAdd(wp.ticket, 1u);
@@ -209,14 +209,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     l_ci = 0;
                     decode(tk, lnext);                         // the item after this one
                     tk = (int)atomicAdd(wp.ticket, 1u);        // and the ticket of the one after that: consumed an item later
-#pragma unroll 1
-                    for (int c = 0; c < lnext.nch; ++c) {
-                        const int t0 = lnext.seg * W_SEG + c * CHUNK;
-                        tma_prefetch_4d(&maps.k, 0, t0, lnext.h, lnext.b);
-                        tma_prefetch_4d(lnext.dir ? &maps.gb : &maps.gf, 0, t0, lnext.h, lnext.b);
-                        tma_prefetch_4d(&maps.q, 0, t0, lnext.h, lnext.b);
-                        tma_prefetch_4d(&maps.v, 0, t0, lnext.h, lnext.b);
-                    }
                     if (l_items > 0) break;                    // a real item is in lcur (an empty one ends the stream below)
                 }
                 const uint32_t s = lm % 3;
@@ -246,8 +238,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (m_ci == mcur.nch) { read_item(m_items, mcur); ++m_items; m_ci = 0; }
                 if (mcur.nch == 0) break;
                 // descriptor low words (16-byte units): +2 = 32 bytes along K inside a 128-byte row, +128 = 16 rows
-                const uint32_t q_lo = make_desc(st + WS_Q), k_lo = make_desc(st + WS_K), v_lo = make_desc(st + WS_V), p0_lo = make_desc(st + WS_G);
-                const uint32_t p1_lo = k_lo;                   // masked scores of key columns 64..127 go over the k tile once U has read it
+                const uint32_t q_lo = make_desc(st + WS_Q), k_lo = make_desc(st + WS_K), v_lo = make_desc(st + WS_V);
                 const uint32_t o_acc = tmem + WT_O + 64u * (m & 1u), u_acc = tmem + WT_U + 64u * (m & 1u);
                 const bool s_zero = state_zero(mcur, m_ci);
                 tc_fence_after();
@@ -280,8 +271,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (!pre_pr) waiter.wait_lite(bar(B_PREADY), m & 1);
                 tc_fence_after();
 #pragma unroll
-                for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) {
-                    if (issuer) tc_mma(o_acc, (k8 < 4 ? p0_lo : p1_lo) + 2 * (k8 & 3), v_lo + 128 * k8, IDESC_OV, !s_zero || k8 > 0);
+                for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) {      // A = masked scores in tensor memory, 8 packed columns per K = 16 step
+                    if (issuer) tc_mma_ts(o_acc, tmem + WT_P16 + 8 * k8, v_lo + 128 * k8, IDESC_OV, !s_zero || k8 > 0);
                 }
                 if (issuer) { tc_commit(bar(B_OFULL + (m & 1))); tc_commit(bar(B_SFREE + s)); }
                 __syncwarp();
@@ -355,8 +346,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // A test of an mbarrier costs a few hundred cycles even when its phase completed long ago (it queues behind the
             // CTA's shared-memory traffic).  The barriers this trip will need are therefore all asked about here, at once and
             // without blocking; the answers arrive during the gate phase, and a wait loop is entered later only on "not yet".
-            uint32_t pre_pfull = 0, pre_ufull = 0, pre_ofull = 0, pre_xfree = 0;
-            if (m >= 1) { pre_pfull = mbar_test_wait(bar(B_PFULL), (m - 1) & 1); pre_ufull = mbar_test_wait(bar(B_UFULL + ((m - 1) & 1)), ((m - 1) >> 1) & 1); }
+            uint32_t pre_pfull = 0, pre_ofull = 0, pre_xfree = 0;
+            if (m >= 1) pre_pfull = mbar_test_wait(bar(B_PFULL), (m - 1) & 1);
             if (m >= 2) pre_ofull = mbar_test_wait(bar(B_OFULL + (m & 1)), ((m - 2) >> 1) & 1);
             if (m >= 3) pre_xfree = mbar_test_wait(bar(B_XFREE), (m - 3) & 1);
             if (!ended) {
@@ -422,18 +413,16 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (*abort_flag) break;
                 tc_fence_after();
                 const int cb = sub, dir = dir_mask_it;
-                uint8_t* stj = smem + (j % 3) * W_STAGE_B;
-                if (cb >= 2) {                                // keys 64..127 go over the k tile: the state update must have read it
-                    if (!pre_ufull) waiter.wait_lite(bar(B_UFULL + (j & 1)), (j >> 1) & 1);
-                    __syncwarp();
-                }
-                uint8_t* prow = stj + (cb < 2 ? WS_G : WS_K) + row * 128;
-                const uint32_t chunk0 = (uint32_t)(cb & 1) * 4;           // first 16-byte chunk of this block in the 128-byte row
+                // The masked scores go back to tensor memory as packed 16-bit pairs (64 columns for 128 keys) and step (c)
+                // reads its A operand from there: no shared-memory tile, no proxy fence, and no wait for the state update to
+                // have read the k tile.  The slot is single: step (c) of iteration j-1 has completed before the scores of
+                // iteration j exist (its commit precedes theirs in the MMA warp's program order).
                 // A 32x32 block of scores is wholly kept, wholly masked, or on the diagonal (warp-uniform test)
                 const bool all_zero = dir ? cb < quad : cb > quad;
+                uint32_t pk[16];
                 if (all_zero) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    for (int i = 0; i < 16; ++i) pk[i] = 0u;
                 } else {
                     float a[32];
                     tc_ld32(tmem + lane_base + WT_P + 32 * cb, a);
@@ -444,15 +433,11 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                         for (int e = 0; e < 32; ++e) a[e] = (keep >> e) & 1u ? a[e] : 0.f;
                     }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint4 w4;
-                        w4.x = Pack2<T>::pack(a[8 * i], a[8 * i + 1]); w4.y = Pack2<T>::pack(a[8 * i + 2], a[8 * i + 3]);
-                        w4.z = Pack2<T>::pack(a[8 * i + 4], a[8 * i + 5]); w4.w = Pack2<T>::pack(a[8 * i + 6], a[8 * i + 7]);
-                        *reinterpret_cast<uint4*>(prow + (((chunk0 + i) ^ (row & 7)) << 4)) = w4;
-                    }
+                    for (int i = 0; i < 16; ++i) pk[i] = Pack2<T>::pack(a[2 * i], a[2 * i + 1]);
                 }
+                tc_st16(tmem + lane_base + WT_P16 + 16 * cb, pk);
+                tc_wait_st();
                 tc_fence_before();
-                fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
             }
