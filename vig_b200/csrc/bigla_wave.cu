@@ -1,6 +1,6 @@
 // Bi-directional gated linear attention, warp-specialised "wavefront" form for large batches (tcgen05 + TMEM).
 //
-// Work item = (sequence b*h, segment of 256 tokens, direction).  Items are drawn from a ticket counter in
+// Work item = (sequence b*h, segment of 256, 512 or 1024 tokens, direction).  Items are drawn from a ticket counter in
 // wavefront order: step w holds segment w of every forward chain and segment nseg-1-w of every backward chain, so
 // the state that enters an item was produced by an item with a smaller ticket, which is running or done.  States
 // pass from segment to segment through a two-slot mailbox per (sequence, direction) in global memory; the two
@@ -37,7 +37,10 @@ namespace {
 using namespace tc;
 
 constexpr int WDK = 64, WDV = 64;
-constexpr int W_SEG_CHUNKS = 2, W_SEG = CHUNK * W_SEG_CHUNKS;
+// A work item is a run of 2, 4 or 8 chunks of one (sequence, direction) chain: a longer run has fewer hand-overs (state
+// mailbox, ring restart: 0.361 -> 0.340 -> 0.337 ms at 64 x 3 sequences of 4096 tokens for 2 -> 4 -> 8 chunks), a shorter one
+// gives the wavefront more items to balance over the SMs.  The host picks the length per call (wave_seg_chunks).
+constexpr int W_SEG_CHUNKS_MIN = 2, W_SEG_CHUNKS_MAX = 8;
 // six warpgroups: workers x4, state, control (MMA warp, load thread, store thread)
 constexpr int W_PREP_WARPS = 16, W_STATE_WARP0 = 16, W_CTRL_WARP0 = 20, W_THREADS = 24 * 32;
 constexpr int W_MMA_WARP = W_CTRL_WARP0, W_LOAD_WARP = W_CTRL_WARP0 + 1, W_STORE_WARP = W_CTRL_WARP0 + 2;
@@ -74,9 +77,9 @@ struct WaveParams {
     BiglaParams p;
     uint32_t* ticket;      // [1]
     uint32_t* chain_cnt;   // [B*H][2]: state warps that have published step w (4 per step)
-    uint32_t* chunk_flag;  // [B*H][nseg*2]: score warps of the first direction that have stored the chunk (4 = done)
+    uint32_t* chunk_flag;  // [B*H][nchunk]: raised by the first direction once its half of the chunk is in place
     float* mailbox;        // [B*H][2 dirs][2 slots][dk*dv + dk]
-    int nseg;
+    int nseg, seg_chunks, nchunk;   // segments (work items) per chain, chunks per segment, chunks per sequence
     float inv_per_step, inv_H;   // reciprocals for the ticket decode (a division costs twenty-odd instructions)
 };
 
@@ -132,7 +135,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         return;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nseg = wp.nseg;
+    const int nseg = wp.nseg, seg_chunks = wp.seg_chunks, seg_tokens = wp.seg_chunks * CHUNK;
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, ndir = (p.dir_mask == 3) ? 2 : 1;
     const int per_step = p.B * p.H * ndir, total = per_step * nseg;
 
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     it.dir = dir_first + (ndir == 2 ? r & 1 : 0);
                     divmod(it.bh, p.H, wp.inv_H, it.b, it.h);
                     it.seg = it.dir ? nseg - 1 - it.w : it.w;
-                    it.nch = min(W_SEG_CHUNKS, (p.L - it.seg * W_SEG + CHUNK - 1) / CHUNK);
+                    it.nch = min(seg_chunks, (p.L - it.seg * seg_tokens + CHUNK - 1) / CHUNK);
                 }
             };
             // A ticket is drawn two items before its loads are issued and decoded one item before, when its value has long
@@ -215,7 +218,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (lm >= 3) waiter.wait_lite(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
                 if (*abort_flag) break;
                 if (lcur.nch == 0) { mbar_arrive_plain(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
-                const int t0 = lcur.seg * W_SEG + chunk_of(lcur, l_ci) * CHUNK;
+                const int t0 = lcur.seg * seg_tokens + chunk_of(lcur, l_ci) * CHUNK;
                 const int b = lcur.b, h = lcur.h;
                 const uint32_t dst = sbase + s * W_STAGE_B, fb = bar(B_FULL + s);
                 mbar_expect_tx(fb, W_STAGE_B);
@@ -290,10 +293,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (ci == cur.nch) { read_item(items, cur); cur.b = ring[items & 7].b; cur.h = ring[items & 7].h; ++items; ci = 0; }
                 if (cur.nch == 0) break;
                 const int c = chunk_of(cur, ci);
-                const int t0 = cur.seg * W_SEG + c * CHUNK, b = cur.b, h = cur.h;
+                const int t0 = cur.seg * seg_tokens + c * CHUNK, b = cur.b, h = cur.h;
                 const int w_other = nseg - 1 - cur.w;
                 const bool first = ndir == 1 || cur.w < w_other || (cur.w == w_other && cur.dir == 0);
-                uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * nseg * W_SEG_CHUNKS + cur.seg * W_SEG_CHUNKS + c;
+                uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * wp.nchunk + cur.seg * seg_chunks + c;   // one flag per chunk of the sequence
                 const uint32_t src = sbase + WO_X;
                 if (first) {
                     tma_store_4d(&maps.o, 0, t0, h, b, src);     // rows past L are clipped by the tensor map
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             } else {
             have = true;
             dir_prev = cur.dir;
-            const int t0 = cur.seg * W_SEG + chunk_of(cur, ci) * CHUNK;
+            const int t0 = cur.seg * seg_tokens + chunk_of(cur, ci) * CHUNK;
             const int n_valid = p.L - t0;                     // rows at or past it are padding: decay 1
             dmask = cur.dir ? 7 : 0;
             // ---- gate phase: transform, running sums over my 4 tokens, group sum published ----
@@ -671,40 +674,60 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     }
 }
 
-size_t wave_counter_bytes(int B, int H, int nseg) {
-    return ((1 + 2 * (size_t)B * H + (size_t)B * H * nseg * W_SEG_CHUNKS) * sizeof(uint32_t) + 255) & ~(size_t)255;
+size_t wave_counter_bytes(int B, int H, int L) {       // ticket, two progress counters per (b, h), one flag per chunk
+    return ((1 + 2 * (size_t)B * H + (size_t)B * H * ((L + CHUNK - 1) / CHUNK)) * sizeof(uint32_t) + 255) & ~(size_t)255;
+}
+
+int wave_sm_count() {
+    static int sm_count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (!sm_count[dev]) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        sm_count[dev] = sms;
+    }
+    return sm_count[dev];
+}
+
+// Chunks per work item: the longest of 8, 4, 2 that still leaves two segments per sequence and about six items per SM
+int wave_seg_chunks(const BiglaParams& p, int sms) {
+    const long long chains = (long long)p.B * p.H * (p.dir_mask == 3 ? 2 : 1);
+    int sc = W_SEG_CHUNKS_MAX;
+    while (sc > W_SEG_CHUNKS_MIN) {
+        const int nseg = (p.L + sc * CHUNK - 1) / (sc * CHUNK);
+        if (nseg >= 2 && chains * nseg >= 6ll * sms) break;
+        sc /= 2;
+    }
+    return sc;
 }
 
 template <typename T, bool RAW, bool CLAMP>
 int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream_t stream) {
-    const int nseg = (p.L + W_SEG - 1) / W_SEG;
+    const int sms = wave_sm_count();
+    if (sms <= 0) return VIG_ERR_DEVICE;
+    const int seg_chunks = wave_seg_chunks(p, sms);
+    const int nseg = (p.L + seg_chunks * CHUNK - 1) / (seg_chunks * CHUNK);
     const int BH = p.B * p.H;
     WaveParams wp;
     wp.p = p;
     wp.nseg = nseg;
+    wp.seg_chunks = seg_chunks;
+    wp.nchunk = (p.L + CHUNK - 1) / CHUNK;
     wp.inv_per_step = 1.0f / (float)(BH * (p.dir_mask == 3 ? 2 : 1));
     wp.inv_H = 1.0f / (float)p.H;
     wp.ticket = reinterpret_cast<uint32_t*>(ws);
     wp.chain_cnt = wp.ticket + 1;
     wp.chunk_flag = wp.chain_cnt + 2 * (size_t)BH;
-    const size_t cb = wave_counter_bytes(p.B, p.H, nseg);
+    const size_t cb = wave_counter_bytes(p.B, p.H, p.L);
     wp.mailbox = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + cb);
     cudaError_t e;
     if ((e = cudaMemsetAsync(ws, 0, cb, stream)) != cudaSuccess) return (int)e;
-    static int sm_count[64] = {};
-    int dev = 0;
-    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64) return VIG_ERR_DEVICE;
     auto kern = bigla_wave_kernel<T, RAW, CLAMP>;
-    if (!sm_count[dev]) {
-        int sms = 0;
-        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-        sm_count[dev] = sms;
-    }
     if ((e = ensure_smem_attr(reinterpret_cast<const void*>(kern), W_SMEM_BYTES)) != cudaSuccess) return (int)e;
     const int ndir = p.dir_mask == 3 ? 2 : 1;
     const long long items = (long long)BH * ndir * nseg;
-    const int grid = (int)(items < sm_count[dev] ? items : sm_count[dev]);
+    const int grid = (int)(items < sms ? items : sms);
     kern<<<grid, W_THREADS, W_SMEM_BYTES, stream>>>(maps, wp);
     return (int)cudaGetLastError();
 }
@@ -715,7 +738,7 @@ bool bigla_wave_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
     if (p.dv != WDV || p.dk != WDK || !p.o || !p.q || p.B * p.H < 1 || p.L < 1) return false;
     if (p.dir_mask < 1 || p.dir_mask > 3) return false;
-    if ((long long)p.B * p.H * 2 * ((p.L + W_SEG - 1) / W_SEG) >= (1ll << 24)) return false;   // tickets are decoded in fp32
+    if ((long long)p.B * p.H * 2 * ((p.L + W_SEG_CHUNKS_MIN * CHUNK - 1) / (W_SEG_CHUNKS_MIN * CHUNK)) >= (1ll << 24)) return false;   // tickets are decoded in fp32
     if (!tc::tma_ok(p.q, p.sq, p.B, p.H) || !tc::tma_ok(p.k, p.sk, p.B, p.H) || !tc::tma_ok(p.v, p.sv, p.B, p.H)) return false;
     if ((p.dir_mask & 1) && (!p.gf || !tc::tma_ok(p.gf, p.sgf, p.B, p.H))) return false;
     if ((p.dir_mask & 2) && (!p.gb || !tc::tma_ok(p.gb, p.sgb, p.B, p.H))) return false;
@@ -727,22 +750,14 @@ bool bigla_wave_supported(const BiglaParams& p) {
 // wavefront form beats the segment-parallel forms (0.46 against 0.58 ms at 64 x 3 sequences of 4096 tokens); with
 // fewer chains its CTAs idle, and a single segment has nothing to hand on.
 bool bigla_wave_preferred(const BiglaParams& p) {
-    static int sm_count[64] = {};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    if (!sm_count[dev]) {
-        int sms = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
-        sm_count[dev] = sms;
-    }
+    const int sms = wave_sm_count();
     const int ndir = p.dir_mask == 3 ? 2 : 1;
-    return p.L > W_SEG && (long long)p.B * p.H * ndir >= sm_count[dev];
+    return sms > 0 && p.L > W_SEG_CHUNKS_MIN * CHUNK && (long long)p.B * p.H * ndir >= sms;
 }
 
 // Counters (ticket, chain progress, chunk flags) followed by the state mailboxes.
 size_t bigla_wave_workspace(int B, int H, int L, int dk, int dv) {
-    const int nseg = (L + W_SEG - 1) / W_SEG;
-    return wave_counter_bytes(B, H, nseg) + (size_t)B * H * 2 * 2 * ((size_t)dk * dv + dk) * sizeof(float);
+    return wave_counter_bytes(B, H, L) + (size_t)B * H * 2 * 2 * ((size_t)dk * dv + dk) * sizeof(float);
 }
 
 int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
