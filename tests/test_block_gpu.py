@@ -294,3 +294,26 @@ def test_dwconv3x3_band_with_halo_rows(dtype):
         bottom = x[:, r1 * w:(r1 + 1) * w].contiguous() if r1 < h else None
         y = vig_b200.dwconv3x3(band, taps, None, (r1 - r0, w), True, top=top, bottom=bottom)
         assert torch.equal(y, whole[:, r0 * w:r1 * w])
+
+
+def test_model_forward_captures_into_a_cuda_graph_after_eager_forwards():
+    """The model's forward can be captured into a CUDA graph at any point: eager forwards leave an asynchronous read of
+    the status word pending, and the forward must not query it while the stream is capturing.  The replay gives the eager
+    result bit for bit."""
+    import vig_b200
+    shape = _shape("vig_t_dk64")
+    model = vig_b200.ViG.from_shape(shape)
+    model.load_state_dict(oracle.make_state_dict(shape, seed=0))
+    model = model.to("cuda", torch.bfloat16).eval()
+    x = oracle.make_images(2, 320, seed=3).to("cuda", torch.bfloat16)
+    with torch.no_grad():
+        for _ in range(3):
+            eager = model(x)                                   # leaves a snapshot of the status word in flight
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = model(x)
+        captured.zero_()
+        graph.replay()
+    torch.cuda.synchronize()
+    vig_b200.check_status()
+    assert torch.equal(captured, eager)

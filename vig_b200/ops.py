@@ -56,7 +56,10 @@ class StatusWord:
             self._event.record()
 
     def poll(self):
-        """Look at the last snapshot if its copy has finished; raises like ``check``."""
+        """Look at the last snapshot if its copy has finished; raises like ``check``.  A no-op while the stream is being
+        captured into a CUDA graph (an event query is not permitted there and would invalidate the capture)."""
+        if torch.cuda.is_current_stream_capturing():
+            return
         if self._event is not None and self._event.query():
             self._event = None
             value = int(self._host[0])
