@@ -380,16 +380,19 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     const float2 a = Pack2<T>::unpack(raw[u].x), b2 = Pack2<T>::unpack(raw[u].y);
                     float4 t = make_float4(a.x, a.y, b2.x, b2.y);
                     if (RAW) {                                // log2(1 + 2^(-x log2 e)) = -log2 sigmoid(x)
-                        t.x = lg2(1.f + ex2(t.x * -LOG2E)); t.y = lg2(1.f + ex2(t.y * -LOG2E));
-                        t.z = lg2(1.f + ex2(t.z * -LOG2E)); t.w = lg2(1.f + ex2(t.w * -LOG2E));
+                        const F2 nl = f2_make(-LOG2E, -LOG2E), one = f2_make(1.f, 1.f);
+                        const F2 y01 = f2_mul(f2_make(t.x, t.y), nl), y23 = f2_mul(f2_make(t.z, t.w), nl);
+                        const F2 e01 = f2_add(one, f2_make(ex2(f2_lo(y01)), ex2(f2_hi(y01)))), e23 = f2_add(one, f2_make(ex2(f2_lo(y23)), ex2(f2_hi(y23))));
+                        t.x = lg2(f2_lo(e01)); t.y = lg2(f2_hi(e01)); t.z = lg2(f2_lo(e23)); t.w = lg2(f2_hi(e23));
                     }
                     const float cu = grp * 8 + ((half * 4 + u) ^ dmask) < n_valid ? coef : 0.f;   // padding rows: gate 0
                     if (CLAMP) {
                         run.x += fmaxf(t.x * cu, clamp_lo); run.y += fmaxf(t.y * cu, clamp_lo);
                         run.z += fmaxf(t.z * cu, clamp_lo); run.w += fmaxf(t.w * cu, clamp_lo);
                     } else {
-                        run.x = fmaf(t.x, cu, run.x); run.y = fmaf(t.y, cu, run.y);
-                        run.z = fmaf(t.z, cu, run.z); run.w = fmaf(t.w, cu, run.w);
+                        const F2 c2 = f2_make(cu, cu);
+                        const F2 r01 = f2_fma(f2_make(t.x, t.y), c2, f2_make(run.x, run.y)), r23 = f2_fma(f2_make(t.z, t.w), c2, f2_make(run.z, run.w));
+                        run = make_float4(f2_lo(r01), f2_hi(r01), f2_lo(r23), f2_hi(r23));
                     }
                     gl[u] = run;
                 }
@@ -459,12 +462,16 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 __syncwarp();
                 if (lane == 0) mbar_arrive_plain(bar(B_OFREE + (j & 1)));   // the slot is read: hand it back
                 uint8_t* orow = smem + WO_X + row * 128;
+                const F2 os2 = f2_make(o_sign, o_sign);
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
-                    uint4 w4;
-                    w4.x = Pack2<T>::pack(o_sign * a[8 * i], o_sign * a[8 * i + 1]); w4.y = Pack2<T>::pack(o_sign * a[8 * i + 2], o_sign * a[8 * i + 3]);
-                    w4.z = Pack2<T>::pack(o_sign * a[8 * i + 4], o_sign * a[8 * i + 5]); w4.w = Pack2<T>::pack(o_sign * a[8 * i + 6], o_sign * a[8 * i + 7]);
-                    *reinterpret_cast<uint4*>(orow + (((uint32_t)(2 * sub + i) ^ (row & 7)) << 4)) = w4;
+                    uint32_t w[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const F2 v = f2_mul(os2, f2_make(a[8 * i + 2 * k], a[8 * i + 2 * k + 1]));
+                        w[k] = Pack2<T>::pack(f2_lo(v), f2_hi(v));
+                    }
+                    *reinterpret_cast<uint4*>(orow + (((uint32_t)(2 * sub + i) ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 fence_proxy_async();
                 __syncwarp();
@@ -494,15 +501,20 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const float4* part = reinterpret_cast<const float4*>(smem + WO_PART) + (m & 1) * (W_PREP_WARPS * 16) + c4l;
                 const int flip = cur.dir ? W_PREP_WARPS - 1 : 0;          // scan position go <-> group go ^ flip
                 const int mygo = grp ^ flip;
-                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f), bef = sum;
+                // two-wide fp32 arithmetic (the workers are bound by instruction issue)
+                F2 s01 = f2_make(0.f, 0.f), s23 = s01, b01 = s01, b23 = s01;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int go = half * 8 + i;
                     const float4 t = part[(go ^ flip) * 16];
-                    sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+                    const F2 t01 = f2_make(t.x, t.y), t23 = f2_make(t.z, t.w);
+                    s01 = f2_add(s01, t01); s23 = f2_add(s23, t23);
                     const float k = go < mygo ? 1.f : 0.f;
-                    bef.x = fmaf(k, t.x, bef.x); bef.y = fmaf(k, t.y, bef.y); bef.z = fmaf(k, t.z, bef.z); bef.w = fmaf(k, t.w, bef.w);
+                    const F2 kk = f2_make(k, k);
+                    b01 = f2_fma(kk, t01, b01); b23 = f2_fma(kk, t23, b23);
                 }
+                const float4 sum = make_float4(f2_lo(s01), f2_hi(s01), f2_lo(s23), f2_hi(s23));
+                const float4 bef = make_float4(f2_lo(b01), f2_hi(b01), f2_lo(b23), f2_hi(b23));
                 float4 osum, obef;
                 osum.x = __shfl_xor_sync(0xffffffffu, sum.x, 16); osum.y = __shfl_xor_sync(0xffffffffu, sum.y, 16);
                 osum.z = __shfl_xor_sync(0xffffffffu, sum.z, 16); osum.w = __shfl_xor_sync(0xffffffffu, sum.w, 16);

@@ -24,13 +24,6 @@ constexpr int DW_SEG = 8;                      // columns per thread
 constexpr int DW_ROWS = 2;                     // image rows per tile
 constexpr int DW_STAGES = 2;
 
-// a pair of fp32 values in one 64-bit register, and the packed arithmetic on it
-typedef unsigned long long F2;
-__device__ __forceinline__ F2 f2_make(float lo, float hi) { F2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
-__device__ __forceinline__ float f2_lo(F2 v) { float lo, hi; asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); return lo; }
-__device__ __forceinline__ float f2_hi(F2 v) { float lo, hi; asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); return hi; }
-__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) { F2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
-__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) { F2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 // sigmoid of both lanes; 16-bit outputs take the one-MUFU form of sigmoid_t: 0.5 tanh(x / 2) + 0.5
 template <typename T> __device__ __forceinline__ F2 f2_sigmoid(F2 x) {
     const F2 half = f2_make(0.5f, 0.5f);

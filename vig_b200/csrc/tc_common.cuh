@@ -185,6 +185,17 @@ struct Waiter {
     }
 };
 
+// A pair of fp32 values in one 64-bit register and the two-wide fp32 arithmetic of sm_100 on it (add / mul / fma .f32x2:
+// one instruction for two values, each lane the IEEE operation, so results equal the scalar form's).  For loops that are
+// bound by instruction issue.
+typedef unsigned long long F2;
+__device__ __forceinline__ F2 f2_make(float lo, float hi) { F2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ float f2_lo(F2 v) { float lo, hi; asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); return lo; }
+__device__ __forceinline__ float f2_hi(F2 v) { float lo, hi; asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); return hi; }
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) { F2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) { F2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) { F2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
 // single-instruction exp2 / log2 (flush-to-zero forms: no denormal fix-up code around the MUFU)
