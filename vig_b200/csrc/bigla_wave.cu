@@ -79,7 +79,8 @@ struct WaveParams {
     uint32_t* chain_cnt;   // [B*H][2]: state warps that have published step w (4 per step)
     uint32_t* chunk_flag;  // [B*H][nchunk]: raised by the first direction once its half of the chunk is in place
     float* mailbox;        // [B*H][2 dirs][2 slots][dk*dv + dk]
-    int nseg, seg_chunks, nchunk;   // segments (work items) per chain, chunks per segment, chunks per sequence
+    int nseg, seg_chunks, nchunk;   // steps (work items) per chain, chunks per long step, chunks per sequence
+    int n_long, short_chunks;       // the first n_long steps have seg_chunks chunks, the others short_chunks (the last one what is left)
     float inv_per_step, inv_H;   // reciprocals for the ticket decode (a division costs twenty-odd instructions)
 };
 
@@ -91,7 +92,7 @@ __device__ __forceinline__ void divmod(int n, int d, float inv_d, int& q, int& r
     if (r < 0) { --q; r += d; }
 }
 
-struct Item { int bh, seg, dir, nch, w, b, h, pad; };
+struct Item { int bh, c0, dir, nch, w, b, h, pad; };   // c0: first chunk of the item (index into the sequence), nch: its chunks, w: its step
 
 
 // Bounded wait on a global counter (one lane polls).
@@ -135,7 +136,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         return;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nseg = wp.nseg, seg_chunks = wp.seg_chunks, seg_tokens = wp.seg_chunks * CHUNK;
+    const int nseg = wp.nseg, seg_chunks = wp.seg_chunks;
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, ndir = (p.dir_mask == 3) ? 2 : 1;
     const int per_step = p.B * p.H * ndir, total = per_step * nseg;
 
@@ -166,7 +167,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
 
     auto read_item = [&](int idx, Item& it) {
         const volatile Item* r = ring + (idx & 7);
-        it.bh = r->bh; it.seg = r->seg; it.dir = r->dir; it.nch = r->nch; it.w = r->w;
+        it.bh = r->bh; it.c0 = r->c0; it.dir = r->dir; it.nch = r->nch; it.w = r->w;
     };
     // chunk (inside its segment) of sweep position ci, and its first token
     auto chunk_of = [&](const Item& it, int ci) { return it.dir ? it.nch - 1 - ci : ci; };
@@ -189,15 +190,20 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     it.bh = ndir == 2 ? r >> 1 : r;
                     it.dir = dir_first + (ndir == 2 ? r & 1 : 0);
                     divmod(it.bh, p.H, wp.inv_H, it.b, it.h);
-                    it.seg = it.dir ? nseg - 1 - it.w : it.w;
-                    it.nch = min(seg_chunks, (p.L - it.seg * seg_tokens + CHUNK - 1) / CHUNK);
+                    // steps of seg_chunks chunks, then shorter ones at the end of the scan (the last items of the
+                    // schedule decide how evenly the SMs finish); a backward chain counts its chunks from the far end
+                    int sc0, len;
+                    if (it.w < wp.n_long) { sc0 = it.w * seg_chunks; len = seg_chunks; }
+                    else { sc0 = wp.n_long * seg_chunks + (it.w - wp.n_long) * wp.short_chunks; len = min(wp.short_chunks, wp.nchunk - sc0); }
+                    it.nch = len;
+                    it.c0 = it.dir ? wp.nchunk - sc0 - len : sc0;
                 }
             };
             // A ticket is drawn two items before its loads are issued and decoded one item before, when its value has long
             // arrived.  (Asking the next item's tiles into L2 at that point, with bulk prefetches, made the kernel 5 % slower:
             // the TMA unit and the memory system are loaded enough that the extra requests cost more than the latency they hide.)
             Item lcur, lnext;
-            lcur.nch = 0; lcur.bh = lcur.seg = lcur.dir = lcur.w = lcur.b = lcur.h = 0; lnext = lcur;
+            lcur.nch = 0; lcur.bh = lcur.c0 = lcur.dir = lcur.w = lcur.b = lcur.h = 0; lnext = lcur;
             int tk = (int)atomicAdd(wp.ticket, 1u);
             int l_items = -1, l_ci = 0;                        // the first pass through the item block only fills lnext
             #pragma unroll 1
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     lcur = lnext;
                     if (l_items >= 0) {
                         volatile Item* r = ring + (l_items & 7);
-                        r->bh = lcur.bh; r->seg = lcur.seg; r->dir = lcur.dir; r->nch = lcur.nch; r->w = lcur.w; r->b = lcur.b; r->h = lcur.h;
+                        r->bh = lcur.bh; r->c0 = lcur.c0; r->dir = lcur.dir; r->nch = lcur.nch; r->w = lcur.w; r->b = lcur.b; r->h = lcur.h;
                     }
                     ++l_items;
                     l_ci = 0;
@@ -218,7 +224,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (lm >= 3) waiter.wait_lite(bar(B_SFREE + s), ((lm / 3) - 1) & 1);
                 if (*abort_flag) break;
                 if (lcur.nch == 0) { mbar_arrive_plain(bar(B_FULL + s)); break; }   // end marker: wakes the prep warps
-                const int t0 = lcur.seg * seg_tokens + chunk_of(lcur, l_ci) * CHUNK;
+                const int t0 = (lcur.c0 + chunk_of(lcur, l_ci)) * CHUNK;
                 const int b = lcur.b, h = lcur.h;
                 const uint32_t dst = sbase + s * W_STAGE_B, fb = bar(B_FULL + s);
                 mbar_expect_tx(fb, W_STAGE_B);
@@ -230,7 +236,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         } else if (warp == W_MMA_WARP) {
             // ---- MMA warp: all 32 lanes walk the loop (uniform control flow keeps the descriptor arithmetic in the
             // uniform datapath, off the issuing lane's critical path); lane 0 issues ----
-            Item mcur; mcur.nch = 0; mcur.bh = mcur.seg = mcur.dir = mcur.w = 0;
+            Item mcur; mcur.nch = 0; mcur.bh = mcur.c0 = mcur.dir = mcur.w = 0;
             int m_items = 0, m_ci = 0;
             const uint32_t st_lo = make_desc(sbase + WO_ST);
             #pragma unroll 1
@@ -284,7 +290,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             // ---- store thread: the output tile of iteration j, staged by the score warps, goes out as one TMA store (first direction to reach the chunk) or one TMA reduction (second).
             // The global-memory latencies of the hand-over between the directions (write complete -> flag; flag -> add)
             // are spent here, by a thread that has nothing else to do.
-            Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
+            Item cur; cur.nch = 0; cur.bh = cur.c0 = cur.dir = cur.w = 0;
             int items = 0, ci = 0;
             #pragma unroll 1
             for (uint32_t j = 0;; ++j, ++ci) {
@@ -293,10 +299,14 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (ci == cur.nch) { read_item(items, cur); cur.b = ring[items & 7].b; cur.h = ring[items & 7].h; ++items; ci = 0; }
                 if (cur.nch == 0) break;
                 const int c = chunk_of(cur, ci);
-                const int t0 = cur.seg * seg_tokens + c * CHUNK, b = cur.b, h = cur.h;
-                const int w_other = nseg - 1 - cur.w;
+                const int t0 = (cur.c0 + c) * CHUNK, b = cur.b, h = cur.h;
+                // the step at which the other direction reaches this chunk: it counts chunks from the other end of the
+                // sequence, through the same schedule of long steps followed by short ones
+                const int sc_other = cur.dir ? cur.c0 + c : wp.nchunk - 1 - (cur.c0 + c);
+                const int n_long_chunks = wp.n_long * seg_chunks;
+                const int w_other = sc_other < n_long_chunks ? sc_other / seg_chunks : wp.n_long + (sc_other - n_long_chunks) / wp.short_chunks;
                 const bool first = ndir == 1 || cur.w < w_other || (cur.w == w_other && cur.dir == 0);
-                uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * wp.nchunk + cur.seg * seg_chunks + c;   // one flag per chunk of the sequence
+                uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * wp.nchunk + cur.c0 + c;   // one flag per chunk of the sequence
                 const uint32_t src = sbase + WO_X;
                 if (first) {
                     tma_store_4d(&maps.o, 0, t0, h, b, src);     // rows past L are clipped by the tensor map
@@ -334,7 +344,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         const int row = 32 * quad + lane;
         const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
         const float o_sign = p.qscale;                        // scale * out_scale, applied to the finished accumulators
-        Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
+        Item cur; cur.nch = 0; cur.bh = cur.c0 = cur.dir = cur.w = 0;
         int items = 0, ci = -1, dir_prev = 0;
         bool ended = false;
         uint32_t end_m = 0;                                   // first iteration that does not exist
@@ -365,7 +375,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             } else {
             have = true;
             dir_prev = cur.dir;
-            const int t0 = cur.seg * seg_tokens + chunk_of(cur, ci) * CHUNK;
+            const int t0 = (cur.c0 + chunk_of(cur, ci)) * CHUNK;
             const int n_valid = p.L - t0;                     // rows at or past it are padding: decay 1
             dmask = cur.dir ? 7 : 0;
             // ---- gate phase: transform, running sums over my 4 tokens, group sum published ----
@@ -573,7 +583,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
         constexpr int NE = WDK * WDV, SLOT = NE + WDK;
         float S[32];
         float gacc = 0.f;                                     // summed log2-gates of my channel along the chain so far
-        Item cur; cur.nch = 0; cur.bh = cur.seg = cur.dir = cur.w = 0;
+        Item cur; cur.nch = 0; cur.bh = cur.c0 = cur.dir = cur.w = 0;
         int items = 0, ci = 0;
         bool s_zero = true;
         #pragma unroll 1
@@ -719,13 +729,20 @@ int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream
     const int sms = wave_sm_count();
     if (sms <= 0) return VIG_ERR_DEVICE;
     const int seg_chunks = wave_seg_chunks(p, sms);
-    const int nseg = (p.L + seg_chunks * CHUNK - 1) / (seg_chunks * CHUNK);
+    const int nchunk = (p.L + CHUNK - 1) / CHUNK;
+    // the schedule ends with half-length steps: the tail of the ticket queue then has items half as long, and the SMs finish
+    // within half an item of each other
+    const int short_chunks = seg_chunks >= 4 ? seg_chunks / 2 : seg_chunks;
+    const int n_long = short_chunks == seg_chunks ? 0 : (nchunk / seg_chunks > 1 ? nchunk / seg_chunks - 1 : 0);
+    const int nseg = n_long + (nchunk - n_long * seg_chunks + short_chunks - 1) / short_chunks;
     const int BH = p.B * p.H;
     WaveParams wp;
     wp.p = p;
     wp.nseg = nseg;
     wp.seg_chunks = seg_chunks;
-    wp.nchunk = (p.L + CHUNK - 1) / CHUNK;
+    wp.nchunk = nchunk;
+    wp.n_long = n_long;
+    wp.short_chunks = short_chunks;
     wp.inv_per_step = 1.0f / (float)(BH * (p.dir_mask == 3 ? 2 : 1));
     wp.inv_H = 1.0f / (float)p.H;
     wp.ticket = reinterpret_cast<uint32_t*>(ws);
