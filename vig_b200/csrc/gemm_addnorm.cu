@@ -154,7 +154,9 @@ __global__ void __launch_bounds__(AN_THREADS, 1) linear_add_rmsnorm_kernel(const
             const uint32_t use = nbuf == 2 ? (acc_it >> 1) : acc_it;
             const uint32_t eb = acc_it & 1u;
             uint8_t* ebuf = smem + off_e + eb * E_BYTES;
-            if (lane == 0) { waiter.wait(bar_res_full + 8 * eb, (acc_it >> 1) & 1u); waiter.wait(bar_acc_full + 8 * buf, use & 1u); }
+            // both waits by the whole warp: a wait by one lane with the others parked at a warp barrier resumes microseconds late
+            waiter.wait(bar_res_full + 8 * eb, (acc_it >> 1) & 1u);
+            waiter.wait(bar_acc_full + 8 * buf, use & 1u);
             __syncwarp();                         // (no early exit on an abort: the four warps meet at named barriers below,
             tc_fence_after();                     //  and after an abort every wait returns at once)
             const uint32_t acc = tmem + lane_base + buf * (uint32_t)NT;
