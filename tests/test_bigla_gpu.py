@@ -175,10 +175,14 @@ def test_single_launch_form_matches_oracle_and_three_launch_form(shape):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape,dir_mask,init", [((2, 3, 1300), 3, True), ((1, 1, 128), 3, False), ((3, 2, 196), 3, False),
-                                                 ((2, 2, 1024), 1, True), ((2, 2, 700), 2, False), ((30, 3, 1000), 3, False)])
+                                                 ((2, 2, 1024), 1, True), ((2, 2, 700), 2, False), ((30, 3, 1000), 3, False),
+                                                 # enough chains for long work items: 8 chunks with a tail of 4, 4, 1 (ragged last chunk),
+                                                 # one direction only, 4 chunks with a tail of 2, 2
+                                                 ((50, 3, 2100), 3, True), ((100, 3, 2100), 1, True), ((100, 3, 1500), 2, False)])
 def test_wavefront_form_matches_oracle(shape, dir_mask, init, dtype):
     """The warp-specialised wavefront form (impl 5): every state passes from segment to segment through the
-    mailbox, the two directions of a chunk meet in the output tensor (store, then vector reduction)."""
+    mailbox, the two directions of a chunk meet in the output tensor (store, then reduction); small batches run
+    work items of 2 chunks, large ones 4 or 8 with shorter items at the end of every chain."""
     import vig_b200
     from vig_b200 import _lib
     B, H, L = shape
