@@ -305,7 +305,12 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const int sc_other = cur.dir ? cur.c0 + c : wp.nchunk - 1 - (cur.c0 + c);
                 const int n_long_chunks = wp.n_long * seg_chunks;
                 const int w_other = sc_other < n_long_chunks ? sc_other / seg_chunks : wp.n_long + (sc_other - n_long_chunks) / wp.short_chunks;
-                const bool first = ndir == 1 || cur.w < w_other || (cur.w == w_other && cur.dir == 0);
+                // Which direction stores and which adds is fixed by the schedule: the one whose step is earlier; within the
+                // same step the one that reaches the chunk earlier inside its item (so neither item starts by waiting for the
+                // other: short sequences are one step); on a full tie the forward one.
+                const int pos_mine = ci, pos_other = (sc_other < n_long_chunks ? sc_other % seg_chunks : (sc_other - n_long_chunks) % wp.short_chunks);
+                const bool first = ndir == 1 || cur.w < w_other ||
+                                   (cur.w == w_other && (pos_mine < pos_other || (pos_mine == pos_other && cur.dir == 0)));
                 uint32_t* flag = wp.chunk_flag + (size_t)cur.bh * wp.nchunk + cur.c0 + c;   // one flag per chunk of the sequence
                 const uint32_t src = sbase + WO_X;
                 if (first) {
