@@ -2,26 +2,25 @@
 // One GEMM produces [q | k | v | output-gate logits | gate logits] per token (qkv_proj, g_proj and the folded gk_proj of
 // GatedLinearAttention, classification/models/vig.py:283-290 and 431-439), N = 1152 at width 192.
 //
-// The product is write-bound (x: 100 MB in, z: 604 MB out at the headline shape), so the kernel is organised around
-// keeping the store path busy.  A persistent CTA owns tiles of 256 rows of x (two 128-row subtiles, whole K, resident in
-// shared memory); the weights stream through a ring of three 24 KB boxes of 192 rows x 64 k, and ONE M128 N192 MMA per
-// k step fills an accumulator [128 x 192]; two accumulators double-buffer in tensor memory: unit u+1 (column block,
-// subtile) is multiplied while unit u is read out.  Both subtiles use the same weight boxes.  Sixteen epilogue warps
-// share a unit: a warp owns the 32 rows of its TMEM lane quarter and 48 columns, adds the bias in fp32, rounds, packs
-// its [32 rows x 48 columns] into a 3 KB box of shared memory and lane 0 sends the box with ONE TMA store per unit (a
-// thread owns a row, so direct stores would touch 32 lines per request; a round through the box -- wait for the
-// previous store's read, shared-memory stores, proxy fence, store -- costs ~1300 cycles whatever its size, so a warp
-// makes one round per unit: with 256-column blocks and 2 KB boxes, two rounds per unit, the kernel took 193 us against
-// the vendor GEMM's 165).  Columns past N in the last column block are zero rows of W (TMA fill) on the way in and are
-// clipped by the tensor map on the way out.
-// Measured at M = 262144, K = 192, N = 1152: 199 us against 160 us for the vendor GEMM (a 2-CTA kernel), so the block
-// keeps the vendor GEMM by default.  Switching phases off: without the stores 175, without the MMAs 172, without the
-// box round 163 -- the MMA stream alone takes 163 us, ~310 cycles per MMA against ~110 in isolation: the ring holds exactly
-// one column block's three boxes (x tile 96 KB + ring 72 KB + boxes 48 KB fill shared memory), so every block starts by
-// waiting for reloads that could only be requested when the second subtile had used the boxes.  A fourth ring slot does
-// not fit; CTA pairs sharing the weight boxes (`cta_group::2`) are what the vendor kernel uses to get out of this.
+// The product is write-bound (x: 100 MB in, z: 604 MB out at the headline shape).  Weight-stationary organisation: a
+// persistent CTA owns ONE block of 192 output columns for the whole launch -- its [192 x K] slice of W (72 KB at K = 192)
+// is loaded once and stays in shared memory -- and walks tiles of 128 rows of x, which stream through a two-stage ring
+// (48 KB each) and are multiplied with one M128 N192 MMA per k step into one of two accumulators in tensor memory (tile
+// t+1 is multiplied while tile t is read out).  The CTAs that hold the different column blocks of the same row tile have
+// consecutive block indices and run in step, so a tile of x comes from DRAM once and from L2 for the others.  No weight
+// box is ever reloaded: an earlier organisation that kept 256 rows of x resident and streamed the weights through a
+// ring of one column block's boxes waited for reloads at every block and took 199 us.
+// Twelve epilogue warps share a tile: a warp owns the 32 rows of its TMEM lane quarter and 64 columns, adds the bias in
+// fp32, rounds, packs its [32 rows x 64 columns] into a swizzled 4 KB box of shared memory and lane 0 sends the box with ONE
+// TMA store (a thread owns a row, so direct stores touch 32 lines per request: 32-byte stores straight from registers
+// were tried and took 207 us).  Columns past N in the last column block are zero rows of W (TMA fill) on the way in and
+// are clipped by the tensor map on the way out.
+// Measured at M = 262144, K = 192, N = 1152: 171 us against 160-165 us for the vendor GEMM (a 2-CTA kernel), so the block
+// keeps the vendor GEMM by default.  Switching phases off (timing only): without the stores 132, without the MMAs 150,
+// without the box round 118 -- the output path is the bound (604 MB in 171 us = 3.5 TB/s of writes); boxes with 96-byte
+// rows (sixteen warps of 48 columns) and with 128-byte rows take the same time, so it is not the TMA unit's row rate.
 // Roles: warp 0 TMA producer, warp 1 MMA issuer (the whole warp walks the loops, only the issue is predicated on lane
-// 0; barriers are asked about ahead of use with the non-blocking test), warps 2..17 epilogue.  Every wait is bounded.
+// 0; barriers are asked about ahead of use with the non-blocking test), warps 2..13 epilogue.  Every wait is bounded.
 #include "tc_common.cuh"
 
 namespace vig {
@@ -32,45 +31,44 @@ using namespace tc;
 constexpr int GB_BK = 64;                          // k elements per box row (128 bytes)
 constexpr int GB_A_BOX = 128 * GB_BK * 2;          // one [128 rows x 64 k] box of x
 constexpr int GB_COLS = 192;                       // output columns per block (1152 = 6 x 192 at width 192)
-constexpr int GB_W_BOX = GB_COLS * GB_BK * 2;      // one k box of weights, 24 KB
-constexpr int GB_RING = 3;
-constexpr int GB_EPI_WARPS = 16;
+constexpr int GB_W_BOX = GB_COLS * GB_BK * 2;      // one k box of the CTA's weight slice, 24 KB
+constexpr int GB_XSTAGES = 2;                      // x tiles in flight
+constexpr int GB_EPI_WARPS = 12;                   // 4 TMEM lane quarters x 3 groups of 64 columns
 constexpr int GB_THREADS = 64 + 32 * GB_EPI_WARPS;
-constexpr int GB_WCOLS = GB_COLS / 4;              // columns per epilogue warp
-constexpr int GB_OUT_BOX = 32 * GB_WCOLS * 2;      // one epilogue warp's [32 rows x 48 columns] box
+constexpr int GB_WCOLS = 64;                       // columns per epilogue warp: 128-byte rows in its output box
+constexpr int GB_OUT_BOX = 32 * GB_WCOLS * 2;      // one epilogue warp's [32 rows x 64 columns] box, 128-byte swizzle
 
 template <typename T> struct GbPk;
 template <> struct GbPk<__nv_bfloat16> { static constexpr uint32_t FMT = 1;
-    __device__ static uint32_t pack(float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
-    __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); } };
+    __device__ static uint32_t pack(float a, float b) { __nv_bfloat162 t = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); } };
 template <> struct GbPk<__half> { static constexpr uint32_t FMT = 0;
-    __device__ static uint32_t pack(float a, float b) { __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); }
-    __device__ static float to_f(__half v) { return __half2float(v); } };
+    __device__ static uint32_t pack(float a, float b) { __half2 t = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&t); } };
 
 struct GbMaps { CUtensorMap x, w, o; };
 
+// grid = row_groups * nblocks CTAs; CTA i holds column block i % nblocks and walks row tiles i / nblocks, + row_groups, ...
 template <typename T>
 __global__ void __launch_bounds__(GB_THREADS, 1) linear_bias_kernel(const __grid_constant__ GbMaps maps, const T* __restrict__ bias,
-                                                                    int M, int N, int KB, int32_t* status) {
+                                                                    int M, int N, int KB, int nblocks, int row_groups, int32_t* status) {
     extern __shared__ uint8_t gb_smem_raw[];
     uint8_t* smem = gb_smem_raw + ((1024u - (smem_u32(gb_smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t off_b = 2u * KB * GB_A_BOX;
-    const uint32_t off_out = off_b + GB_RING * GB_W_BOX;
+    const uint32_t off_x = (uint32_t)KB * GB_W_BOX;                         // after the weight slice
+    const uint32_t x_stage = (uint32_t)KB * GB_A_BOX;
+    const uint32_t off_out = off_x + GB_XSTAGES * x_stage;
     const uint32_t off_bar = off_out + GB_EPI_WARPS * GB_OUT_BOX;
-    // barriers: x boxes per (subtile, k box): full / empty; weight ring slots: full / empty; accumulator halves: full / empty
-    const uint32_t bar_a_full = sbase + off_bar, bar_a_empty = bar_a_full + 8 * 6;
-    const uint32_t bar_b_full = bar_a_empty + 8 * 6, bar_b_empty = bar_b_full + 8 * GB_RING;
-    const uint32_t bar_acc_full = bar_b_empty + 8 * GB_RING, bar_acc_empty = bar_acc_full + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (12 + 2 * GB_RING + 4));
+    // barriers: weight slice full; x stages full / empty; accumulators full / empty
+    const uint32_t bar_w = sbase + off_bar;
+    const uint32_t bar_x_full = bar_w + 8, bar_x_empty = bar_x_full + 8 * GB_XSTAGES;
+    const uint32_t bar_acc_full = bar_x_empty + 8 * GB_XSTAGES, bar_acc_empty = bar_acc_full + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (1 + 2 * GB_XSTAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const Waiter waiter{abort_flag, status};
 
-    const int nblocks = (N + GB_COLS - 1) / GB_COLS;
     if (tid == 0) {
-        for (int i = 0; i < 6; ++i) { mbar_init(bar_a_full + 8 * i, 1); mbar_init(bar_a_empty + 8 * i, 1); }
-        for (int i = 0; i < GB_RING; ++i) { mbar_init(bar_b_full + 8 * i, 1); mbar_init(bar_b_empty + 8 * i, 1); }
+        mbar_init(bar_w, 1);
+        for (int i = 0; i < GB_XSTAGES; ++i) { mbar_init(bar_x_full + 8 * i, 1); mbar_init(bar_x_empty + 8 * i, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, GB_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -84,131 +82,98 @@ __global__ void __launch_bounds__(GB_THREADS, 1) linear_bias_kernel(const __grid
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    const int ntiles = (M + 255) / 256;
+    const int ntiles = (M + 127) / 128;
+    const int nb = (int)blockIdx.x % nblocks, rg = (int)blockIdx.x / nblocks;
     constexpr uint32_t IDESC = make_idesc(GbPk<T>::FMT, 0, 0, 128, GB_COLS);
 
     if (warp == 0) {
         if (lane == 0) {                          // ---- TMA producer -------------------------------------------
-            uint32_t a_phase = 0, slot = 0, b_phase = 0;
-            auto load_x = [&](int tile, int s, int kb) {
-                const uint32_t i = (uint32_t)(s * 3 + kb);
-                waiter.wait(bar_a_empty + 8 * i, a_phase ^ 1u);         // the previous tile's MMAs have read this box
-                mbar_expect_tx(bar_a_full + 8 * i, GB_A_BOX);
-                tma_load_2d(sbase + (s * KB + kb) * GB_A_BOX, &maps.x, kb * GB_BK, tile * 256 + s * 128, bar_a_full + 8 * i);
-            };
-            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-                for (int nb = 0; nb < nblocks; ++nb) {
-                    for (int kb = 0; kb < KB; ++kb) {
-                        if (nb == 0) load_x(tile, 0, kb);               // first subtile's box just ahead of the weights that meet it
-                        waiter.wait(bar_b_empty + 8 * slot, b_phase ^ 1u);
-                        if (*abort_flag) { tile = ntiles; nb = nblocks; break; }
-                        mbar_expect_tx(bar_b_full + 8 * slot, GB_W_BOX);
-                        tma_load_2d(sbase + off_b + slot * GB_W_BOX, &maps.w, kb * GB_BK, nb * GB_COLS, bar_b_full + 8 * slot);   // rows past N arrive as zeros
-                        if (++slot == GB_RING) { slot = 0; b_phase ^= 1u; }
-                    }
-                    if (nb == 0)
-                        for (int kb = 0; kb < KB; ++kb) load_x(tile, 1, kb);
-                }
-                a_phase ^= 1u;
+            mbar_expect_tx(bar_w, (uint32_t)KB * GB_W_BOX);
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(sbase + kb * GB_W_BOX, &maps.w, kb * GB_BK, nb * GB_COLS, bar_w);      // rows past N arrive as zeros
+            uint32_t st = 0, phase = 0;
+            for (int tile = rg; tile < ntiles; tile += row_groups) {
+                waiter.wait(bar_x_empty + 8 * st, phase ^ 1u);            // the MMAs of the tile two back have read this stage
+                if (*abort_flag) break;
+                mbar_expect_tx(bar_x_full + 8 * st, x_stage);
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(sbase + off_x + st * x_stage + kb * GB_A_BOX, &maps.x, kb * GB_BK, tile * 128, bar_x_full + 8 * st);
+                if (++st == GB_XSTAGES) { st = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {                       // ---- MMA issuer ---------------------------------------------
         const bool issuer = lane == 0;
-        uint32_t a_phase = 0, slot0 = 0, b_phase0 = 0, unit = 0;
-        const uint32_t a_lo0 = make_desc(sbase), b_lo0 = make_desc(sbase + off_b);
-        uint32_t pre_acc = 0;
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            for (int nb = 0; nb < nblocks; ++nb) {
-                for (int s = 0; s < 2; ++s, ++unit) {
-                    const uint32_t buf = unit & 1u;
-                    if (!pre_acc) waiter.wait_lite(bar_acc_empty + 8 * buf, ((unit >> 1) & 1u) ^ 1u);   // the epilogue has read this half out
-                    pre_acc = 0;
-                    if (*abort_flag) break;
-                    const uint32_t d = tmem + buf * 256u;
-                    uint32_t slot = slot0, b_phase = b_phase0;
-                    // the first subtile meets freshly loaded weight boxes: ask about all of them at once (one round trip)
-                    uint32_t have[3] = {1u, 1u, 1u};
-                    if (s == 0) {
-                        uint32_t sl = slot0, ph = b_phase0;
-                        for (int kb = 0; kb < KB; ++kb) {
-                            have[kb] = mbar_test_wait(bar_b_full + 8 * sl, ph);
-                            if (++sl == GB_RING) { sl = 0; ph ^= 1u; }
-                        }
-                    }
-                    for (int kb = 0; kb < KB; ++kb) {
-                        if (nb == 0) waiter.wait_lite(bar_a_full + 8 * (uint32_t)(s * 3 + kb), a_phase);
-                        if (!have[kb]) waiter.wait_lite(bar_b_full + 8 * slot, b_phase);
-                        tc_fence_after();
-                        // asked before the unit's last MMAs, answered while they are issued: is the other half free?
-                        if (kb == KB - 1) pre_acc = mbar_test_wait(bar_acc_empty + 8 * (buf ^ 1u), (((unit + 1) >> 1) & 1u) ^ 1u);
-                        const uint32_t a_lo = a_lo0 + (uint32_t)(s * KB + kb) * (GB_A_BOX >> 4);
-                        const uint32_t b_lo = b_lo0 + slot * (GB_W_BOX >> 4);
-#pragma unroll
-                        for (uint32_t k4 = 0; k4 < 4; ++k4) { if (issuer) tc_mma(d, a_lo + 2 * k4, b_lo + 2 * k4, IDESC, (kb | k4) > 0 ? 1u : 0u); }
-                        if (s == 1) { if (issuer) tc_commit(bar_b_empty + 8 * slot); }                 // both subtiles have used the box
-                        if (nb == nblocks - 1) { if (issuer) tc_commit(bar_a_empty + 8 * (uint32_t)(s * 3 + kb)); }   // the tile's last use of the x box
-                        if (++slot == GB_RING) { slot = 0; b_phase ^= 1u; }
-                    }
-                    if (issuer) tc_commit(bar_acc_full + 8 * buf);
-                    if (s == 1) { slot0 = slot; b_phase0 = b_phase; }
-                }
-                if (*abort_flag) break;
-            }
+        const uint32_t w_lo0 = make_desc(sbase), x_lo0 = make_desc(sbase + off_x);
+        waiter.wait_lite(bar_w, 0);
+        uint32_t st = 0, phase = 0, it = 0;
+        uint32_t pre_x = 0, pre_acc = 0;
+        for (int tile = rg; tile < ntiles; tile += row_groups, ++it) {
+            const uint32_t buf = it & 1u;
+            if (!pre_acc) waiter.wait_lite(bar_acc_empty + 8 * buf, ((it >> 1) & 1u) ^ 1u);   // the epilogue has read this accumulator out
+            if (!pre_x) waiter.wait_lite(bar_x_full + 8 * st, phase);
             if (*abort_flag) break;
-            a_phase ^= 1u;
+            tc_fence_after();
+            // asked before this tile's MMAs, answered while they are issued: the next tile's stage and accumulator
+            const uint32_t st_next = st + 1 == GB_XSTAGES ? 0u : st + 1, ph_next = st + 1 == GB_XSTAGES ? phase ^ 1u : phase;
+            pre_x = mbar_test_wait(bar_x_full + 8 * st_next, ph_next);
+            pre_acc = mbar_test_wait(bar_acc_empty + 8 * (buf ^ 1u), (((it + 1) >> 1) & 1u) ^ 1u);
+            const uint32_t d = tmem + buf * 256u;
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint32_t a_lo = x_lo0 + (st * x_stage >> 4) + (uint32_t)kb * (GB_A_BOX >> 4);
+                const uint32_t b_lo = w_lo0 + (uint32_t)kb * (GB_W_BOX >> 4);
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < 4; ++k4) { if (issuer) tc_mma(d, a_lo + 2 * k4, b_lo + 2 * k4, IDESC, (kb | k4) > 0 ? 1u : 0u); }
+            }
+            if (issuer) { tc_commit(bar_x_empty + 8 * st); tc_commit(bar_acc_full + 8 * buf); }
+            st = st_next; phase = ph_next;
         }
     } else {                                      // ---- epilogue: + bias -> out ----------------------------------
-        const int ew = warp - 2;                  // 0..15
-        const int cq = ew >> 2;                   // which 48 of the block's 192 columns
+        const int ew = warp - 2;                  // 0..11
+        const int cq = ew >> 2;                   // which 64 of the block's 192 columns
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;   // a warp reads the TMEM lanes of its quarter
-        uint8_t* my_row = smem + off_out + ew * GB_OUT_BOX + lane * (GB_WCOLS * 2);
+        uint8_t* my_row = smem + off_out + ew * GB_OUT_BOX + lane * 128;
+        const uint32_t sw = (uint32_t)(lane & 7);
         const uint32_t box_u32 = sbase + off_out + ew * GB_OUT_BOX;
-        uint32_t unit = 0;
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            for (int nb = 0; nb < nblocks; ++nb) {
-                for (int s = 0; s < 2; ++s, ++unit) {
-                    const uint32_t buf = unit & 1u;
-                    waiter.wait_lite(bar_acc_full + 8 * buf, (unit >> 1) & 1u);   // by the whole warp
-                    if (*abort_flag) break;
-                    tc_fence_after();
-                    const uint32_t acc = tmem + lane_base + buf * 256u + (uint32_t)(GB_WCOLS * cq);
-                    const int col0 = nb * GB_COLS + GB_WCOLS * cq;
-                    const int row0 = tile * 256 + s * 128 + 32 * (warp & 3);
-                    float v[GB_WCOLS];
-                    tc_ld32(acc, v);
-                    tc_ld16(acc + 32, v + 32);
-                    tc_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
-                    uint32_t pk[GB_WCOLS / 2];
-#pragma unroll
-                    for (int j = 0; j < GB_WCOLS / 8; ++j) {              // 8 columns at a time; N is a multiple of 8
-                        uint4 t = make_uint4(0u, 0u, 0u, 0u);
-                        // bias values: the same addresses for all lanes (one broadcast transaction per load, L1-resident)
-                        if (bias && col0 + 8 * j < N) t = __ldg(reinterpret_cast<const uint4*>(bias + col0 + 8 * j));
-                        const uint32_t w4[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const float2 bb = Pack2<T>::unpack(w4[i]);
-                            pk[4 * j + i] = GbPk<T>::pack(v[8 * j + 2 * i] + bb.x, v[8 * j + 2 * i + 1] + bb.y);
-                        }
-                    }
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the box
-                    __syncwarp();
-#pragma unroll
-                    for (int j = 0; j < GB_WCOLS / 8; ++j)
-                        *reinterpret_cast<uint4*>(my_row + 16 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0 && row0 < M && col0 < N) {
-                        tma_store_2d(&maps.o, col0, row0, box_u32);      // rows past M / columns past N are clipped by the tensor map
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                }
-                if (*abort_flag) break;
-            }
+        const int col0 = nb * GB_COLS + GB_WCOLS * cq;
+        uint32_t it = 0;
+        for (int tile = rg; tile < ntiles; tile += row_groups, ++it) {
+            const uint32_t buf = it & 1u;
+            waiter.wait_lite(bar_acc_full + 8 * buf, (it >> 1) & 1u);   // by the whole warp
             if (*abort_flag) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + lane_base + buf * 256u + (uint32_t)(GB_WCOLS * cq);
+            const int row0 = tile * 128 + 32 * (warp & 3);
+            float v[GB_WCOLS];
+            tc_ld32(acc, v);
+            tc_ld32(acc + 32, v + 32);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
+            uint32_t pk[GB_WCOLS / 2];
+#pragma unroll
+            for (int j = 0; j < GB_WCOLS / 8; ++j) {                  // 8 columns at a time; N is a multiple of 8
+                uint4 t = make_uint4(0u, 0u, 0u, 0u);
+                // bias values: the same addresses for all lanes (one broadcast transaction per load, L1-resident)
+                if (bias && col0 + 8 * j < N) t = __ldg(reinterpret_cast<const uint4*>(bias + col0 + 8 * j));
+                const uint32_t w4[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 bb = Pack2<T>::unpack(w4[i]);
+                    pk[4 * j + i] = GbPk<T>::pack(v[8 * j + 2 * i] + bb.x, v[8 * j + 2 * i + 1] + bb.y);
+                }
+            }
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the box
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < GB_WCOLS / 8; ++j)
+                *reinterpret_cast<uint4*>(my_row + (((uint32_t)j ^ sw) << 4)) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && row0 < M && col0 < N) {
+                tma_store_2d(&maps.o, col0, row0, box_u32);      // rows past M / columns past N are clipped by the tensor map
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA exits
     }
@@ -262,17 +227,21 @@ extern "C" int vig_linear_bias_fwd(const void* x, int64_t ldx, const void* w, co
     cudaError_t e;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-    const int smem = 2 * KB * GB_A_BOX + GB_RING * GB_W_BOX + GB_EPI_WARPS * GB_OUT_BOX + 8 * (12 + 2 * GB_RING + 4) + 16 + 1024;
-    const int ntiles = (int)((M + 255) / 256);
-    const int grid = ntiles < sms ? ntiles : sms;
+    const int smem = KB * GB_W_BOX + GB_XSTAGES * KB * GB_A_BOX + GB_EPI_WARPS * GB_OUT_BOX + 8 * (1 + 2 * GB_XSTAGES + 4) + 16 + 1024;
+    const int nblocks = (N + GB_COLS - 1) / GB_COLS;
+    if (nblocks > sms) return VIG_ERR_SHAPE;
+    const int ntiles = (int)((M + 127) / 128);
+    int row_groups = sms / nblocks;                            // CTAs per column block
+    if (row_groups > ntiles) row_groups = ntiles;
+    const int grid = row_groups * nblocks;
     if (dtype == VIG_DTYPE_BF16) {
         auto kfn = linear_bias_kernel<__nv_bfloat16>;
         if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
-        kfn<<<grid, GB_THREADS, smem, (cudaStream_t)stream>>>(maps, (const __nv_bfloat16*)bias, (int)M, N, KB, status_dev);
+        kfn<<<grid, GB_THREADS, smem, (cudaStream_t)stream>>>(maps, (const __nv_bfloat16*)bias, (int)M, N, KB, nblocks, row_groups, status_dev);
     } else {
         auto kfn = linear_bias_kernel<__half>;
         if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
-        kfn<<<grid, GB_THREADS, smem, (cudaStream_t)stream>>>(maps, (const __half*)bias, (int)M, N, KB, status_dev);
+        kfn<<<grid, GB_THREADS, smem, (cudaStream_t)stream>>>(maps, (const __half*)bias, (int)M, N, KB, nblocks, row_groups, status_dev);
     }
     return (int)cudaGetLastError();
 }

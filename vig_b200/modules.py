@@ -102,8 +102,8 @@ class GatedLinearAttention(nn.Module):
         n_main = 2 * kd + 2 * vd
         # one GEMM for [q | k | v | output-gate logits | low-rank gate features] (folded: | raw gate logits)
         w_z, b_z = (merged[0], merged[1]) if fold else (w_in, b_in)
-        # the vendor GEMM by default: the library's own kernel for this product (``ops.linear_bias``) measures 199 us against
-        # 160 us at the benchmark's shape; ``own_in_proj_gemm`` switches it in where it is supported
+        # the vendor GEMM by default: the library's own kernel for this product (``ops.linear_bias``) measures 171 us against
+        # 160-165 us at the benchmark's shape; ``own_in_proj_gemm`` switches it in where it is supported
         use_own = self.own_in_proj_gemm and ops.linear_bias_supported(xs, w_z)
         z = ops.linear_bias(xs, w_z, b_z) if use_own else F.linear(xs, w_z, b_z)
         heads = lambda t, d: t.unflatten(-1, (H, d)).permute(0, 2, 1, 3)           # [B,H,L,d] views, no copy
