@@ -266,42 +266,46 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_kernel(const __gr
 
 
 // ---------------------------------------------------------------------------------------------------
-// Wide form, for K <= 192 and I % 128 == 0 (the shipped MLP shapes at widths up to 192).
+// Weight-stationary form, for K <= 192 and I % 128 == 0 (the shipped MLP shapes at widths up to 192) and many rows.
 //
 // A 128x128x16 MMA takes ~80-130 cycles here where a 128x256x16 one takes ~130: at N = 128 the tensor pipe runs at half its
-// rate.  This form multiplies one 128-row subtile by 128 gate rows and their 128 y rows at once (N = 256), so a unit of
-// work is (feature block of 128, subtile) and its accumulator [128 x 256] takes half of tensor memory; the two halves
-// double-buffer (unit u+1 is multiplied while unit u is read out).  Both subtiles of a tile use the same weight boxes,
-// which therefore stay in their ring slots for two units: a 96 KB ring of three 32 KB boxes holds exactly one block's
-// boxes at K = 192, so the reload of a box for the next block (from L2) starts when the second subtile has used it and
-// is only partly hidden -- still far cheaper than running the tensor pipe at half rate.  x boxes are released per
-// subtile, so the first subtile's part of the next tile streams in while the second subtile of the last block is multiplied.
+// rate.  This form multiplies a 128-row tile of x by 128 gate rows and their 128 y rows at once (N = 256).  A persistent CTA
+// owns ONE block of 128 features for the whole launch: its [256 x K] slice of W (96 KB at K = 192) is loaded once and stays
+// in shared memory, the x tiles stream through a two-stage ring (48 KB each), the accumulator [128 x 256] takes half of
+// tensor memory and the two halves double-buffer (tile t+1 is multiplied while tile t is read out).  The CTAs that hold
+// the feature blocks of the same row tile have consecutive block indices and run in step, so a tile of x comes from DRAM
+// once and from L2 for the others.  (An earlier N = 256 form kept 256 rows of x resident and streamed the weights through
+// a ring that held exactly one block's boxes: every block began by waiting for reloads, 134 us; before that the N = 128
+// form, 155-165 us.)
 constexpr int WB_FEAT = 128;                         // features per block
-constexpr int WB_BOX_BYTES = 2 * WB_FEAT * BK * 2;   // one k box of weights: 128 gate rows + 128 y rows, 32 KB
-constexpr int WB_RING = 3;
+constexpr int WB_BOX_BYTES = 2 * WB_FEAT * BK * 2;   // one k box of the CTA's weight slice: 128 gate rows + 128 y rows, 32 KB
+constexpr int WB_XSTAGES = 2;
 
 struct GsWideMaps { CUtensorMap x, w, o; };
 
+// grid = row_groups * nblocks CTAs; CTA i holds feature block i % nblocks and walks row tiles i / nblocks, + row_groups, ...
 template <typename T>
-__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const __grid_constant__ GsWideMaps maps, int M, int I, int KB, int32_t* status) {
+__global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const __grid_constant__ GsWideMaps maps, int M, int I, int KB, int nblocks,
+                                                                           int row_groups, int32_t* status) {
     extern __shared__ uint8_t gs_smem_raw[];
     uint8_t* smem = gs_smem_raw + ((1024u - (smem_u32(gs_smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t off_b = 2u * KB * A_BOX_BYTES;
-    const uint32_t off_out = off_b + WB_RING * WB_BOX_BYTES;
+    const uint32_t off_x = (uint32_t)KB * WB_BOX_BYTES;                     // after the weight slice
+    const uint32_t x_stage = (uint32_t)KB * A_BOX_BYTES;
+    const uint32_t off_out = off_x + WB_XSTAGES * x_stage;
     const uint32_t off_bar = off_out + OUT_STAGE_BYTES;
-    // barriers: x boxes per (subtile, k box): full / empty; weight ring slots: full / empty; accumulator halves: full / empty
-    const uint32_t bar_a_full = sbase + off_bar, bar_a_empty = bar_a_full + 8 * 6;
-    const uint32_t bar_b_full = bar_a_empty + 8 * 6, bar_b_empty = bar_b_full + 8 * WB_RING;
-    const uint32_t bar_acc_full = bar_b_empty + 8 * WB_RING, bar_acc_empty = bar_acc_full + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (12 + 2 * WB_RING + 4));
+    // barriers: weight slice full; x stages full / empty; accumulator halves full / empty
+    const uint32_t bar_w = sbase + off_bar;
+    const uint32_t bar_x_full = bar_w + 8, bar_x_empty = bar_x_full + 8 * WB_XSTAGES;
+    const uint32_t bar_acc_full = bar_x_empty + 8 * WB_XSTAGES, bar_acc_empty = bar_acc_full + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + off_bar + 8 * (1 + 2 * WB_XSTAGES + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const Waiter waiter{abort_flag, status};
 
     if (tid == 0) {
-        for (int i = 0; i < 6; ++i) { mbar_init(bar_a_full + 8 * i, 1); mbar_init(bar_a_empty + 8 * i, 1); }
-        for (int i = 0; i < WB_RING; ++i) { mbar_init(bar_b_full + 8 * i, 1); mbar_init(bar_b_empty + 8 * i, 1); }
+        mbar_init(bar_w, 1);
+        for (int i = 0; i < WB_XSTAGES; ++i) { mbar_init(bar_x_full + 8 * i, 1); mbar_init(bar_x_empty + 8 * i, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, GS_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -315,81 +319,52 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    const int ntiles = (M + 255) / 256;
-    const int nblocks = I / WB_FEAT;
+    const int ntiles = (M + 127) / 128;
+    const int nb = (int)blockIdx.x % nblocks, rg = (int)blockIdx.x / nblocks;
     constexpr uint32_t IDESC = make_idesc(Pk<T>::FMT, 0, 0, 128, 256);
 
     if (warp == 0) {
         if (lane == 0) {                          // ---- TMA producer -------------------------------------------
-            uint32_t a_phase = 0, slot = 0, b_phase = 0;
-            auto load_x = [&](int tile, int s, int kb) {
-                const uint32_t i = (uint32_t)(s * 3 + kb);
-                waiter.wait(bar_a_empty + 8 * i, a_phase ^ 1u);         // the previous tile's MMAs have read this box
-                mbar_expect_tx(bar_a_full + 8 * i, A_BOX_BYTES);
-                tma_load_2d(sbase + (s * KB + kb) * A_BOX_BYTES, &maps.x, kb * BK, tile * 256 + s * 128, bar_a_full + 8 * i);
-            };
-            for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-                for (int nb = 0; nb < nblocks; ++nb) {
-                    for (int kb = 0; kb < KB; ++kb) {
-                        if (nb == 0) load_x(tile, 0, kb);               // first subtile's box just ahead of the weights that meet it
-                        waiter.wait(bar_b_empty + 8 * slot, b_phase ^ 1u);
-                        if (*abort_flag) { tile = ntiles; nb = nblocks; break; }
-                        mbar_expect_tx(bar_b_full + 8 * slot, WB_BOX_BYTES);
-                        const uint32_t dst = sbase + off_b + slot * WB_BOX_BYTES;
-                        tma_load_2d(dst, &maps.w, kb * BK, nb * WB_FEAT, bar_b_full + 8 * slot);                       // gate rows
-                        tma_load_2d(dst + WB_FEAT * BK * 2, &maps.w, kb * BK, I + nb * WB_FEAT, bar_b_full + 8 * slot); // matching y rows
-                        if (++slot == WB_RING) { slot = 0; b_phase ^= 1u; }
-                    }
-                    if (nb == 0)
-                        for (int kb = 0; kb < KB; ++kb) load_x(tile, 1, kb);
-                }
-                a_phase ^= 1u;
+            mbar_expect_tx(bar_w, (uint32_t)KB * WB_BOX_BYTES);
+            for (int kb = 0; kb < KB; ++kb) {
+                tma_load_2d(sbase + kb * WB_BOX_BYTES, &maps.w, kb * BK, nb * WB_FEAT, bar_w);                          // gate rows
+                tma_load_2d(sbase + kb * WB_BOX_BYTES + WB_FEAT * BK * 2, &maps.w, kb * BK, I + nb * WB_FEAT, bar_w);   // matching y rows
+            }
+            uint32_t st = 0, phase = 0;
+            for (int tile = rg; tile < ntiles; tile += row_groups) {
+                waiter.wait(bar_x_empty + 8 * st, phase ^ 1u);            // the MMAs of the tile two back have read this stage
+                if (*abort_flag) break;
+                mbar_expect_tx(bar_x_full + 8 * st, x_stage);
+                for (int kb = 0; kb < KB; ++kb)
+                    tma_load_2d(sbase + off_x + st * x_stage + kb * A_BOX_BYTES, &maps.x, kb * BK, tile * 128, bar_x_full + 8 * st);
+                if (++st == WB_XSTAGES) { st = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {                       // ---- MMA issuer ---------------------------------------------
         const bool issuer = lane == 0;
-        uint32_t a_phase = 0, slot0 = 0, b_phase0 = 0, unit = 0;
-        const uint32_t a_lo0 = make_desc(sbase), b_lo0 = make_desc(sbase + off_b);
-        uint32_t pre_acc = 0;
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            for (int nb = 0; nb < nblocks; ++nb) {
-                for (int s = 0; s < 2; ++s, ++unit) {
-                    const uint32_t buf = unit & 1u;
-                    if (!pre_acc) waiter.wait_lite(bar_acc_empty + 8 * buf, ((unit >> 1) & 1u) ^ 1u);   // the epilogue has read this half out
-                    pre_acc = 0;
-                    if (*abort_flag) break;
-                    const uint32_t d = tmem + buf * 256u;
-                    uint32_t slot = slot0, b_phase = b_phase0;
-                    // the first subtile meets freshly loaded weight boxes: ask about all of them at once (one round trip)
-                    uint32_t have[3] = {1u, 1u, 1u};
-                    if (s == 0) {
-                        uint32_t sl = slot0, ph = b_phase0;
-                        for (int kb = 0; kb < KB; ++kb) {
-                            have[kb] = mbar_test_wait(bar_b_full + 8 * sl, ph);
-                            if (++sl == WB_RING) { sl = 0; ph ^= 1u; }
-                        }
-                    }
-                    for (int kb = 0; kb < KB; ++kb) {
-                        if (nb == 0) waiter.wait_lite(bar_a_full + 8 * (uint32_t)(s * 3 + kb), a_phase);
-                        if (!have[kb]) waiter.wait_lite(bar_b_full + 8 * slot, b_phase);
-                        tc_fence_after();
-                        // asked before the unit's last MMAs, answered while they are issued: is the other half free?
-                        if (kb == KB - 1) pre_acc = mbar_test_wait(bar_acc_empty + 8 * (buf ^ 1u), (((unit + 1) >> 1) & 1u) ^ 1u);
-                        const uint32_t a_lo = a_lo0 + (uint32_t)(s * KB + kb) * (A_BOX_BYTES >> 4);
-                        const uint32_t b_lo = b_lo0 + slot * (WB_BOX_BYTES >> 4);
-#pragma unroll
-                        for (uint32_t k4 = 0; k4 < 4; ++k4) { if (issuer) tc_mma(d, a_lo + 2 * k4, b_lo + 2 * k4, IDESC, (kb | k4) > 0 ? 1u : 0u); }
-                        if (s == 1) { if (issuer) tc_commit(bar_b_empty + 8 * slot); }                 // both subtiles have used the box
-                        if (nb == nblocks - 1) { if (issuer) tc_commit(bar_a_empty + 8 * (uint32_t)(s * 3 + kb)); }   // the tile's last use of the x box
-                        if (++slot == WB_RING) { slot = 0; b_phase ^= 1u; }
-                    }
-                    if (issuer) tc_commit(bar_acc_full + 8 * buf);
-                    if (s == 1) { slot0 = slot; b_phase0 = b_phase; }
-                }
-                if (*abort_flag) break;
-            }
+        const uint32_t w_lo0 = make_desc(sbase), x_lo0 = make_desc(sbase + off_x);
+        waiter.wait_lite(bar_w, 0);
+        uint32_t st = 0, phase = 0, it = 0;
+        uint32_t pre_x = 0, pre_acc = 0;
+        for (int tile = rg; tile < ntiles; tile += row_groups, ++it) {
+            const uint32_t buf = it & 1u;
+            if (!pre_acc) waiter.wait_lite(bar_acc_empty + 8 * buf, ((it >> 1) & 1u) ^ 1u);   // the epilogue has read this half out
+            if (!pre_x) waiter.wait_lite(bar_x_full + 8 * st, phase);
             if (*abort_flag) break;
-            a_phase ^= 1u;
+            tc_fence_after();
+            // asked before this tile's MMAs, answered while they are issued: the next tile's stage and accumulator half
+            const uint32_t st_next = st + 1 == WB_XSTAGES ? 0u : st + 1, ph_next = st + 1 == WB_XSTAGES ? phase ^ 1u : phase;
+            pre_x = mbar_test_wait(bar_x_full + 8 * st_next, ph_next);
+            pre_acc = mbar_test_wait(bar_acc_empty + 8 * (buf ^ 1u), (((it + 1) >> 1) & 1u) ^ 1u);
+            const uint32_t d = tmem + buf * 256u;
+            for (int kb = 0; kb < KB; ++kb) {
+                const uint32_t a_lo = x_lo0 + (st * x_stage >> 4) + (uint32_t)kb * (A_BOX_BYTES >> 4);
+                const uint32_t b_lo = w_lo0 + (uint32_t)kb * (WB_BOX_BYTES >> 4);
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < 4; ++k4) { if (issuer) tc_mma(d, a_lo + 2 * k4, b_lo + 2 * k4, IDESC, (kb | k4) > 0 ? 1u : 0u); }
+            }
+            if (issuer) { tc_commit(bar_x_empty + 8 * st); tc_commit(bar_acc_full + 8 * buf); }
+            st = st_next; phase = ph_next;
         }
     } else {                                      // ---- epilogue: silu(gate) * y -> out ----------------------------
         const int ew = warp - 2;                  // 0..15
@@ -397,30 +372,24 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;   // a warp reads the TMEM lanes of its quarter
         uint8_t* my_row = smem + off_out + ew * OUT_BOX_BYTES + lane * 64;
         const uint32_t box_u32 = sbase + off_out + ew * OUT_BOX_BYTES;
-        uint32_t unit = 0;
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-            for (int nb = 0; nb < nblocks; ++nb) {
-                for (int s = 0; s < 2; ++s, ++unit) {
-                    const uint32_t buf = unit & 1u;
-                    waiter.wait_lite(bar_acc_full + 8 * buf, (unit >> 1) & 1u);   // by the whole warp
-                    if (*abort_flag) break;
-                    tc_fence_after();
-                    const uint32_t acc = tmem + lane_base + buf * 256u + 32u * fq;
-                    float g[32], y[32];
-                    tc_ld32(acc, g);
-                    tc_ld32(acc + WB_FEAT, y);
-                    tc_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
-                    uint32_t pk[16];
-                    swiglu_pack<T>(g, y, pk);
-                    const int row0 = tile * 256 + s * 128 + 32 * (warp & 3);
-                    send_box(my_row, box_u32, pk, &maps.o, nb * WB_FEAT + 32 * fq, row0, row0 < M, lane);
-                }
-                if (*abort_flag) break;
-            }
+        uint32_t it = 0;
+        for (int tile = rg; tile < ntiles; tile += row_groups, ++it) {
+            const uint32_t buf = it & 1u;
+            waiter.wait_lite(bar_acc_full + 8 * buf, (it >> 1) & 1u);   // by the whole warp
             if (*abort_flag) break;
+            tc_fence_after();
+            const uint32_t acc = tmem + lane_base + buf * 256u + 32u * fq;
+            float g[32], y[32];
+            tc_ld32(acc, g);
+            tc_ld32(acc + WB_FEAT, y);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
+            uint32_t pk[16];
+            swiglu_pack<T>(g, y, pk);
+            const int row0 = tile * 128 + 32 * (warp & 3);
+            send_box(my_row, box_u32, pk, &maps.o, nb * WB_FEAT + 32 * fq, row0, row0 < M, lane);
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA exits
     }
@@ -473,22 +442,25 @@ extern "C" int vig_linear_swiglu_fwd(const void* x, int64_t ldx, const void* w, 
     cudaError_t e;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-    if (KB <= 3 && I % WB_FEAT == 0 && M >= 256 * (int64_t)sms) {
-        // wide form: N = 256 MMAs on tiles of 256 rows, when there are enough of them to fill the machine
+    if (KB <= 3 && I % WB_FEAT == 0 && M >= 256 * (int64_t)sms && I / WB_FEAT <= sms) {
+        // weight-stationary form: N = 256 MMAs, a CTA per feature block and row group, when there are enough rows to fill the machine
         GsWideMaps maps;
         if (!tc::make_map_2d(&maps.x, x, M, K, ldx, 128, dtype) || !tc::make_map_2d(&maps.w, w, 2 * (int64_t)I, K, K, WB_FEAT, dtype) ||
             !make_out_map(&maps.o, out, M, I, ldo, dtype)) return VIG_ERR_DEVICE;
-        const int smem = 2 * KB * A_BOX_BYTES + WB_RING * WB_BOX_BYTES + OUT_STAGE_BYTES + 8 * (12 + 2 * WB_RING + 4) + 16 + 1024;
-        const int ntiles = (int)((M + 255) / 256);
-        const int grid = ntiles < sms ? ntiles : sms;
+        const int smem = KB * WB_BOX_BYTES + WB_XSTAGES * KB * A_BOX_BYTES + OUT_STAGE_BYTES + 8 * (1 + 2 * WB_XSTAGES + 4) + 16 + 1024;
+        const int nblocks = I / WB_FEAT;
+        const int ntiles = (int)((M + 127) / 128);
+        int row_groups = sms / nblocks;                        // CTAs per feature block
+        if (row_groups > ntiles) row_groups = ntiles;
+        const int grid = row_groups * nblocks;
         if (dtype == VIG_DTYPE_BF16) {
             auto kfn = linear_swiglu_wide_kernel<__nv_bfloat16>;
             if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
-            kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, status_dev);
+            kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, nblocks, row_groups, status_dev);
         } else {
             auto kfn = linear_swiglu_wide_kernel<__half>;
             if ((e = tc::ensure_smem_attr(reinterpret_cast<const void*>(kfn), smem)) != cudaSuccess) return (int)e;
-            kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, status_dev);
+            kfn<<<grid, GS_THREADS, smem, (cudaStream_t)stream>>>(maps, (int)M, I, KB, nblocks, row_groups, status_dev);
         }
         return (int)cudaGetLastError();
     }
