@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const
     if (tid == 0) {
         mbar_init(bar_w, 1);
         for (int i = 0; i < WB_XSTAGES; ++i) { mbar_init(bar_x_full + 8 * i, 1); mbar_init(bar_x_empty + 8 * i, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, GS_EPI_WARPS); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full + 8 * b, 1); mbar_init(bar_acc_empty + 8 * b, GS_EPI_WARPS / 2); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -367,29 +367,40 @@ __global__ void __launch_bounds__(GS_THREADS, 1) linear_swiglu_wide_kernel(const
             st = st_next; phase = ph_next;
         }
     } else {                                      // ---- epilogue: silu(gate) * y -> out ----------------------------
+        // Two sets of eight warps take alternate tiles (set = accumulator half), so a warp has two tile periods for its
+        // [32 rows x 64 features]: the epilogue of a tile is a chain of latencies (accumulator ready -> TMEM load -> 32 sigmoids
+        // -> box -> store, ~3 k cycles) longer than the tile's MMAs, and with all sixteen warps on every tile it set the pace.
         const int ew = warp - 2;                  // 0..15
-        const int fq = ew >> 2;                   // which 32 of the block's 128 features
+        const uint32_t set = (uint32_t)ew >> 3;   // tiles of which parity / which accumulator half
+        const int fh = (ew >> 2) & 1;             // which 64 of the block's 128 features (taken as two halves of 32)
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;   // a warp reads the TMEM lanes of its quarter
         uint8_t* my_row = smem + off_out + ew * OUT_BOX_BYTES + lane * 64;
         const uint32_t box_u32 = sbase + off_out + ew * OUT_BOX_BYTES;
-        uint32_t it = 0;
+        const uint32_t acc = tmem + lane_base + set * 256u + 64u * fh;
+        uint32_t it = 0, uses = 0;
         for (int tile = rg; tile < ntiles; tile += row_groups, ++it) {
-            const uint32_t buf = it & 1u;
-            waiter.wait_lite(bar_acc_full + 8 * buf, (it >> 1) & 1u);   // by the whole warp
+            if ((it & 1u) != set) continue;
+            waiter.wait_lite(bar_acc_full + 8 * set, uses & 1u);   // by the whole warp
+            ++uses;
             if (*abort_flag) break;
             tc_fence_after();
-            const uint32_t acc = tmem + lane_base + buf * 256u + 32u * fq;
+            const int row0 = tile * 128 + 32 * (warp & 3);
+            const int col0 = nb * WB_FEAT + 64 * fh;
             float g[32], y[32];
+            uint32_t pk[16];
             tc_ld32(acc, g);
             tc_ld32(acc + WB_FEAT, y);
             tc_wait_ld();
+            swiglu_pack<T>(g, y, pk);
+            tc_ld32(acc + 32, g);
+            tc_ld32(acc + WB_FEAT + 32, y);
+            tc_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * buf);   // the accumulator is in registers: the MMA warp may refill it
-            uint32_t pk[16];
+            if (lane == 0) mbar_arrive_plain(bar_acc_empty + 8 * set);   // the accumulator is in registers: the MMA warp may refill it
+            send_box(my_row, box_u32, pk, &maps.o, col0, row0, row0 < M, lane);
             swiglu_pack<T>(g, y, pk);
-            const int row0 = tile * 128 + 32 * (warp & 3);
-            send_box(my_row, box_u32, pk, &maps.o, nb * WB_FEAT + 32 * fq, row0, row0 < M, lane);
+            send_box(my_row, box_u32, pk, &maps.o, col0 + 32, row0, row0 < M, lane);
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA exits
     }
