@@ -153,15 +153,26 @@ def _halo_local_fn(group, rank, world):
 def vig_forward_sequence_parallel(model, images, group=None):
     """Logits of ``model`` (a ``vig_b200.ViG`` in eval mode) with the token sequence of every image split across
     the ranks of ``group`` by rows of the patch grid.  Every rank passes the same ``images`` and gets the same
-    logits.  The stem is computed redundantly on every rank (about 4 % of the model's work)."""
+    logits.  The stem is split by image rows like the blocks (one patch row of overlap above each rank's rows)."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    tokens, (h, w) = model.patch_embed(images)
+    patch = 2 * model.patch_embed.stride
+    B, _, H_img, W_img = images.shape
+    if H_img % patch or W_img % patch:
+        raise ValueError("image sides must be multiples of the patch size")
+    h, w = H_img // patch, W_img // patch
     if h < world:
         raise ValueError("more ranks than rows in the patch grid")
-    B, _, C = tokens.shape
-    x = tokens + model._pos((h, w))
     r0, r1 = row_range(h, rank, world)
-    x = x.view(B, h, w, C)[:, r0:r1].reshape(B, (r1 - r0) * w, C).contiguous()
+    # The stem is split too: a patch row depends on image rows 16 p - 9 .. 16 p + 15 (conv k9 s8 p1, then conv k3 s2 p1),
+    # so a rank runs the stem on its own image rows plus the patch row above and drops that row of the result; nothing
+    # below its last row is needed.
+    top = 1 if r0 > 0 else 0
+    sub = images[:, :, patch * (r0 - top):patch * r1].contiguous()
+    tokens, (hs, _) = model.patch_embed(sub)
+    C = tokens.shape[-1]
+    tokens = tokens.view(B, hs, w, C)[:, top:]
+    x = tokens + model._pos((h, w)).view(1, h, w, C)[:, r0:r1]
+    x = x.reshape(B, (r1 - r0) * w, C).contiguous()
     hooks = dict(patch_resolution=(r1 - r0, w), local_fn=_halo_local_fn(group, rank, world),
                  scan_fn=lambda q, k, v, gf, gb, **kw: bi_gla_sequence_parallel(q, k, v, gf, gb, group=group, **kw))
     hidden, residual = x, None
