@@ -208,6 +208,29 @@ def test_wavefront_form_matches_oracle(shape, dir_mask, init, dtype):
             assert rel_err(o1.float(), ref) < 2e-2
 
 
+@pytest.mark.parametrize("shape,dir_mask,impl_wave", [((2, 3, 1300), 3, True), ((50, 3, 2100), 3, False), ((100, 3, 1500), 1, False),
+                                                      ((3, 2, 196), 2, True)])
+def test_wavefront_form_states_only(shape, dir_mask, impl_wave):
+    """A call without an output tensor (end states and summed log-gates only: the summary pass of the sequence split) runs
+    the wavefront kernel without its score / output half -- on request, and by default for large batches -- and gives the
+    states of the full call and of the three-launch form."""
+    import vig_b200
+    from vig_b200 import _lib
+    B, H, L = shape
+    dev = _cuda(oracle.make_bigla_inputs(B, H, L, 64, 64, seed=L + 7), torch.bfloat16)
+    kw = dict(output_final_state=True, output_logdecay=True, dir_mask=dir_mask)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _, ex = vig_b200.bi_gla(*dev, want_output=False, status=status, impl=_lib.IMPL_TC_WAVE if impl_wave else _lib.IMPL_AUTO, **kw)
+    assert int(status.item()) == 0
+    _, ex_full = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_WAVE, **kw)
+    _, ex_split = vig_b200.bi_gla(*dev, want_output=False, impl=_lib.IMPL_TC_SPLIT, **kw)
+    assert set(ex) == set(ex_full) == set(ex_split)
+    for name in ex:
+        assert torch.equal(ex[name], ex_full[name]), name               # the same state chain, bit for bit
+        tol = 1e-5 if name.startswith("logdecay") else 1e-2
+        assert rel_err(ex[name], ex_split[name]) < tol, name
+
+
 def test_wavefront_form_is_the_default_for_large_batches():
     """Enough (sequence, direction) chains to fill the GPU and more than one segment: the default routes to the
     wavefront form; results agree with the three-launch form and a second call gives the same bits."""

@@ -110,11 +110,11 @@ int vig::bigla_fwd_internal(const void* q, const void* k, const void* v, const v
     p.dir_mask = dir_mask; p.status = status_dev;
 
     if (impl == VIG_IMPL_TC_WAVE) {
-        if (!bigla_wave_supported(p) || need_states && !o) return VIG_ERR_SHAPE;
+        if (!bigla_wave_supported(p)) return VIG_ERR_SHAPE;
         if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255)) return VIG_ERR_ALIGN;
         return bigla_wave_launch(p, workspace, workspace_bytes, (cudaStream_t)stream);
     }
-    if (impl == VIG_IMPL_AUTO && !no_single && o && bigla_wave_supported(p) && bigla_wave_preferred(p) && workspace &&
+    if (impl == VIG_IMPL_AUTO && !no_single && bigla_wave_supported(p) && bigla_wave_preferred(p) && workspace &&
         !(reinterpret_cast<uintptr_t>(workspace) & 255) && workspace_bytes >= bigla_wave_workspace(B, H, L, dk, dv))
         return bigla_wave_launch(p, workspace, workspace_bytes, (cudaStream_t)stream);
     bool use_tc = false;

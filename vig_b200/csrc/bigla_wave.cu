@@ -139,6 +139,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     const int nseg = wp.nseg, seg_chunks = wp.seg_chunks;
     const int dir_first = (p.dir_mask & 1) ? 0 : 1, ndir = (p.dir_mask == 3) ? 2 : 1;
     const int per_step = p.B * p.H * ndir, total = per_step * nseg;
+    // States-only call (no output tensor: the caller wants the chains' end states and summed log-gates, e.g. the summary pass
+    // of the sequence split): q is not loaded, the scores, both output products, the masking and the staging are skipped;
+    // what runs is the gate prefix, the K-tilde scaling, the state-update MMA and the state chain.
+    const bool so = p.o == nullptr;
 
     auto bar = [&](int i) { return sbase + WO_BAR + 8u * (uint32_t)i; };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + WO_MISC);
@@ -227,10 +231,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const int t0 = (lcur.c0 + chunk_of(lcur, l_ci)) * CHUNK;
                 const int b = lcur.b, h = lcur.h;
                 const uint32_t dst = sbase + s * W_STAGE_B, fb = bar(B_FULL + s);
-                mbar_expect_tx(fb, W_STAGE_B);
+                mbar_expect_tx(fb, so ? W_STAGE_B - W_TILE : W_STAGE_B);
                 tma_load_4d(dst + WS_K, &maps.k, 0, t0, h, b, fb);
                 tma_load_4d(dst + WS_G, lcur.dir ? &maps.gb : &maps.gf, 0, t0, h, b, fb);
-                tma_load_4d(dst + WS_Q, &maps.q, 0, t0, h, b, fb);
+                if (!so) tma_load_4d(dst + WS_Q, &maps.q, 0, t0, h, b, fb);
                 tma_load_4d(dst + WS_V, &maps.v, 0, t0, h, b, fb);
             }
         } else if (warp == W_MMA_WARP) {
@@ -255,6 +259,18 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 // control flow stays convergent, so loop counters and descriptor arithmetic run in the uniform datapath
                 // instead of on the issuing lane (a lane-0 branch around the loops made every MMA cost ~150 cycles to issue).
                 const bool issuer = lane == 0;
+                if (so) {                                      // states only: the state update, then the stage is free
+                    // the state warps' arrival for this iteration says they have taken the previous state update out of tensor
+                    // memory: the update two back shared this one's slot and barrier (in a full call the wait before step (b) is
+                    // what keeps the MMA warp from running ahead)
+                    waiter.wait_lite(bar(B_STREADY), m & 1);
+                    tc_fence_after();
+#pragma unroll
+                    for (uint32_t k8 = 0; k8 < CHUNK / 16; ++k8) { if (issuer) tc_mma(u_acc, k_lo + 128 * k8, v_lo + 128 * k8, IDESC_U, k8 > 0); }
+                    if (issuer) { tc_commit(bar(B_UFULL + (m & 1u))); tc_commit(bar(B_SFREE + s)); }
+                    __syncwarp();
+                    continue;
+                }
                 // the barriers of (b) are asked about before (a) and the state update are issued, that of (c) before (b)
                 const uint32_t pre_st = mbar_test_wait(bar(B_STREADY), m & 1);
                 const uint32_t pre_of = m >= 2 ? mbar_test_wait(bar(B_OFREE + (m & 1)), ((m >> 1) - 1) & 1) : 1u;
@@ -293,7 +309,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             Item cur; cur.nch = 0; cur.bh = cur.c0 = cur.dir = cur.w = 0;
             int items = 0, ci = 0;
             #pragma unroll 1
-            for (uint32_t j = 0;; ++j, ++ci) {
+            for (uint32_t j = 0; !so; ++j, ++ci) {              // (a states-only call stages nothing)
                 waiter.wait_lite(bar(B_OSTAGED + (j & 1)), (j >> 1) & 1);
                 if (*abort_flag) break;
                 if (ci == cur.nch) { read_item(items, cur); cur.b = ring[items & 7].b; cur.h = ring[items & 7].h; ++items; ci = 0; }
@@ -427,7 +443,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             }
             }
             // ---- scores of iteration j = m - 1: TMEM -> masked 16-bit tiles (my 32 rows x key block `sub`) ----
-            if (m >= 1 && (!ended || m - 1 < end_m)) {
+            if (!so && m >= 1 && (!ended || m - 1 < end_m)) {
                 const uint32_t j = m - 1;
                 if (!pre_pfull) waiter.wait_lite(bar(B_PFULL), j & 1);
                 __syncwarp();
@@ -463,7 +479,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (lane == 0) mbar_arrive_plain(bar(B_PREADY));
             }
             // ---- output of iteration j = m - 2: accumulator slot -> 16-bit staging tile (my 32 rows x 16 columns) ----
-            if (m >= 2 && (!ended || m - 2 < end_m)) {
+            if (!so && m >= 2 && (!ended || m - 2 < end_m)) {
                 const uint32_t j = m - 2;
                 if (!pre_ofull) waiter.wait_lite(bar(B_OFULL + (j & 1)), (j >> 1) & 1);
                 if (j > 0 && !pre_xfree) waiter.wait_lite(bar(B_XFREE), (j - 1) & 1);        // the store thread has sent the previous tile
@@ -504,7 +520,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const uint32_t r7 = (uint32_t)((half * 4 + u) ^ dmask);
                 offs[u] = (uint32_t)(grp * 8 + r7) * 128 + ((chunk ^ r7) << 4) + sw_in;
                 rk[u] = *reinterpret_cast<const uint2*>(stg + WS_K + offs[u]);
-                rq[u] = *reinterpret_cast<const uint2*>(stg + WS_Q + offs[u]);
+                rq[u] = so ? make_uint2(0u, 0u) : *reinterpret_cast<const uint2*>(stg + WS_Q + offs[u]);
             }
             if (!pre_part) waiter.wait_lite(bar(B_PART + (m & 1)), (m >> 1) & 1);     // all sixteen group sums are in
             __syncwarp();
@@ -564,16 +580,16 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 const float ex = off.x + gl[u].x, ey = off.y + gl[u].y, ez = off.z + gl[u].z, ew = off.w + gl[u].w;
                 uint2 ko, qo;                                 // scale * out_scale is applied to the output instead
                 ko.x = ScalePair<T>::mul(rk[u].x, ex2(-ex), ex2(-ey)); ko.y = ScalePair<T>::mul(rk[u].y, ex2(-ez), ex2(-ew));
-                qo.x = ScalePair<T>::mul(rq[u].x, ex2(ex), ex2(ey)); qo.y = ScalePair<T>::mul(rq[u].y, ex2(ez), ex2(ew));
+                if (!so) { qo.x = ScalePair<T>::mul(rq[u].x, ex2(ex), ex2(ey)); qo.y = ScalePair<T>::mul(rq[u].y, ex2(ez), ex2(ew)); }
                 *reinterpret_cast<uint2*>(stg + WS_K + offs[u]) = ko;
-                *reinterpret_cast<uint2*>(stg + WS_Q + offs[u]) = qo;
+                if (!so) *reinterpret_cast<uint2*>(stg + WS_Q + offs[u]) = qo;
             }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive_plain(bar(B_PREPPED + s));
             }
-            if (ended && m >= end_m + 1) {                    // everything that exists is masked and staged: tell the store thread
-                if (lane == 0) mbar_arrive_plain(bar(B_OSTAGED + (end_m & 1)));
+            if (ended && (so || m >= end_m + 1)) {            // everything that exists is masked and staged: tell the store thread
+                if (lane == 0 && !so) mbar_arrive_plain(bar(B_OSTAGED + (end_m & 1)));
                 break;
             }
         }
@@ -626,11 +642,11 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             __syncwarp();
             if (*abort_flag) break;
             const float* ve = vec + (m & 3) * 128;             // [G_ref | G_last] of this iteration, log2 units
-            if (m > 0) {                                      // the previous iteration's state product has read the operand
+            if (m > 0 && !so) {                               // the previous iteration's state product has read the operand
                 waiter.wait_lite(bar(B_STFREE), (m - 1) & 1);
                 __syncwarp();
             }
-            if (!s_zero) {                                    // bf16(2^G_ref * S_in), MN-major [channel][value]
+            if (!s_zero && !so) {                             // bf16(2^G_ref * S_in), MN-major [channel][value]
                 const float eg = ex2(ve[st_row]);
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
@@ -770,13 +786,14 @@ int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream
 
 bool bigla_wave_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
-    if (p.dv != WDV || p.dk != WDK || !p.o || !p.q || p.B * p.H < 1 || p.L < 1) return false;
+    if (p.dv != WDV || p.dk != WDK || p.B * p.H < 1 || p.L < 1) return false;
+    if (p.o ? !p.q : !(p.final_f || p.final_b || p.logdecay_f || p.logdecay_b)) return false;   // an output, or a states-only call
     if (p.dir_mask < 1 || p.dir_mask > 3) return false;
     if ((long long)p.B * p.H * 2 * ((p.L + W_SEG_CHUNKS_MIN * CHUNK - 1) / (W_SEG_CHUNKS_MIN * CHUNK)) >= (1ll << 24)) return false;   // tickets are decoded in fp32
-    if (!tc::tma_ok(p.q, p.sq, p.B, p.H) || !tc::tma_ok(p.k, p.sk, p.B, p.H) || !tc::tma_ok(p.v, p.sv, p.B, p.H)) return false;
+    if ((p.o && !tc::tma_ok(p.q, p.sq, p.B, p.H)) || !tc::tma_ok(p.k, p.sk, p.B, p.H) || !tc::tma_ok(p.v, p.sv, p.B, p.H)) return false;
     if ((p.dir_mask & 1) && (!p.gf || !tc::tma_ok(p.gf, p.sgf, p.B, p.H))) return false;
     if ((p.dir_mask & 2) && (!p.gb || !tc::tma_ok(p.gb, p.sgb, p.B, p.H))) return false;
-    if ((reinterpret_cast<uintptr_t>(p.o) & 15) || (p.so[0] * 2) % 16 || (p.so[1] * 2) % 16 || (p.so[2] * 2) % 16) return false;
+    if (p.o && ((reinterpret_cast<uintptr_t>(p.o) & 15) || (p.so[0] * 2) % 16 || (p.so[1] * 2) % 16 || (p.so[2] * 2) % 16)) return false;
     return tc::encode_fn() != nullptr;
 }
 
@@ -801,12 +818,14 @@ int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStrea
     const int64_t* gfst = p.gf ? p.sgf : p.sgb;
     const void* gbs = p.gb ? p.gb : p.gf;
     const int64_t* gbst = p.gb ? p.sgb : p.sgf;
-    if (!tc::make_map(&maps.q, p.q, p.sq, p.B, p.H, p.L, p.dk, p.dtype, true) ||
+    // a states-only call reads no q and writes no output: those two maps stand in with the k / v tensors and are never used
+    const bool so = p.o == nullptr;
+    if (!tc::make_map(&maps.q, so ? p.k : p.q, so ? p.sk : p.sq, p.B, p.H, p.L, p.dk, p.dtype, true) ||
         !tc::make_map(&maps.k, p.k, p.sk, p.B, p.H, p.L, p.dk, p.dtype, true) ||
         !tc::make_map(&maps.v, p.v, p.sv, p.B, p.H, p.L, p.dv, p.dtype, true) ||
         !tc::make_map(&maps.gf, gfs, gfst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
         !tc::make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
-        !tc::make_map(&maps.o, p.o, p.so, p.B, p.H, p.L, p.dv, p.dtype, true))
+        !tc::make_map(&maps.o, so ? p.v : p.o, so ? p.sv : p.so, p.B, p.H, p.L, p.dv, p.dtype, true))
         return VIG_ERR_DEVICE;
     // gate form and clamp are compile-time properties of the kernel: no branch inside its token loops
     const bool raw = p.gate_norm > 0.f, clamp = p.clamp_min == p.clamp_min;
