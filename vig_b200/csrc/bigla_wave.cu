@@ -126,7 +126,7 @@ template <> struct ScalePair<__half> {
     }
 };
 
-template <typename T, bool RAW, bool CLAMP>
+template <typename T, bool RAW, bool CLAMP, bool SO>
 __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_constant__ WaveMaps maps, const WaveParams wp) {
     const BiglaParams& p = wp.p;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
     // States-only call (no output tensor: the caller wants the chains' end states and summed log-gates, e.g. the summary pass
     // of the sequence split): q is not loaded, the scores, both output products, the masking and the staging are skipped;
     // what runs is the gate prefix, the K-tilde scaling, the state-update MMA and the state chain.
-    const bool so = p.o == nullptr;
+    constexpr bool so = SO;                                   // a template parameter: the full kernel carries none of this mode's code
 
     auto bar = [&](int i) { return sbase + WO_BAR + 8u * (uint32_t)i; };
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + WO_MISC);
@@ -745,7 +745,7 @@ int wave_seg_chunks(const BiglaParams& p, int sms) {
     return sc;
 }
 
-template <typename T, bool RAW, bool CLAMP>
+template <typename T, bool RAW, bool CLAMP, bool SO>
 int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream_t stream) {
     const int sms = wave_sm_count();
     if (sms <= 0) return VIG_ERR_DEVICE;
@@ -773,7 +773,7 @@ int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream
     wp.mailbox = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + cb);
     cudaError_t e;
     if ((e = cudaMemsetAsync(ws, 0, cb, stream)) != cudaSuccess) return (int)e;
-    auto kern = bigla_wave_kernel<T, RAW, CLAMP>;
+    auto kern = bigla_wave_kernel<T, RAW, CLAMP, SO>;
     if ((e = ensure_smem_attr(reinterpret_cast<const void*>(kern), W_SMEM_BYTES)) != cudaSuccess) return (int)e;
     const int ndir = p.dir_mask == 3 ? 2 : 1;
     const long long items = (long long)BH * ndir * nseg;
@@ -829,12 +829,14 @@ int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStrea
         return VIG_ERR_DEVICE;
     // gate form and clamp are compile-time properties of the kernel: no branch inside its token loops
     const bool raw = p.gate_norm > 0.f, clamp = p.clamp_min == p.clamp_min;
-#define VIG_WAVE(TT)                                                                   \
-    if (raw) return clamp ? launch_wave<TT, true, true>(p, maps, ws, stream) : launch_wave<TT, true, false>(p, maps, ws, stream); \
-    return clamp ? launch_wave<TT, false, true>(p, maps, ws, stream) : launch_wave<TT, false, false>(p, maps, ws, stream);
+#define VIG_WAVE2(TT, SO_)                                                             \
+    if (raw) return clamp ? launch_wave<TT, true, true, SO_>(p, maps, ws, stream) : launch_wave<TT, true, false, SO_>(p, maps, ws, stream); \
+    return clamp ? launch_wave<TT, false, true, SO_>(p, maps, ws, stream) : launch_wave<TT, false, false, SO_>(p, maps, ws, stream);
+#define VIG_WAVE(TT) if (so) { VIG_WAVE2(TT, true) } VIG_WAVE2(TT, false)
     if (p.dtype == VIG_DTYPE_BF16) { VIG_WAVE(__nv_bfloat16) }
     VIG_WAVE(__half)
 #undef VIG_WAVE
+#undef VIG_WAVE2
 }
 
 }  // namespace vig
