@@ -46,12 +46,13 @@ def test_dwconv3x3(dtype, hw, C, act, bias):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,hw,C,act,bias", [(8, (64, 64), 192, True, False), (8, (33, 47), 384, True, True), (2, (61, 130), 768, False, False),
-                                             (8, (50, 60), 200, True, True), (4, (3, 700), 512, True, False)])
+                                             (8, (50, 60), 200, True, True), (4, (3, 700), 512, True, False),
+                                             (4096, (7, 5), 192, True, False), (64, (64, 300), 8, False, True)])
 def test_dwconv3x3_tma_form(dtype, B, hw, C, act, bias):
     """Inputs of 4M elements and more run the TMA-fed kernel (tiles of 2 rows with a zero-filled border): against the
     oracle at the type's bar, and bit for bit against the sliding-window kernel, reached through the halo entry point
     with no halo rows.  Shapes: the headline one, ragged widths and heights, channel counts cut into chunks of 256 / 192
-    channels, a width cut into several column blocks."""
+    channels, a width cut into several column blocks, images narrower than a thread's run of 8 columns, 8 channels."""
     import vig_b200
     from vig_b200 import _lib
     h, w = hw
