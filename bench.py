@@ -60,11 +60,15 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
+        self.t_mark = None                      # wall-clock start of the timed region: samples from then on are "under load"
+
+    def mark(self):
+        self.t_mark = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -73,7 +77,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -82,7 +86,10 @@ class ClockSampler:
         self.thread.join(timeout=2)
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        # the sampler is started before the warm-up (nvidia-smi takes a while to come up) and read from the start of the
+        # timed region on; a region too short to catch a sample falls back to the warm-up's samples (same load)
+        in_region = [ln for t, ln in self.lines if self.t_mark is None or t >= self.t_mark]
+        for ln in in_region or [ln for _, ln in self.lines]:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 7:
                 continue
@@ -245,6 +252,8 @@ def main():
     # on the same seeded inputs (two different kernels of the product; the oracle is not involved)
     output_check = scan_self_check(vig_b200, batch, shape.num_heads, L, shape.key_dim // shape.num_heads,
                                    shape.value_dim // shape.num_heads, dev)
+    sampler = ClockSampler(local)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
     vops.check_status()          # no kernel reported a run-out wait or an out-of-range gate during warm-up
@@ -260,12 +269,11 @@ def main():
             graph = None
             torch.cuda.synchronize()
     sync_all()
-    sampler = ClockSampler(local)
-    sampler.start()
     counts["launches"] = 0
     timing["on"] = graph is None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
+    sampler.mark()
     e0.record()
     for _ in range(args.steps):
         if graph is not None:
