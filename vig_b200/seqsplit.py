@@ -41,30 +41,37 @@ def fold(summaries, rank, dk, dv, init_fwd=None, init_bwd=None):
     forward:  S = init_fwd; for r < rank:            S = exp(D_f[r]) * S + U_f[r]
     backward: S = init_bwd; for r > rank, descending: S = exp(D_b[r]) * S + U_b[r]
 
-    Unrolled, S = sum_r w_r * U_r with w_r = exp(sum of the log-decays of the slices between r and this one): two
-    cumulative sums over the rank axis and one weighted sum per direction, a handful of launches whatever the world size.
+    Unrolled, S = sum_r w_r * U_r with w_r = exp(sum of the log-decays of the slices between r and this one).  With
+    P = cumulative sum of D over the rank axis (one call for both directions), the slices between r and ``rank`` sum to
+    ``P[rank-1] - P[r]`` (forward, r < rank) and ``P[r-1] - P[rank]`` (backward, r > rank): one cumulative sum, and per
+    direction a subtraction, an exponential and a weighted sum -- a dozen launches whatever the world size (the host's
+    launch time is what bounds the split forward at 8 ranks).
     """
     msgs = summaries if torch.is_tensor(summaries) else torch.stack(list(summaries))
     world = msgs.shape[0]
-    u = msgs[..., :dk * dv].reshape(*msgs.shape[:-1], dk, dv)          # [world, B, H, 2, dk, dv]
+    u = msgs[..., :dk * dv].unflatten(-1, (dk, dv))                    # [world, B, H, 2, dk, dv]
     d = msgs[..., dk * dv:]                                            # [world, B, H, 2, dk]
-    zero_d = torch.zeros_like(d[0, :, :, 0])
+    prefix = torch.cumsum(d, 0)                                        # inclusive, both directions at once
 
-    def chain(us, ds, init):
-        """us/ds: the slices the state passes through, in scan order (nearest to this slice last)."""
-        n = us.shape[0]
-        if n == 0:
-            return torch.zeros_like(u[0, :, :, 0]) if init is None else init.float().clone()
-        # decay applied to U of slice i: the slices after it in scan order; suffix sums of the log-decays, exclusive
-        after = torch.flip(torch.cumsum(torch.flip(ds, [0]), 0), [0]) - ds
-        state = (us * after.exp().unsqueeze(-1)).sum(0)
-        if init is not None:
-            state = state + init.float() * ds.sum(0).exp().unsqueeze(-1)
-        return state
+    def zero_state():
+        return torch.zeros_like(u[0, :, :, 0])
 
-    s_f = chain(u[:rank, :, :, 0], d[:rank, :, :, 0], init_fwd)
-    s_b = chain(torch.flip(u[rank + 1:, :, :, 1], [0]), torch.flip(d[rank + 1:, :, :, 1], [0]), init_bwd)
-    del zero_d, world
+    if rank > 0:
+        # forward: slices r = 0 .. rank-1, each decayed by the slices r+1 .. rank-1
+        w = (prefix[rank - 1, :, :, 0].unsqueeze(0) - prefix[:rank, :, :, 0]).exp()
+        s_f = (u[:rank, :, :, 0] * w.unsqueeze(-1)).sum(0)
+        if init_fwd is not None:
+            s_f = s_f + init_fwd.float() * prefix[rank - 1, :, :, 0].exp().unsqueeze(-1)
+    else:
+        s_f = zero_state() if init_fwd is None else init_fwd.float().clone()
+    if rank + 1 < world:
+        # backward: slices r = rank+1 .. world-1, each decayed by the slices rank+1 .. r-1
+        w = (prefix[rank:world - 1, :, :, 1] - prefix[rank, :, :, 1].unsqueeze(0)).exp()
+        s_b = (u[rank + 1:, :, :, 1] * w.unsqueeze(-1)).sum(0)
+        if init_bwd is not None:
+            s_b = s_b + init_bwd.float() * (prefix[world - 1, :, :, 1] - prefix[rank, :, :, 1]).exp().unsqueeze(-1)
+    else:
+        s_b = zero_state() if init_bwd is None else init_bwd.float().clone()
     return s_f.contiguous(), s_b.contiguous()
 
 
