@@ -1,31 +1,34 @@
 // Bi-directional gated linear attention, warp-specialised "wavefront" form for large batches (tcgen05 + TMEM).
 //
-// Work item = (sequence b*h, segment of 256, 512 or 1024 tokens, direction).  Items are drawn from a ticket counter in
-// wavefront order: step w holds segment w of every forward chain and segment nseg-1-w of every backward chain, so
-// the state that enters an item was produced by an item with a smaller ticket, which is running or done.  States
-// pass from segment to segment through a two-slot mailbox per (sequence, direction) in global memory; the two
-// directions of a chunk meet in the output tensor: the direction that is scheduled first stores its half, the other
-// adds to it with a TMA reduction once the first has raised the chunk's flag.
+// Work item = (sequence b*h, run of 2, 4 or 8 chunks of 128 tokens, direction).  Items are drawn from a ticket counter
+// in wavefront order: step w holds the w-th item of every chain (a forward chain counts its chunks from the start of the
+// sequence, a backward chain from its end, both through the same schedule of item lengths, shorter at the end), so the
+// state that enters an item was produced by an item with a smaller ticket, which is running or done.  States pass from
+// item to item through a two-slot mailbox per (sequence, direction) in global memory; the two directions of a chunk
+// meet in the output tensor: the direction that is scheduled first stores its half, the other adds to it with a TMA
+// reduction once the first has raised the chunk's flag.
 //
 // One persistent CTA per SM runs a pipeline over its stream of chunk iterations, roles decoupled by mbarriers:
 //
 //   load thread       work tickets; TMA loads of q, k, gates, v into a 3-stage ring
-//   MMA thread        all tcgen05.mma issue
-//   16 prep warps     gate transform and cumulative log-gates (in registers), then q * 2^(G_i - G_ref) and
-//                     k * 2^(G_ref - G_j) IN PLACE over the raw tiles
-//                     (group sums exchanged through shared memory; every warp forms its own offset from them: code that
-//                     all sixteen run stays in the instruction cache, a seventeenth warp's would not)
-//   4 score warps     scores TMEM -> masked bf16 tiles; output accumulators TMEM -> 16-bit tile in shared memory
-//   store thread      output tile -> global by TMA (store, or reduction onto the other direction's half); chunk flags
+//   MMA warp          all tcgen05.mma issue (the whole warp walks the loops, lane 0 issues)
+//   16 worker warps   one instruction stream per trip: for iteration m the gate transform and cumulative log-gates (in
+//                     registers; group sums exchanged through shared memory, every warp forms its own offset from them),
+//                     then q * 2^(G_i - G_ref) and k * 2^(G_ref - G_j) IN PLACE over the raw tiles; in between, the scores
+//                     of iteration m-1 from tensor memory, masked, back to tensor memory as packed 16-bit pairs, and the
+//                     output accumulator of iteration m-2 from tensor memory to a 16-bit staging tile in shared memory
+//   store thread      staging tile -> global by TMA (store, or reduction onto the other direction's half); chunk flags
 //   4 state warps     S <- 2^G_last S + 2^(G_last - G_ref) K~^T V in registers; bf16 state operand; mailbox
 //
 // Per iteration m (one chunk of 128 tokens, one direction), on the tensor core:
-//   P  = Q~ K~^T                (128x128x64)   then masked by the score warps
+//   P  = Q~ K~^T                (128x128x64)   then masked by the worker warps
+//   U  = K~^T V                 ( 64x 64x128)  right behind it: the state chain waits for nothing else
 //   O  = Q~ (2^G_ref S_in)      (128x 64x64)   skipped when S_in is exactly zero
-//   O += P V                    (128x 64x128)
-//   U  = K~^T V                 ( 64x 64x128)
+//   O += P V                    (128x 64x128)  P read from tensor memory
 // Only the state chain (U -> S -> state operand -> next chunk's second product) is sequential; everything else of
 // the following iterations runs ahead as far as the rings allow.
+// A call without an output (end states and summed log-gates only) runs the SO instantiation: no q, no P, no O, no masking,
+// no staging.
 //
 // Every wait (mbarrier, mailbox counter, chunk flag) is bounded; when one runs out the CTA sets bit 0 of the status
 // word, stops waiting on anything else, drains its control flow and frees its tensor memory.
