@@ -467,7 +467,11 @@ def run_seq_split(vig_b200, vops, oracle, dev, rank, world, steps=5, warmup=3):
         vops.check_status()
         ms_one, whole = timed(lambda: model(images))
         vops.check_status()
-        phases = seqsplit.phase_times(model, images) if hasattr(seqsplit, "phase_times") else None
+        try:                                                # rank 0's view of where a split forward's time goes
+            phases = seqsplit.phase_times(model, images)
+        except Exception as exc:                            # a diagnostic: never in the way of the measurement
+            sys.stderr.write(f"bench: phase times unavailable ({exc})\n")
+            phases = None
     err = float((split.float() - whole.float()).abs().max() / whole.float().abs().max())
     line = {"workload": f"vig_b_2048_seq: ViG {preset} forward, {size}x{size} images (L={(size // 16) ** 2}), batch {batch}, "
                         "token sequence split across the GPUs", "n_gpus": world, "steps": steps, "warmup": warmup,

@@ -189,3 +189,47 @@ def vig_forward_sequence_parallel(model, images, group=None):
     pooled = x.float().sum(dim=1)
     dist.all_reduce(pooled, group=group)
     return model.head((pooled / (h * w)).to(x.dtype))
+
+
+def phase_times(model, images, group=None, steps=3):
+    """Milliseconds per forward that this rank spends in the parts the sequence split adds (CUDA events around each call:
+    ``summary`` = states-only scan + packing, ``all_gather``, ``fold``, ``halo_exchange``) and in the scan proper and the
+    stem, averaged over ``steps`` forwards after one warm-up.  A collective's figure includes the time this rank waits for
+    the slowest one."""
+    import sys
+    mod = sys.modules[__name__]
+    events = {}
+
+    def timed(name, fn):
+        def inner(*a, **k):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **k)
+            e1.record()
+            events.setdefault(name, []).append((e0, e1))
+            return r
+        return inner
+
+    saved = {n: getattr(mod, n) for n in ("exchange", "fold", "exchange_halo_rows", "bi_gla_sequence_parallel")}
+    summary_fn, scan_fn = timed("summary", cuda_summary), timed("scan", cuda_scan)
+    inner_split = saved["bi_gla_sequence_parallel"]
+    stem = model.patch_embed.forward
+    try:
+        mod.exchange = timed("all_gather", saved["exchange"])
+        mod.fold = timed("fold", saved["fold"])
+        mod.exchange_halo_rows = timed("halo_exchange", saved["exchange_halo_rows"])
+        mod.bi_gla_sequence_parallel = lambda q, k, v, gf, gb, group=None, **kw: inner_split(
+            q, k, v, gf, gb, group=group, summary_fn=summary_fn, scan_fn=scan_fn, **kw)
+        model.patch_embed.forward = timed("stem", stem)
+        with torch.no_grad():
+            vig_forward_sequence_parallel(model, images, group)
+            torch.cuda.synchronize()
+            events.clear()
+            for _ in range(steps):
+                vig_forward_sequence_parallel(model, images, group)
+            torch.cuda.synchronize()
+    finally:
+        for n, f in saved.items():
+            setattr(mod, n, f)
+        model.patch_embed.forward = stem
+    return {n: sum(a.elapsed_time(b) for a, b in ev) / steps for n, ev in events.items()}
