@@ -231,6 +231,43 @@ def test_wavefront_form_states_only(shape, dir_mask, impl_wave):
         assert rel_err(ex[name], ex_split[name]) < tol, name
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,dir_mask,init,impl_wave", [((2, 3, 1300), 3, True, True), ((50, 3, 2100), 3, False, False),
+                                                           ((100, 3, 1500), 2, True, False), ((3, 2, 196), 3, False, True)])
+def test_wavefront_form_dk32(shape, dir_mask, init, impl_wave, dtype):
+    """The reference's shipped head size (dk = 32, dv = 64) in the wavefront form: the q / k / gate boxes are 64 channels
+    wide over 32-channel tensors, the upper half zero-filled by the TMA unit; initial states go in and final states and
+    log-decays come out as [.., 32, ..] tensors.  Against the three-launch form (which has a dk = 32 kernel of its own) and,
+    where the token loop is affordable, the fp32 oracle; the states-only call gives the same states bit for bit."""
+    import vig_b200
+    from vig_b200 import _lib
+    B, H, L = shape
+    ins = oracle.make_bigla_inputs(B, H, L, 32, 64, seed=L + dir_mask)
+    g = torch.Generator().manual_seed(9)
+    i_f, i_b = torch.randn(B, H, 32, 64, generator=g), torch.randn(B, H, 32, 64, generator=g)
+    dev = _cuda(ins, dtype)
+    kw = dict(output_final_state=True, output_logdecay=True, dir_mask=dir_mask)
+    if init:
+        kw.update(init_state_fwd=i_f.cuda(), init_state_bwd=i_b.cuda())
+    impl = _lib.IMPL_TC_WAVE if impl_wave else _lib.IMPL_AUTO
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    o1, ex1 = vig_b200.bi_gla(*dev, impl=impl, status=status, **kw)
+    o0, ex0 = vig_b200.bi_gla(*dev, impl=_lib.IMPL_TC_SPLIT, **kw)
+    assert int(status.item()) == 0
+    assert rel_err(o1.float(), o0.float()) < 1.5e-2
+    for name in ex0:
+        assert ex1[name].shape == ex0[name].shape
+        tol = 1e-5 if name.startswith("logdecay") else 1e-2
+        assert rel_err(ex1[name], ex0[name]) < tol, name
+    _, ex_so = vig_b200.bi_gla(*dev, want_output=False, impl=impl, **kw)
+    for name in ex1:
+        assert torch.equal(ex_so[name], ex1[name]), name
+    if B * L <= 4096 and dir_mask == 3:
+        f32 = [t.float().cpu() for t in dev]
+        ref = oracle.naive_bi_gla(*f32, init_fwd=i_f if init else None, init_bwd=i_b if init else None)
+        assert rel_err(o1.float(), ref) < 2e-2
+
+
 def test_wavefront_form_is_the_default_for_large_batches():
     """Enough (sequence, direction) chains to fill the GPU and more than one segment: the default routes to the
     wavefront form; results agree with the three-launch form and a second call gives the same bits."""

@@ -46,7 +46,7 @@ size_t vig::bigla_workspace_internal(int B, int H, int L, int dk, int dv, int dt
     if (B <= 0 || H <= 0 || L <= 0 || !dims_ok(dk, dv)) return 0;
     size_t simt = bigla_simt_workspace(B, H, L, dk, dv);
     size_t tc = (dtype != VIG_DTYPE_F32 && impl != VIG_IMPL_SIMT) ? bigla_tc_workspace(B, H, L, dk, dv, no_single || !(impl == VIG_IMPL_TC_SINGLE || (impl != VIG_IMPL_TC_SPLIT && bigla_tc_prefers_single(L)))) : 0;
-    size_t wave = (dtype != VIG_DTYPE_F32 && (impl == VIG_IMPL_TC_WAVE || impl == VIG_IMPL_AUTO) && dk == 64 && dv == 64) ? bigla_wave_workspace(B, H, L, dk, dv) : 0;
+    size_t wave = (dtype != VIG_DTYPE_F32 && (impl == VIG_IMPL_TC_WAVE || impl == VIG_IMPL_AUTO) && (dk == 64 || dk == 32) && dv == 64) ? bigla_wave_workspace(B, H, L, dk, dv) : 0;
     if (impl == VIG_IMPL_TC_WAVE) return wave;
     if (no_single) wave = 0;
     size_t m = simt > tc ? simt : tc;

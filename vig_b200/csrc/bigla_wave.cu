@@ -624,8 +624,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
             if (ci == 0) {                                    // the chain enters a new segment
                 const float* src = nullptr;
                 if (cur.w == 0) {
+                    // the caller's states are [dk, dv] per (b, h): with dk = 32 the kernel's upper 32 key channels are padding
                     const float* init = cur.dir ? p.init_b : p.init_f;
-                    if (init) src = init + (size_t)cur.bh * NE;
+                    if (init) src = init + (size_t)cur.bh * p.dk * WDV;
                     gacc = 0.f;
                 } else {
                     uint32_t* cnt = wp.chain_cnt + cur.bh * 2 + cur.dir;
@@ -635,9 +636,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                     gacc = __ldcg(box + NE + st_row);
                 }
                 s_zero = src == nullptr;
+                const bool row_in = cur.w > 0 || st_row < p.dk;     // (the mailbox holds all 64 rows, the padding ones zero)
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
-                    const float4 t4 = src ? __ldcg(reinterpret_cast<const float4*>(src + st_row * WDV + col_of(j))) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    const float4 t4 = src && row_in ? __ldcg(reinterpret_cast<const float4*>(src + st_row * WDV + col_of(j))) : make_float4(0.f, 0.f, 0.f, 0.f);
                     S[j] = t4.x; S[j + 1] = t4.y; S[j + 2] = t4.z; S[j + 3] = t4.w;
                 }
             }
@@ -691,18 +693,19 @@ __global__ void __launch_bounds__(W_THREADS, 1) bigla_wave_kernel(const __grid_c
                 if (last) {
                     float* fin = cur.dir ? p.final_b : p.final_f;
                     float* ld = cur.dir ? p.logdecay_b : p.logdecay_f;
-                    if (fin) dst = fin + (size_t)cur.bh * NE;
-                    if (ld) gdst = ld + (size_t)cur.bh * WDK;
+                    if (fin) dst = fin + (size_t)cur.bh * p.dk * WDV;
+                    if (ld) gdst = ld + (size_t)cur.bh * p.dk;
                 } else {
                     float* box = wp.mailbox + (((size_t)cur.bh * 2 + cur.dir) * 2 + (cur.w & 1)) * SLOT;
                     dst = box; gdst = box + NE;
                 }
-                if (dst) {
+                const bool row_out = !last || st_row < p.dk;        // the caller's tensors end at dk rows
+                if (dst && row_out) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 4)
                         *reinterpret_cast<float4*>(dst + st_row * WDV + col_of(j)) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
                 }
-                if (gdst && hi == 0) gdst[st_row] = last ? gacc * LN2 : gacc;   // the caller gets natural-log units
+                if (gdst && hi == 0 && row_out) gdst[st_row] = last ? gacc * LN2 : gacc;   // the caller gets natural-log units
                 if (!last) {
                     __syncwarp();
                     if (lane == 0) { __threadfence(); atomicAdd(wp.chain_cnt + cur.bh * 2 + cur.dir, 1u); }
@@ -789,7 +792,10 @@ int launch_wave(const BiglaParams& p, const WaveMaps& maps, void* ws, cudaStream
 
 bool bigla_wave_supported(const BiglaParams& p) {
     if (p.dtype != VIG_DTYPE_BF16 && p.dtype != VIG_DTYPE_F16) return false;
-    if (p.dv != WDV || p.dk != WDK || p.B * p.H < 1 || p.L < 1) return false;
+    // dk = 32 runs as dk = 64 with the upper 32 key channels zero: the q / k / gate boxes are declared 64 wide over tensors
+    // of 32 channels and the TMA unit fills the rest with zeros, which stay zero through the scaling; half of the MMA
+    // work on those operands is wasted, the DRAM traffic is that of dk = 32
+    if (p.dv != WDV || (p.dk != WDK && p.dk != 32) || p.B * p.H < 1 || p.L < 1) return false;
     if (p.o ? !p.q : !(p.final_f || p.final_b || p.logdecay_f || p.logdecay_b)) return false;   // an output, or a states-only call
     if (p.dir_mask < 1 || p.dir_mask > 3) return false;
     if ((long long)p.B * p.H * 2 * ((p.L + W_SEG_CHUNKS_MIN * CHUNK - 1) / (W_SEG_CHUNKS_MIN * CHUNK)) >= (1ll << 24)) return false;   // tickets are decoded in fp32
@@ -811,7 +817,8 @@ bool bigla_wave_preferred(const BiglaParams& p) {
 
 // Counters (ticket, chain progress, chunk flags) followed by the state mailboxes.
 size_t bigla_wave_workspace(int B, int H, int L, int dk, int dv) {
-    return wave_counter_bytes(B, H, L) + (size_t)B * H * 2 * 2 * ((size_t)dk * dv + dk) * sizeof(float);
+    (void)dk; (void)dv;                                     // the mailbox slots hold the kernel's 64 x 64 states whatever dk is
+    return wave_counter_bytes(B, H, L) + (size_t)B * H * 2 * 2 * ((size_t)WDK * WDV + WDK) * sizeof(float);
 }
 
 int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStream_t stream) {
@@ -823,11 +830,11 @@ int bigla_wave_launch(const BiglaParams& p, void* ws, size_t ws_bytes, cudaStrea
     const int64_t* gbst = p.gb ? p.sgb : p.sgf;
     // a states-only call reads no q and writes no output: those two maps stand in with the k / v tensors and are never used
     const bool so = p.o == nullptr;
-    if (!tc::make_map(&maps.q, so ? p.k : p.q, so ? p.sk : p.sq, p.B, p.H, p.L, p.dk, p.dtype, true) ||
-        !tc::make_map(&maps.k, p.k, p.sk, p.B, p.H, p.L, p.dk, p.dtype, true) ||
+    if (!tc::make_map(&maps.q, so ? p.k : p.q, so ? p.sk : p.sq, p.B, p.H, p.L, p.dk, p.dtype, true, WDK) ||
+        !tc::make_map(&maps.k, p.k, p.sk, p.B, p.H, p.L, p.dk, p.dtype, true, WDK) ||
         !tc::make_map(&maps.v, p.v, p.sv, p.B, p.H, p.L, p.dv, p.dtype, true) ||
-        !tc::make_map(&maps.gf, gfs, gfst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
-        !tc::make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false) ||
+        !tc::make_map(&maps.gf, gfs, gfst, p.B, p.H, p.L, p.dk, p.dtype, false, WDK) ||
+        !tc::make_map(&maps.gb, gbs, gbst, p.B, p.H, p.L, p.dk, p.dtype, false, WDK) ||
         !tc::make_map(&maps.o, so ? p.v : p.o, so ? p.sv : p.so, p.B, p.H, p.L, p.dv, p.dtype, true))
         return VIG_ERR_DEVICE;
     // gate form and clamp are compile-time properties of the kernel: no branch inside its token loops

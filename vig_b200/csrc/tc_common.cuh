@@ -295,12 +295,13 @@ inline bool encode_cached(CUtensorMap* m, const MapKey& key) {
 }
 
 // [B,H,L,d] view with element strides s = (b, h, l): box of 128 tokens x d channels of one (b, h).
-inline bool make_map(CUtensorMap* m, const void* base, const int64_t* s, int B, int H, int L, int d, int dtype, bool swizzle128) {
+// ``box_d`` > d: the box is wider than the tensor's channel extent and the channels past d arrive as zeros (TMA fill).
+inline bool make_map(CUtensorMap* m, const void* base, const int64_t* s, int B, int H, int L, int d, int dtype, bool swizzle128, int box_d = 0) {
     MapKey key{};
     key.base = base; key.rank = 4; key.dtype = dtype; key.swizzle = swizzle128 ? 1 : 0;
     key.dims[0] = (uint64_t)d; key.dims[1] = (uint64_t)L; key.dims[2] = (uint64_t)H; key.dims[3] = (uint64_t)B;
     key.strides[0] = (uint64_t)s[2] * 2; key.strides[1] = (uint64_t)s[1] * 2; key.strides[2] = (uint64_t)s[0] * 2;
-    key.box[0] = (uint32_t)d; key.box[1] = CHUNK; key.box[2] = 1; key.box[3] = 1;
+    key.box[0] = (uint32_t)(box_d > 0 ? box_d : d); key.box[1] = CHUNK; key.box[2] = 1; key.box[3] = 1;
     return encode_cached(m, key);
 }
 
