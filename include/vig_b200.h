@@ -55,7 +55,7 @@ extern "C" {
                                256-token segments (falls back to three launches when either is missing).  AUTO and TC
                                pick it for sequences of 2048..8192 tokens, where it is the faster form. */
 #define VIG_IMPL_TC_SPLIT 4  /* tensor-core path as three launches (segment states, scan, outputs) at every length */
-#define VIG_IMPL_TC_WAVE 5   /* warp-specialised wavefront form (dk = dv = 64, 16-bit types, output requested): one persistent
+#define VIG_IMPL_TC_WAVE 5   /* warp-specialised wavefront form (dk = 64 or 32, dv = 64, 16-bit types; with or without an output): one persistent
                               CTA per SM, states handed from segment to segment; built for batches with at least as
                               many (sequence, direction) chains as the GPU has SMs */
 
