@@ -375,6 +375,8 @@ def main():
         # same rule as the library's default routing (bigla_wave_preferred): the wavefront kernel for large batches
         sms = torch.cuda.get_device_properties(0).multi_processor_count
         entry = tj.get("wave") if (dk == 64 and dv == 64 and L > 256 and 2 * batch * H >= sms) else tj.get("single_launch")
+        if dk != 64:
+            entry = None                                    # the captures are of dk = dv = 64 calls
         per_unit = (entry or {}).get("dram_bytes_per_token_head")
         traffic = per_unit * batch * H * L if per_unit else None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
