@@ -12,7 +12,10 @@ import torch.nn as nn
 
 import oracle
 
-REF_VIG = os.environ.get("VIG_REFERENCE_ROOT", "/root/reference") + "/classification/models/vig.py"
+# the reference checkout: named by VIG_REFERENCE_ROOT, else looked for as a `reference` folder beside this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_VIG = os.path.join(os.environ.get("VIG_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference")),
+                       "classification", "models", "vig.py")
 
 
 @pytest.fixture
