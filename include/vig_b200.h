@@ -238,6 +238,21 @@ VIG_API int vig_layernorm_act_add_fwd(const void* x, const void* pre_bias, const
 VIG_API int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream);
 
 /*
+ * The stem's first convolution with its bias, the LayerNorm2d after it and the swish after that, as one tensor-core
+ * kernel (bf16 / fp16; `V2PatchEmbed.proj[0..2]`, classification/models/vig.py:650-656, for kernel 9, stride 8, 3 input
+ * channels and 96 output channels: ViG-T).  cells: [B, CH, CW, 192] from `vig_stem_unfold_fwd`.  w2: [96, 512], the
+ * convolution's weight in the cell layout: columns 0..191 multiply cell (oy, ox), 192..383 cell (oy, ox+1), 384..447 the
+ * first 64 values of cell (oy+1, ox), 448..511 the first 64 values of cell (oy+1, ox+1), each in the cell's value order
+ * (dy*8 + dx)*3 + ic (the taps a 9 x 9 kernel has in the lower cells are among those values).  conv_bias (optional), ln_w,
+ * ln_b: [96].  y: [B, CH-1, CW-1, 96] contiguous (channels last).  Same roundings as convolution -> bias add -> LayerNorm
+ * run separately.  status_dev as in vig_bigla_fwd.
+ */
+VIG_API int vig_stem_conv_ln_supported(int B, int CH, int CW, int cell, int N, int dtype);
+VIG_API int vig_stem_conv_ln_fwd(const void* cells, const void* w2, const void* conv_bias, const void* ln_w, const void* ln_b, void* y,
+                                 int B, int CH, int CW, int cell, int N, float eps, int act_swish, int dtype,
+                                 int32_t* status_dev, void* stream);
+
+/*
  * Projection with the residual add and the next RMSNorm as its epilogue (bf16 / fp16): r = x W^T + residual (r = x W^T
  * when residual is NULL), h = RMSNorm(r) * norm_weight -- `o_proj` followed by `mlp_norm(h, residual, prenorm=True)`,
  * and `down_proj` followed by the next block's `attn_norm` / the model's final norm (classification/models/vig.py:463,

@@ -137,6 +137,43 @@ def test_stem_unfold(dtype, B, H, W):
     assert torch.equal(got, ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,W,bias,act", [(2, 1024, 1024, True, True), (3, 224, 224, True, True), (2, 320, 320, False, True),
+                                            (1, 8, 8, True, False), (5, 264, 1000, True, True), (150, 224, 224, True, True)])
+def test_stem_conv_layernorm_fused_gemm(dtype, B, H, W, bias, act):
+    """First stem convolution + bias + LayerNorm2d + swish as one tensor-core kernel: against the fp32 convolution of the
+    same 16-bit operands followed by LayerNorm (+ swish), and against the separate steps (library convolution on the
+    unfolded cells, then the LayerNorm kernel) it replaces.  Output widths that fill a 128-pixel tile exactly, that split
+    into 32 x 4 and 64 x 2 tiles with clipped edges, a single pixel, a ragged wide image, and more tiles than SMs."""
+    import torch.nn.functional as F
+    import vig_b200
+    from vig_b200.vig import V2PatchEmbed
+    g = torch.Generator().manual_seed(H + W + B)
+    pe = V2PatchEmbed(img_size=H, patch_size=16, in_chans=3, embed_dim=192, use_bias_in_patch=bias)
+    with torch.no_grad():
+        for prm in pe.parameters():
+            prm.copy_(torch.randn(prm.shape, generator=g) * (0.08 if prm.dim() > 1 else 0.3) + (1.0 if prm.dim() == 1 and prm.numel() == 96 else 0.0))
+    pe = pe.to(dtype).cuda().eval()
+    x = torch.randn(B, 3, H, W, generator=g).to(dtype).cuda()
+    conv, ln1 = pe.proj[0], pe.proj[1]
+    with torch.no_grad():
+        cells = vig_b200.ops.stem_unfold(x, 8)
+        assert vig_b200.ops.stem_conv_ln_supported(cells, 96)
+        got = vig_b200.ops.stem_conv_ln(cells, pe._gemm_weight(), conv.bias, ln1.weight, ln1.bias, ln1.eps, act_swish=act)
+        # the steps it replaces
+        y = pe._conv1(x)
+        sep = vig_b200.ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=act, pre_bias=conv.bias)
+        # fp32 reference from the same 16-bit operands
+        ref = F.conv2d(x.float(), conv.weight.float(), conv.bias.float() if bias else None, conv.stride, conv.padding).permute(0, 2, 3, 1)
+        ref = F.layer_norm(ref, (96,), ln1.weight.float(), ln1.bias.float(), ln1.eps)
+        if act:
+            ref = ref * torch.sigmoid(ref)
+    assert got.shape == sep.shape == ref.shape
+    assert rel_err(got.float(), ref) < TOL[dtype]
+    assert rel_err(got.float(), sep.float()) < TOL[dtype]
+    vig_b200.check_status()
+
+
 def test_patch_embed_matches_oracle():
     import vig_b200
     shape = oracle.ViGShape(192, 3, 1, 0.5, 1.0, True, True, num_classes=16)

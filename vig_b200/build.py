@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libvig_b200.so")
-SOURCES = ["abi.cu", "bigla_simt.cu", "bigla_tc.cu", "bigla_wave.cu", "elementwise.cu", "noalloc.cu", "bigla_bwd_simt.cu", "gemm_swiglu.cu", "gemm_addnorm.cu", "dwconv_tma.cu", "gemm_bias.cu"]
+SOURCES = ["abi.cu", "bigla_simt.cu", "bigla_tc.cu", "bigla_wave.cu", "elementwise.cu", "noalloc.cu", "bigla_bwd_simt.cu", "gemm_swiglu.cu", "gemm_addnorm.cu", "dwconv_tma.cu", "gemm_bias.cu", "gemm_stem.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -458,6 +458,35 @@ def stem_unfold(x, s):
     return cells
 
 
+def stem_conv_ln_supported(cells, out_channels):
+    """True when ``stem_conv_ln`` has a kernel for these cells (bf16 / fp16, cells of 192 values, 96 output channels)."""
+    if not (cells.is_cuda and cells.dtype in (torch.bfloat16, torch.float16) and cells.dim() == 4 and cells.is_contiguous()):
+        return False
+    B, CH, CW, cell = cells.shape
+    return bool(_lib.lib().vig_stem_conv_ln_supported(B, CH, CW, cell, int(out_channels), _lib.dtype_code(cells)))
+
+
+def stem_conv_ln(cells, w2, conv_bias, ln_weight, ln_bias, eps=1e-5, act_swish=True):
+    """The stem's first convolution on unfolded cells + bias + LayerNorm over channels (+ swish) in one tensor-core
+    kernel (see ``vig_stem_conv_ln_fwd``).  cells: ``[B, CH, CW, 192]``, w2: ``[96, 512]``; returns ``[B, CH-1, CW-1, 96]``."""
+    _lib.require_cuda(cells, w2, ln_weight, ln_bias)
+    B, CH, CW, cell = cells.shape
+    N = w2.shape[0]
+    if w2.dtype != cells.dtype or tuple(w2.shape) != (N, 2 * cell + 128) or not w2.is_contiguous() or not cells.is_contiguous():
+        raise ValueError("w2 must be a contiguous [N, 2*cell + 128] matrix of the cells' dtype, cells contiguous")
+    for t in (conv_bias, ln_weight, ln_bias):
+        if t is not None and (t.dtype != cells.dtype or t.numel() != N or t.device != cells.device):
+            raise ValueError("conv_bias / ln_weight / ln_bias must be [N] vectors of the cells' dtype on the cells' device")
+    y = torch.empty(B, CH - 1, CW - 1, N, dtype=cells.dtype, device=cells.device)
+    with torch.cuda.device_of(cells):
+        st = _lib.lib().vig_stem_conv_ln_fwd(_lib.ptr(cells), _lib.ptr(w2), _lib.ptr(conv_bias), _lib.ptr(ln_weight.contiguous()),
+                                             _lib.ptr(ln_bias.contiguous()), _lib.ptr(y), B, CH, CW, cell, N, float(eps),
+                                             int(bool(act_swish)), _lib.dtype_code(cells), _status_ptr(None, cells.device),
+                                             _lib.stream_ptr())
+    _lib.check(st, "vig_stem_conv_ln_fwd")
+    return y
+
+
 def swiglu(gate, y):
     """``fla/modules/activations.py:109-113``: ``gate * sigmoid(gate) * y``; inputs may be the two halves of one projection."""
     _lib.require_cuda(gate, y)

@@ -40,6 +40,8 @@ class V2PatchEmbed(nn.Module):
             LayerNorm2d(embed_dim))
         self.num_patches = (img_size // patch_size) ** 2
         self._w_blocks = None
+        self._w_gemm = None
+        self.fuse_conv1 = True          # first convolution + LayerNorm2d + swish as one kernel where there is one (ViG-T, 16-bit)
 
     def _block_weight(self):
         """[O, s*s*Cin, 2, 2] weight of the space-to-depth form, channels-last, cached per parameter version."""
@@ -54,6 +56,30 @@ class V2PatchEmbed(nn.Module):
             wb = big.view(O, Cin, 2, s, 2, s).permute(0, 3, 5, 1, 2, 4).reshape(O, s * s * Cin, 2, 2)
             self._w_blocks = (key, wb.contiguous(memory_format=torch.channels_last))
         return self._w_blocks[1]
+
+    def _gemm_weight(self):
+        """[O, 512] weight of the fused first stage (``ops.stem_conv_ln``): both cells of the upper cell row in full, the
+        first 64 values of the two cells below (a 9 x 9 kernel's taps there are among them: the rest of the block weight
+        is zero by construction).  Cached per parameter version."""
+        wb = self._block_weight()                                          # [O, 192, 2 (cell row), 2 (cell column)]
+        if self._w_gemm is None or self._w_gemm[0] is not wb:
+            w2 = torch.cat([wb[:, :, 0, 0], wb[:, :, 0, 1], wb[:, :64, 1, 0], wb[:, :64, 1, 1]], dim=1).contiguous()
+            self._w_gemm = (wb, w2)
+        return self._w_gemm[1]
+
+    def _conv1_ln_fused(self, x):
+        """Convolution + bias + LayerNorm2d + swish in one tensor-core kernel, channels-last ``[B, h, w, C/2]``; None when
+        the shape has no such kernel (then the two steps run separately)."""
+        from . import ops
+        conv, ln1, s = self.proj[0], self.proj[1], self.stride
+        B, Cin, H, W = x.shape
+        if not (self.fuse_conv1 and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and s == 8 and Cin == 3
+                and H % s == 0 and W % s == 0 and conv.weight.dtype == x.dtype):
+            return None
+        if not ops._lib.lib().vig_stem_conv_ln_supported(B, H // s + 1, W // s + 1, s * s * Cin, conv.weight.shape[0], ops._lib.dtype_code(x)):
+            return None
+        cells = ops.stem_unfold(x, s)
+        return ops.stem_conv_ln(cells, self._gemm_weight(), conv.bias, ln1.weight, ln1.bias, ln1.eps, act_swish=True)
 
     def _conv1(self, x):
         conv = self.proj[0]
@@ -75,9 +101,11 @@ class V2PatchEmbed(nn.Module):
         from . import ops
         ln1, ln2, conv2 = self.proj[1], self.proj[4], self.proj[3]
         # the convolutions run without their bias; it is added inside the LayerNorm kernel that follows
-        y = self._conv1(x)                                                # logical NCHW, channels-last memory
-        y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=True,
-                              pre_bias=self.proj[0].bias)
+        y = self._conv1_ln_fused(x)                                       # [B, h, w, C/2], or None
+        if y is None:
+            y = self._conv1(x)                                            # logical NCHW, channels-last memory
+            y = ops.layernorm_act(y.permute(0, 2, 3, 1).contiguous(), ln1.weight, ln1.bias, ln1.eps, act_swish=True,
+                                  pre_bias=self.proj[0].bias)
         y = F.conv2d(y.permute(0, 3, 1, 2), conv2.weight, None, conv2.stride, conv2.padding)
         y = y.permute(0, 2, 3, 1).contiguous()
         pos = pos_fn((y.shape[1], y.shape[2])) if pos_fn is not None else None
