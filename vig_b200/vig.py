@@ -1,8 +1,9 @@
 """ViG model shell around the CUDA-backed block: ``ViG`` of ``classification/models/vig.py:705-912`` in
 the configuration every shipped YAML uses (v2 patch embed, absolute pos-embed, no cls token, average-pool
 head, RMSNorm + SwiGLU blocks).  Parameter names match the reference so its checkpoints load.
-The stem convolutions, LayerNorm2d, bicubic pos-embed resize, pooling and the classifier run as PyTorch
-library calls; everything inside the blocks except the dense GEMMs is this library's kernels.
+The stem's first stage (convolution + LayerNorm2d + swish) is one kernel of this library for ViG-T in 16 bits; its
+second convolution, wider first stages, the bicubic pos-embed resize, pooling and the classifier run as PyTorch
+library calls; everything inside the blocks except the stacked input projection is this library's kernels.
 """
 import math
 from types import SimpleNamespace
