@@ -238,13 +238,21 @@ VIG_API int vig_layernorm_act_add_fwd(const void* x, const void* pre_bias, const
 VIG_API int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream);
 
 /*
+ * Fold of the input image into cells of 8 x 8 pixels on 8-pixel boundaries (bf16 / fp16, 3 channels):
+ * cells[b, cy, cx, (dy*3 + ic)*8 + dx] = x[b, ic, 8cy + dy, 8cx + dx].  x: [B, 3, H, W] contiguous, cells: [B, H/8, W/8, 192]
+ * contiguous; H, W multiples of 8.  Input of vig_stem_conv_ln_fwd.
+ */
+VIG_API int vig_stem_fold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int dtype, void* stream);
+
+/*
  * The stem's first convolution with its bias, the LayerNorm2d after it and the swish after that, as one tensor-core
- * kernel (bf16 / fp16; `V2PatchEmbed.proj[0..2]`, classification/models/vig.py:650-656, for kernel 9, stride 8, 3 input
- * channels and 96 output channels: ViG-T).  cells: [B, CH, CW, 192] from `vig_stem_unfold_fwd`.  w2: [96, 512], the
- * convolution's weight in the cell layout: columns 0..191 multiply cell (oy, ox), 192..383 cell (oy, ox+1), 384..447 the
- * first 64 values of cell (oy+1, ox), 448..511 the first 64 values of cell (oy+1, ox+1), each in the cell's value order
- * (dy*8 + dx)*3 + ic (the taps a 9 x 9 kernel has in the lower cells are among those values).  conv_bias (optional), ln_w,
- * ln_b: [96].  y: [B, CH-1, CW-1, 96] contiguous (channels last).  Same roundings as convolution -> bias add -> LayerNorm
+ * kernel (bf16 / fp16; `V2PatchEmbed.proj[0..2]`, classification/models/vig.py:650-656, for kernel 9, stride 8, padding 1,
+ * 3 input channels and 96 output channels: ViG-T).  cells: [B, CH, CW, 192] from `vig_stem_fold_fwd`.  w2: [96, 512], the
+ * convolution's weight in the cell layout: columns 0..191 multiply cell (oy, ox), 192..383 cell (oy, ox-1), 384..447 the
+ * last 64 values of cell (oy-1, ox), 448..511 the last 64 values of cell (oy-1, ox-1), each in the cell's value order
+ * (dy*3 + ic)*8 + dx (the window of output pixel (oy, ox) starts at image pixel (8oy - 1, 8ox - 1); the taps a 9 x 9 kernel
+ * has in the neighbouring cells are among those values; cells outside the image count as zeros).  conv_bias (optional),
+ * ln_w, ln_b: [96].  y: [B, CH, CW, 96] contiguous (channels last).  Same roundings as convolution -> bias add -> LayerNorm
  * run separately.  status_dev as in vig_bigla_fwd.
  */
 VIG_API int vig_stem_conv_ln_supported(int B, int CH, int CW, int cell, int N, int dtype);

@@ -157,7 +157,8 @@ def test_stem_conv_layernorm_fused_gemm(dtype, B, H, W, bias, act):
     x = torch.randn(B, 3, H, W, generator=g).to(dtype).cuda()
     conv, ln1 = pe.proj[0], pe.proj[1]
     with torch.no_grad():
-        cells = vig_b200.ops.stem_unfold(x, 8)
+        cells = vig_b200.ops.stem_fold(x)
+        assert torch.equal(cells, x.view(B, 3, H // 8, 8, W // 8, 8).permute(0, 2, 4, 3, 1, 5).reshape(B, H // 8, W // 8, 192))
         assert vig_b200.ops.stem_conv_ln_supported(cells, 96)
         got = vig_b200.ops.stem_conv_ln(cells, pe._gemm_weight(), conv.bias, ln1.weight, ln1.bias, ln1.eps, act_swish=act)
         # the steps it replaces

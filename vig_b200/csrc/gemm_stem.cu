@@ -2,11 +2,13 @@
 // one tcgen05 GEMM kernel (bf16 / fp16): classification/models/vig.py:650-656 (`V2PatchEmbed.proj[0..2]`, kernel s+1,
 // stride s, padding 1 with s = 8 and 3 input channels).
 //
-// The image has been folded into cells of 8 x 8 pixels (`vig_stem_unfold_fwd`: cells[b, cy, cx, (dy*8 + dx)*3 + ic] =
-// x[b, ic, 8cy + dy - 1, 8cx + dx - 1]), so the 9 x 9 window of output pixel (oy, ox) is cell (oy, ox), the first pixel
-// column of cell (oy, ox+1), the first pixel row of cell (oy+1, ox) and the first pixel of cell (oy+1, ox+1).  As a GEMM:
-// row = output pixel, K = 512 = both cells of the upper cell row (2 x 192) + the first 64 values of the two cells below (the
-// taps the kernel has there are among their first 24 and first 3 values; the weight matrix is zero elsewhere), N = 96.
+// The image has been folded into cells of 8 x 8 pixels on 8-pixel boundaries (`vig_stem_fold_fwd`, below: cells[b, cy, cx,
+// (dy*3 + ic)*8 + dx] = x[b, ic, 8cy + dy, 8cx + dx]; every run of 8 pixels is one aligned 16-byte vector, so the fold is a
+// permutation of vectors).  The 9 x 9 window of output pixel (oy, ox) starts one pixel up and left of cell (oy, ox): it is that
+// cell, the last pixel column of cell (oy, ox-1), the last pixel row of cell (oy-1, ox) and the last pixel of cell (oy-1, ox-1).
+// As a GEMM: row = output pixel, K = 512 = cells (oy, ox) and (oy, ox-1) in full (2 x 192) + the last 64 values of the two cells
+// above (the taps the kernel has there are among their last 24 values; the weight matrix is zero elsewhere), N = 96.  Cells
+// outside the image are read as zeros by the TMA unit, which is the convolution's padding.
 //
 // One persistent CTA per SM.  Its [96 x 512] weight matrix stays in shared memory for the whole launch (8 swizzled
 // boxes, 96 KB); tiles of 128 output pixels (Wt columns x Rt rows of the output, Wt * Rt = 128) stream through a ring of
@@ -26,7 +28,7 @@ namespace {
 using namespace tc;
 
 constexpr int SC_CELL = 192, SC_N = 96;
-constexpr int SC_KB = 8;                              // k boxes of 64 values: 3 + 3 from the upper cell row, 1 + 1 from the lower
+constexpr int SC_KB = 8;                              // k boxes of 64 values: 3 + 3 from the pixel's cell row, 1 + 1 from the row above
 constexpr int SC_THREADS = 64 + 256;
 constexpr int SC_W_BOX = SC_N * 128;                  // [96 rows x 64 k] = 12 KB
 constexpr int SC_A_BOX = 128 * 128;                   // [128 pixels x 64 k] = 16 KB
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(SC_THREADS, 1) stem_conv_ln_kernel(const __gri
                 coords(tile, b, oy0, ox0);
                 for (int kb = 0; kb < SC_KB; ++kb) {
                     // k box -> (cell row offset, cell column offset, first value inside the cell)
-                    const int cyo = kb >= 6, cxo = kb < 6 ? (kb >= 3) : (kb - 6), e0 = kb < 6 ? 64 * (kb % 3) : 0;
+                    const int cyo = kb >= 6 ? -1 : 0, cxo = kb < 6 ? (kb >= 3 ? -1 : 0) : 6 - kb, e0 = kb < 6 ? 64 * (kb % 3) : 128;
                     waiter.wait(bar_empty + 8 * st, phase ^ 1u);
                     if (*abort_flag) { live = false; break; }
                     mbar_expect_tx(bar_full + 8 * st, SC_A_BOX);
@@ -236,6 +238,28 @@ __global__ void __launch_bounds__(SC_THREADS, 1) stem_conv_ln_kernel(const __gri
     }
 }
 
+// image -> cells (16-bit types): cells[b, cy, cx, (dy*3 + ic)*8 + dx] = x[b, ic, 8cy + dy, 8cx + dx], as 16-byte vectors.
+// A block owns up to SF_CELLS consecutive cells of one cell row: 24 coalesced runs of the image (8 rows x 3 planes) go
+// into shared memory (rows padded by one vector: the transposed read below is then free of bank conflicts) and leave as
+// one contiguous run of cells.
+constexpr int SF_CELLS = 64, SF_THREADS = 256;
+
+__global__ void __launch_bounds__(SF_THREADS) stem_fold_kernel(const uint4* __restrict__ x, uint4* __restrict__ cells, int H, int W, int nseg) {
+    __shared__ uint4 tile[24][SF_CELLS + 1];
+    const int ch = H / 8, cw = W / 8;
+    int blk = blockIdx.x;
+    const int seg = blk % nseg; blk /= nseg;
+    const int cy = blk % ch, b = blk / ch;
+    const int cx0 = seg * SF_CELLS, ncell = min(SF_CELLS, cw - cx0);
+    for (int i = threadIdx.x; i < 24 * SF_CELLS; i += SF_THREADS) {
+        const int c = i % SF_CELLS, j = i / SF_CELLS, dy = j / 3, ic = j % 3;
+        if (c < ncell) tile[j][c] = __ldg(x + (((size_t)b * 3 + ic) * H + 8 * cy + dy) * cw + cx0 + c);
+    }
+    __syncthreads();
+    uint4* dst = cells + (((size_t)b * ch + cy) * cw + cx0) * 24;
+    for (int v = threadIdx.x; v < ncell * 24; v += SF_THREADS) dst[v] = tile[v % 24][v / 24];
+}
+
 // Output tile of 128 pixels as Wt columns x Rt rows: the split that covers the output with the fewest tiles (the widest on a tie).
 void sc_tile_shape(int OW, int OH, int& Wt, int& Rt) {
     int64_t best = -1;
@@ -253,7 +277,7 @@ using namespace vig;
 
 extern "C" int vig_stem_conv_ln_supported(int B, int CH, int CW, int cell, int N, int dtype) {
     if (dtype != VIG_DTYPE_BF16 && dtype != VIG_DTYPE_F16) return 0;
-    if (B <= 0 || CH < 2 || CW < 2 || cell != SC_CELL || N != SC_N) return 0;
+    if (B <= 0 || CH < 1 || CW < 1 || cell != SC_CELL || N != SC_N) return 0;
     return tc::encode_fn() != nullptr;
 }
 
@@ -263,7 +287,7 @@ extern "C" int vig_stem_conv_ln_fwd(const void* cells, const void* w2, const voi
     if (!cells || !w2 || !ln_w || !ln_b || !y) return VIG_ERR_NULL;
     if (!vig_stem_conv_ln_supported(B, CH, CW, cell, N, dtype)) return VIG_ERR_SHAPE;
     if ((reinterpret_cast<uintptr_t>(cells) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(y)) & 15) return VIG_ERR_ALIGN;
-    const int OH = CH - 1, OW = CW - 1;
+    const int OH = CH, OW = CW;
     int Wt = 128, Rt = 1;
     sc_tile_shape(OW, OH, Wt, Rt);
     const int tiles_x = (OW + Wt - 1) / Wt, tiles_y = (OH + Rt - 1) / Rt;
@@ -307,5 +331,18 @@ extern "C" int vig_stem_conv_ln_fwd(const void* cells, const void* w2, const voi
     }
     if (dtype == VIG_DTYPE_BF16) VIG_SC_LAUNCH(__nv_bfloat16) else VIG_SC_LAUNCH(__half)
 #undef VIG_SC_LAUNCH
+    return (int)cudaGetLastError();
+}
+
+extern "C" int vig_stem_fold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int dtype, void* stream) {
+    if (!x || !cells) return VIG_ERR_NULL;
+    if (dtype != VIG_DTYPE_BF16 && dtype != VIG_DTYPE_F16) return VIG_ERR_DTYPE;
+    if (B < 0 || Cin != 3 || H <= 0 || W <= 0 || H % 8 || W % 8) return VIG_ERR_SHAPE;
+    if (B == 0) return VIG_OK;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(cells)) & 15) return VIG_ERR_ALIGN;
+    const int nseg = (W / 8 + SF_CELLS - 1) / SF_CELLS;
+    const int64_t blocks = (int64_t)B * (H / 8) * nseg;
+    if (blocks >= (1ll << 31)) return VIG_ERR_SHAPE;
+    stem_fold_kernel<<<(int)blocks, SF_THREADS, 0, (cudaStream_t)stream>>>((const uint4*)x, (uint4*)cells, H, W, nseg);
     return (int)cudaGetLastError();
 }

@@ -458,6 +458,19 @@ def stem_unfold(x, s):
     return cells
 
 
+def stem_fold(x):
+    """Fold of a 16-bit image into cells of 8 x 8 pixels on 8-pixel boundaries: ``[B,3,H,W] -> [B, H/8, W/8, 192]`` with
+    ``cells[b, cy, cx, (dy*3 + ic)*8 + dx] = x[b, ic, 8cy + dy, 8cx + dx]`` (see ``vig_stem_fold_fwd``)."""
+    _lib.require_cuda(x)
+    B, Cin, H, W = x.shape
+    x = x.contiguous()
+    cells = torch.empty(B, H // 8, W // 8, 64 * Cin, dtype=x.dtype, device=x.device)
+    with torch.cuda.device_of(x):
+        st = _lib.lib().vig_stem_fold_fwd(_lib.ptr(x), _lib.ptr(cells), B, Cin, H, W, _lib.dtype_code(x), _lib.stream_ptr())
+    _lib.check(st, "vig_stem_fold_fwd")
+    return cells
+
+
 def stem_conv_ln_supported(cells, out_channels):
     """True when ``stem_conv_ln`` has a kernel for these cells (bf16 / fp16, cells of 192 values, 96 output channels)."""
     if not (cells.is_cuda and cells.dtype in (torch.bfloat16, torch.float16) and cells.dim() == 4 and cells.is_contiguous()):
@@ -468,7 +481,8 @@ def stem_conv_ln_supported(cells, out_channels):
 
 def stem_conv_ln(cells, w2, conv_bias, ln_weight, ln_bias, eps=1e-5, act_swish=True):
     """The stem's first convolution on unfolded cells + bias + LayerNorm over channels (+ swish) in one tensor-core
-    kernel (see ``vig_stem_conv_ln_fwd``).  cells: ``[B, CH, CW, 192]``, w2: ``[96, 512]``; returns ``[B, CH-1, CW-1, 96]``."""
+    kernel (see ``vig_stem_conv_ln_fwd``).  cells: ``[B, CH, CW, 192]`` from ``stem_fold``, w2: ``[96, 512]``; returns
+    ``[B, CH, CW, 96]``."""
     _lib.require_cuda(cells, w2, ln_weight, ln_bias)
     B, CH, CW, cell = cells.shape
     N = w2.shape[0]
@@ -477,7 +491,7 @@ def stem_conv_ln(cells, w2, conv_bias, ln_weight, ln_bias, eps=1e-5, act_swish=T
     for t in (conv_bias, ln_weight, ln_bias):
         if t is not None and (t.dtype != cells.dtype or t.numel() != N or t.device != cells.device):
             raise ValueError("conv_bias / ln_weight / ln_bias must be [N] vectors of the cells' dtype on the cells' device")
-    y = torch.empty(B, CH - 1, CW - 1, N, dtype=cells.dtype, device=cells.device)
+    y = torch.empty(B, CH, CW, N, dtype=cells.dtype, device=cells.device)
     with torch.cuda.device_of(cells):
         st = _lib.lib().vig_stem_conv_ln_fwd(_lib.ptr(cells), _lib.ptr(w2), _lib.ptr(conv_bias), _lib.ptr(ln_weight.contiguous()),
                                              _lib.ptr(ln_bias.contiguous()), _lib.ptr(y), B, CH, CW, cell, N, float(eps),

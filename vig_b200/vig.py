@@ -59,13 +59,24 @@ class V2PatchEmbed(nn.Module):
         return self._w_blocks[1]
 
     def _gemm_weight(self):
-        """[O, 512] weight of the fused first stage (``ops.stem_conv_ln``): both cells of the upper cell row in full, the
-        first 64 values of the two cells below (a 9 x 9 kernel's taps there are among them: the rest of the block weight
-        is zero by construction).  Cached per parameter version."""
-        wb = self._block_weight()                                          # [O, 192, 2 (cell row), 2 (cell column)]
-        if self._w_gemm is None or self._w_gemm[0] is not wb:
-            w2 = torch.cat([wb[:, :, 0, 0], wb[:, :, 0, 1], wb[:, :64, 1, 0], wb[:, :64, 1, 1]], dim=1).contiguous()
-            self._w_gemm = (wb, w2)
+        """[O, 512] weight of the fused first stage (``ops.stem_conv_ln``) for cells folded on 8-pixel boundaries, value
+        order (dy, ic, dx).  The 9 x 9 window of output pixel (oy, ox) starts at image pixel (8oy - 1, 8ox - 1): kernel rows /
+        columns 1..8 fall into cell (oy, ox), kernel column 0 into the last pixel column of cell (oy, ox-1), kernel row 0 into
+        the last pixel row of the cells above.  Columns: cell (oy, ox) | cell (oy, ox-1) | last 64 values of cell (oy-1, ox) |
+        last 64 values of cell (oy-1, ox-1).  Cached per parameter version."""
+        w = self.proj[0].weight
+        key = (w.dtype, w.device, w._version)
+        if self._w_gemm is None or self._w_gemm[0] != key:
+            wd = w.detach()
+            O = wd.shape[0]
+            main = wd[:, :, 1:, 1:].permute(0, 2, 1, 3).reshape(O, 192)                  # (dy, ic, dx) <- kernel (dy+1, dx+1)
+            left = wd.new_zeros(O, 8, 3, 8)
+            left[:, :, :, 7] = wd[:, :, 1:, 0].permute(0, 2, 1)                          # dx = 7 <- kernel column 0
+            top = wd.new_zeros(O, 64)                                                    # values 128..191 of the cell above
+            top.view(O, 8, 8)[:, 5:, :] = wd[:, :, 0, 1:]                                # dy = 7: values 168 + 8 ic + dx
+            corner = wd.new_zeros(O, 64)
+            corner.view(O, 8, 8)[:, 5:, 7] = wd[:, :, 0, 0]
+            self._w_gemm = (key, torch.cat([main, left.reshape(O, 192), top, corner], dim=1).contiguous())
         return self._w_gemm[1]
 
     def _conv1_ln_fused(self, x):
@@ -77,9 +88,9 @@ class V2PatchEmbed(nn.Module):
         if not (self.fuse_conv1 and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and s == 8 and Cin == 3
                 and H % s == 0 and W % s == 0 and conv.weight.dtype == x.dtype):
             return None
-        if not ops._lib.lib().vig_stem_conv_ln_supported(B, H // s + 1, W // s + 1, s * s * Cin, conv.weight.shape[0], ops._lib.dtype_code(x)):
+        if not ops._lib.lib().vig_stem_conv_ln_supported(B, H // s, W // s, s * s * Cin, conv.weight.shape[0], ops._lib.dtype_code(x)):
             return None
-        cells = ops.stem_unfold(x, s)
+        cells = ops.stem_fold(x)
         return ops.stem_conv_ln(cells, self._gemm_weight(), conv.bias, ln1.weight, ln1.bias, ln1.eps, act_swish=True)
 
     def _conv1(self, x):
