@@ -204,7 +204,7 @@ def main():
     scan_events = []
     timing = {"on": False}
     orig = {n: getattr(vops, n) for n in ("bi_gla", "dwconv3x3", "gate_inject", "add_rmsnorm", "swiglu", "linear_swiglu",
-                                          "linear_add_rmsnorm", "layernorm_act", "stem_unfold", "stem_conv_ln", "linear_bias")
+                                          "linear_add_rmsnorm", "layernorm_act", "stem_unfold", "stem_fold", "stem_conv_ln", "linear_bias")
             if hasattr(vops, n)}
     L = (size // 16) ** 2
     nseg = (L + 255) // 256                       # 256-token segments of the tensor-core scan
