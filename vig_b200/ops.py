@@ -479,6 +479,16 @@ def stem_conv_ln_supported(cells, out_channels):
     return bool(_lib.lib().vig_stem_conv_ln_supported(B, CH, CW, cell, int(out_channels), _lib.dtype_code(cells)))
 
 
+def stem_conv_ln_supported_for_image(x, out_channels):
+    """The same question asked of the image ``[B, 3, H, W]`` before it is folded (``stem_fold`` then ``stem_conv_ln``)."""
+    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 4 and x.shape[1] == 3):
+        return False
+    B, _, H, W = x.shape
+    if H % 8 or W % 8:
+        return False
+    return bool(_lib.lib().vig_stem_conv_ln_supported(B, H // 8, W // 8, 192, int(out_channels), _lib.dtype_code(x)))
+
+
 def stem_conv_ln(cells, w2, conv_bias, ln_weight, ln_bias, eps=1e-5, act_swish=True):
     """The stem's first convolution on unfolded cells + bias + LayerNorm over channels (+ swish) in one tensor-core
     kernel (see ``vig_stem_conv_ln_fwd``).  cells: ``[B, CH, CW, 192]`` from ``stem_fold``, w2: ``[96, 512]``; returns

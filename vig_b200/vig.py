@@ -84,11 +84,7 @@ class V2PatchEmbed(nn.Module):
         the shape has no such kernel (then the two steps run separately)."""
         from . import ops
         conv, ln1, s = self.proj[0], self.proj[1], self.stride
-        B, Cin, H, W = x.shape
-        if not (self.fuse_conv1 and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and s == 8 and Cin == 3
-                and H % s == 0 and W % s == 0 and conv.weight.dtype == x.dtype):
-            return None
-        if not ops._lib.lib().vig_stem_conv_ln_supported(B, H // s, W // s, s * s * Cin, conv.weight.shape[0], ops._lib.dtype_code(x)):
+        if not (self.fuse_conv1 and s == 8 and conv.weight.dtype == x.dtype and ops.stem_conv_ln_supported_for_image(x, conv.weight.shape[0])):
             return None
         cells = ops.stem_fold(x)
         return ops.stem_conv_ln(cells, self._gemm_weight(), conv.bias, ln1.weight, ln1.bias, ln1.eps, act_swish=True)
