@@ -228,6 +228,12 @@ VIG_API int vig_layernorm_act_fwd(const void* x, const void* pre_bias, const voi
  * (classification/models/vig.py:860-866) folded in. */
 VIG_API int vig_layernorm_act_add_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, const void* post_add,
                                       int64_t post_period, void* y, int64_t rows, int N, float eps, int act_swish, int dtype, void* stream);
+/* The same (post_add optional here), with the RMSNorm that follows as a second output: h = y * rsqrt(mean(y^2) + rms_eps) * rms_w
+ * from the rounded y, like vig_add_rmsnorm_fwd on y -- the stem's last LayerNorm2d, the position-embedding add and the first
+ * block's `attn_norm` (classification/models/vig.py:596-600) in one pass over the tokens. */
+VIG_API int vig_layernorm_act_add_rmsnorm_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, const void* post_add,
+                                              int64_t post_period, void* y, const void* rms_w, float rms_eps, void* h, int64_t rows, int N,
+                                              float eps, int act_swish, int dtype, void* stream);
 
 /*
  * Space-to-depth of the input image for the stem's first convolution (`V2PatchEmbed`, classification/models/vig.py:

@@ -121,6 +121,24 @@ def test_layernorm_with_trailing_add(dtype):
     assert torch.equal(got, ref)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("N,with_pos", [(192, True), (384, True), (768, False), (96, False)])
+def test_layernorm_with_rmsnorm_as_second_output(dtype, N, with_pos):
+    """LayerNorm (+ position add) with the following RMSNorm out of the same pass == the two kernels run one after the other."""
+    import vig_b200
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn(3, 35, N, generator=g).to(dtype).cuda()
+    w, b = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype).cuda(), (0.1 * torch.randn(N, generator=g)).to(dtype).cuda()
+    pb = (0.2 * torch.randn(N, generator=g)).to(dtype).cuda()
+    rw = (1 + 0.1 * torch.randn(N, generator=g)).to(dtype).cuda()
+    pos = torch.randn(1, 35, N, generator=g).to(dtype).cuda() if with_pos else None
+    y, h = vig_b200.ops.layernorm_act(x, w, b, 1e-6, False, pre_bias=pb, post_add=pos, rms_weight=rw, rms_eps=1e-6)
+    y_ref = vig_b200.ops.layernorm_act(x, w, b, 1e-6, False, pre_bias=pb, post_add=pos)
+    h_ref = vig_b200.ops.add_rmsnorm(y_ref, rw, eps=1e-6)
+    assert torch.equal(y, y_ref)
+    assert torch.equal(h, h_ref)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("B,H,W", [(2, 32, 48), (1, 8, 8), (3, 224, 224)])

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "vig_linear_add_rmsnorm_supported": (c_int, [c_int64, c_int, c_int, c_int]),
     "vig_linear_add_rmsnorm_fwd": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
     "vig_layernorm_act_add_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_void_p, c_int64, c_int, c_float, c_int, c_int, c_void_p]),
+    "vig_layernorm_act_add_rmsnorm_fwd": (c_int, [c_void_p] * 5 + [c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int64, c_int, c_float, c_int, c_int, c_void_p]),
     "vig_stem_unfold_fwd": (c_int, [c_void_p, c_void_p] + [c_int] * 6 + [c_void_p]),
     "vig_stem_fold_fwd": (c_int, [c_void_p, c_void_p] + [c_int] * 5 + [c_void_p]),
     "vig_stem_conv_ln_supported": (c_int, [c_int] * 6),

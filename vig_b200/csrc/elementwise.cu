@@ -330,7 +330,8 @@ template <typename T, int MAXV>
 __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __restrict__ x, const T* __restrict__ pre_bias,
                                                                    const T* __restrict__ w, const T* __restrict__ bias,
                                                                    const T* __restrict__ post_add, int64_t post_period,
-                                                                   T* __restrict__ y, int64_t rows, int N, float eps, int act) {
+                                                                   T* __restrict__ y, int64_t rows, int N, float eps, int act,
+                                                                   const T* __restrict__ rms_w, float rms_eps, T* __restrict__ h_out) {
     constexpr int V = DType<T>::VEC;
     const int lane = threadIdx.x & 31;
     const int nv = N / V;
@@ -369,6 +370,7 @@ __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __re
 #pragma unroll
         for (int m = 16; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
         const float rstd = rsqrtf(ss / (float)N + eps);
+        float ss2 = 0.f;                                 // sum of squares of the finished row, for the RMSNorm that may follow
 #pragma unroll
         for (int m = 0; m < MAXV; ++m) {
             const int vi = lane + m * 32;
@@ -390,6 +392,27 @@ __global__ void __launch_bounds__(EW_THREADS) layernorm_act_kernel(const T* __re
                     ov.from_float(val[m]);
                 }
                 ov.store(y + r * N + vi * V);
+                if (h_out) {                             // the rounded row, as a separate norm kernel would read it
+                    ov.to_float(val[m]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) ss2 = fmaf(val[m][i], val[m][i], ss2);
+                }
+            }
+        }
+        if (h_out) {                                     // h = RMSNorm(y) * rms_w: the arithmetic of add_rmsnorm_kernel
+#pragma unroll
+            for (int m = 16; m >= 1; m >>= 1) ss2 += __shfl_xor_sync(0xffffffffu, ss2, m);
+            const float rstd2 = rsqrtf(ss2 / (float)N + rms_eps);
+#pragma unroll
+            for (int m = 0; m < MAXV; ++m) {
+                const int vi = lane + m * 32;
+                if (vi < nv) {
+                    Vec16<T> wv; wv.load_nc(rms_w + vi * V);
+                    float wf[V]; wv.to_float(wf);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[m][i] = val[m][i] * rstd2 * wf[i];
+                    Vec16<T> hv; hv.from_float(val[m]); hv.store(h_out + r * N + vi * V);
+                }
             }
         }
     }
@@ -537,11 +560,11 @@ int add_rmsnorm_t(const void* x, const void* res, const void* w, void* y, void* 
 
 template <typename T>
 int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b, const void* pa, int64_t pa_period, void* y, int64_t rows, int N,
-                    float eps, int act, cudaStream_t s) {
+                    float eps, int act, cudaStream_t s, const void* rms_w = nullptr, float rms_eps = 0.f, void* h_out = nullptr) {
     constexpr int V = DType<T>::VEC;
     if (N % V) return VIG_ERR_SHAPE;
     const int nv = N / V;
-    if (nv <= 16 && !pa) {
+    if (nv <= 16 && !pa && !h_out) {
         const int lpr = nv <= 8 ? 8 : 16;
         const int g = grid_for(rows * lpr, EW_THREADS);
         if (lpr == 8) layernorm_act_short_kernel<T, 8><<<g, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (T*)y, rows, N, eps, act);
@@ -549,7 +572,7 @@ int layernorm_act_t(const void* x, const void* pb, const void* w, const void* b,
         return (int)cudaGetLastError();
     }
     const int grid = grid_for(rows * 32, EW_THREADS);
-#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (const T*)pa, pa_period, (T*)y, rows, N, eps, act)
+#define VIG_LN(MV) layernorm_act_kernel<T, MV><<<grid, EW_THREADS, 0, s>>>((const T*)x, (const T*)pb, (const T*)w, (const T*)b, (const T*)pa, pa_period, (T*)y, rows, N, eps, act, (const T*)rms_w, rms_eps, (T*)h_out)
     if (nv <= 32) VIG_LN(1); else if (nv <= 64) VIG_LN(2); else if (nv <= 128) VIG_LN(4);
     else if (nv <= 256) VIG_LN(8); else return VIG_ERR_SHAPE;
 #undef VIG_LN
@@ -644,6 +667,19 @@ extern "C" int vig_layernorm_act_add_fwd(const void* x, const void* pre_bias, co
     if (rows == 0) return VIG_OK;
     if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y) || !aligned16(post_add)) return VIG_ERR_ALIGN;
     VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, post_add, post_period, y, rows, N, eps, act_swish, (cudaStream_t)stream))
+}
+
+extern "C" int vig_layernorm_act_add_rmsnorm_fwd(const void* x, const void* pre_bias, const void* w, const void* bias, const void* post_add,
+                                                int64_t post_period, void* y, const void* rms_w, float rms_eps, void* h, int64_t rows, int N,
+                                                float eps, int act_swish, int dtype, void* stream) {
+    if (!x || !w || !bias || !y || !rms_w || !h) return VIG_ERR_NULL;
+    if (pre_bias && !aligned16(pre_bias)) return VIG_ERR_ALIGN;
+    if (rows < 0 || N <= 0 || (post_add && post_period <= 0)) return VIG_ERR_SHAPE;
+    if (rows == 0) return VIG_OK;
+    if (!aligned16(x) || !aligned16(w) || !aligned16(bias) || !aligned16(y) || !aligned16(rms_w) || !aligned16(h) || (post_add && !aligned16(post_add)))
+        return VIG_ERR_ALIGN;
+    VIG_DISPATCH(dtype, layernorm_act_t<T>(x, pre_bias, w, bias, post_add, post_add ? post_period : 1, y, rows, N, eps, act_swish, (cudaStream_t)stream,
+                                           rms_w, rms_eps, h))
 }
 
 extern "C" int vig_stem_unfold_fwd(const void* x, void* cells, int B, int Cin, int H, int W, int s, int dtype, void* stream) {

@@ -394,16 +394,29 @@ def add_rmsnorm(x, weight, residual=None, eps=1e-6, prenorm=False):
     return y
 
 
-def layernorm_act(x, weight, bias, eps=1e-5, act_swish=False, pre_bias=None, post_add=None):
+def layernorm_act(x, weight, bias, eps=1e-5, act_swish=False, pre_bias=None, post_add=None, rms_weight=None, rms_eps=1e-6):
     """LayerNorm over the last (contiguous) dimension with affine parameters and optional swish
     (``LayerNorm2d`` of ``classification/models/vig.py:619-624`` on channels-last data).  ``pre_bias`` is an
     optional per-channel vector added to ``x`` first (the bias of the convolution that produced ``x``);
-    ``post_add`` an optional ``[P, N]`` tensor added to row ``r`` as ``post_add[r % P]`` (the position embedding)."""
+    ``post_add`` an optional ``[P, N]`` tensor added to row ``r`` as ``post_add[r % P]`` (the position embedding).
+    With ``rms_weight`` the RMSNorm of the result comes out of the same pass: returns ``(y, RMSNorm(y) * rms_weight)``."""
     _lib.require_cuda(x, weight, bias)
     if not x.is_contiguous():
         raise ValueError("x must be contiguous")
     N = x.shape[-1]
     y = torch.empty_like(x)
+    if rms_weight is not None:
+        _lib.require_cuda(rms_weight)
+        if rms_weight.dtype != x.dtype or rms_weight.numel() != N:
+            raise ValueError("rms_weight must be an [N] vector of x's dtype")
+        pa = post_add.reshape(-1, N).to(x.dtype).contiguous() if post_add is not None else None
+        h = torch.empty_like(x)
+        st = _lib.lib().vig_layernorm_act_add_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(pre_bias), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(pa),
+                                                          pa.shape[0] if pa is not None else 1, _lib.ptr(y), _lib.ptr(rms_weight.contiguous()),
+                                                          float(rms_eps), _lib.ptr(h), x.numel() // N, N, float(eps), int(bool(act_swish)),
+                                                          _lib.dtype_code(x), _lib.stream_ptr())
+        _lib.check(st, "vig_layernorm_act_add_rmsnorm_fwd")
+        return y, h
     if post_add is not None:
         pa = post_add.reshape(-1, N).to(x.dtype).contiguous()
         st = _lib.lib().vig_layernorm_act_add_fwd(_lib.ptr(x), _lib.ptr(pre_bias), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(pa), pa.shape[0],

@@ -104,8 +104,10 @@ class V2PatchEmbed(nn.Module):
             cells = xp.view(B, H // s + 1, s, W // s + 1, s, Cin).permute(0, 1, 3, 2, 4, 5).reshape(B, H // s + 1, W // s + 1, s * s * Cin)
         return F.conv2d(cells.permute(0, 3, 1, 2), self._block_weight(), None)
 
-    def forward(self, x, pos_fn=None):
-        """``pos_fn(hw) -> [1, h*w, C]`` (optional): the position embedding, added inside the last LayerNorm kernel."""
+    def forward(self, x, pos_fn=None, next_norm=None):
+        """``pos_fn(hw) -> [1, h*w, C]`` (optional): the position embedding, added inside the last LayerNorm kernel.
+        ``next_norm`` (optional, an ``RMSNorm``): its output on the tokens comes out of the same kernel; the call then
+        returns ``(tokens, hw, next_norm(tokens))``."""
         from . import ops
         ln1, ln2, conv2 = self.proj[1], self.proj[4], self.proj[3]
         # the convolutions run without their bias; it is added inside the LayerNorm kernel that follows
@@ -117,8 +119,12 @@ class V2PatchEmbed(nn.Module):
         y = F.conv2d(y.permute(0, 3, 1, 2), conv2.weight, None, conv2.stride, conv2.padding)
         y = y.permute(0, 2, 3, 1).contiguous()
         pos = pos_fn((y.shape[1], y.shape[2])) if pos_fn is not None else None
-        y = ops.layernorm_act(y, ln2.weight, ln2.bias, ln2.eps, act_swish=False, pre_bias=conv2.bias, post_add=pos)
         B, h, w, C = y.shape
+        if next_norm is not None:
+            y, normed = ops.layernorm_act(y, ln2.weight, ln2.bias, ln2.eps, act_swish=False, pre_bias=conv2.bias, post_add=pos,
+                                          rms_weight=next_norm.weight, rms_eps=next_norm.eps)
+            return y.view(B, h * w, C), (h, w), normed.view(B, h * w, C)
+        y = ops.layernorm_act(y, ln2.weight, ln2.bias, ln2.eps, act_swish=False, pre_bias=conv2.bias, post_add=pos)
         return y.view(B, h * w, C), (h, w)
 
 
@@ -173,15 +179,18 @@ class ViG(nn.Module):
         return self._pos_cache[key]
 
     def forward_features(self, x):
-        x, hw = self.patch_embed(x, pos_fn=self._pos)  # position embedding added by the stem's last kernel
         # ``fuse_norm_epilogues``: every residual add + RMSNorm runs as the epilogue of the projection in front of it
-        # (hidden size <= 192, 16-bit tensors; measured 74 + 104 us against 112 + 141 us for cuBLAS + the norm kernel).
-        if self.fuse_norm_epilogues and len(self.blocks) and all(blk.fused_epilogues_supported(x) for blk in self.blocks):
-            h, residual = self.blocks[0].attn_norm(x), x
+        # (hidden size <= 192, 16-bit tensors; measured 74 + 104 us against 112 + 141 us for cuBLAS + the norm kernel),
+        # and the first block's norm comes out of the stem's last kernel.
+        probe = x.new_empty(1, 1, self.embed_dim)
+        if self.fuse_norm_epilogues and len(self.blocks) and all(blk.fused_epilogues_supported(probe) for blk in self.blocks):
+            x, hw, h = self.patch_embed(x, pos_fn=self._pos, next_norm=self.blocks[0].attn_norm)
+            residual = x
             for i, blk in enumerate(self.blocks):
                 nxt = self.blocks[i + 1].attn_norm if i + 1 < len(self.blocks) else self.norm
                 h, residual = blk.forward_prenormed(h, residual, nxt, patch_resolution=hw)
             return h.mean(dim=1)
+        x, hw = self.patch_embed(x, pos_fn=self._pos)  # position embedding added by the stem's last kernel
         h, residual = x, None
         for blk in self.blocks:
             h, residual = blk.forward_deferred(h, residual, patch_resolution=hw)
