@@ -113,3 +113,23 @@ def test_halo_rows_come_from_the_two_neighbours_only():
             assert torch.equal(top, ret[r - 1][3])            # the last row of the rank above
         if r < world - 1:
             assert torch.equal(bottom, ret[r + 1][2])         # the first row of the rank below
+
+
+@pytest.mark.parametrize("size,world", [(224, 2), (224, 3), (320, 4), (128, 8)])
+def test_stem_split_by_image_rows_matches_whole_stem(size, world):
+    """The row split of the stem that ``vig_forward_sequence_parallel`` performs (own image rows plus the patch row above,
+    first patch row of the result dropped) reproduces the stem of the whole image: written with the oracle's stem on CPU."""
+    shape = oracle.ViGShape(192, 3, 1, 1.0, 1.0, True, True, num_classes=16)
+    sd = {k: v.float() for k, v in oracle.make_state_dict(shape, seed=3).items()}
+    images = oracle.make_images(2, size, seed=size)
+    whole, (h, w) = oracle.patch_embed_v2(sd, images)
+    whole = whole.view(2, h, w, -1)
+    patch = 16
+    for rank in range(world):
+        r0, r1 = seqsplit.row_range(h, rank, world)
+        top = 1 if r0 > 0 else 0
+        sub = images[:, :, patch * (r0 - top):patch * r1]
+        tokens, (hs, ws) = oracle.patch_embed_v2(sd, sub)
+        assert (hs, ws) == (r1 - r0 + top, w)
+        part = tokens.view(2, hs, w, -1)[:, top:]
+        assert rel_err(part, whole[:, r0:r1]) < 1e-5
